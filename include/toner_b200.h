@@ -1,0 +1,198 @@
+/* toner_b200 -- C ABI of the B200 (sm_100a) kernels behind the Toner optimizer step.
+ *
+ * The reference project is pure Python (PyTorch + Triton); it has no FFI of its own.  Each entry point
+ * below therefore names the reference *operator* it stands in for (path inside the reference project
+ * and line range), which is the seam a maintainer would rebind.
+ *
+ * Conventions
+ *   - plain pointers and sizes only; every pointer is a CUDA device pointer unless said otherwise
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it, nothing synchronises
+ *     unless documented
+ *   - return value 0 = ok, > 0 = host-detected error (toner_last_error() gives the text)
+ *   - numerical / device conditions are reported through int status words in device memory
+ *   - the library never allocates caller-visible memory: scratch is a caller-provided workspace whose
+ *     size comes from the matching *_workspace_bytes query.  (The per-device context keeps one small
+ *     private arena for TMA tensor maps, created on first use.)
+ *   - matrices are row-major FP32 unless said otherwise; "stack" means `batch` equally shaped matrices
+ *     stored back to back
+ *   - there is no CPU fallback: without a CUDA device every compute entry point fails
+ */
+#ifndef TONER_B200_H_
+#define TONER_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ library */
+int toner_init(int device);               /* create the context of `device` (optional: created on first use) */
+const char* toner_last_error(void);       /* text of the last host-side failure on this thread */
+int toner_sm_count(void);                 /* SM count of the current device (0 on failure) */
+/* Synchronise `stream`, then read and clear the device status word that kernels set when one of their
+ * bounded waits runs out (0 = healthy). */
+int toner_device_status(void* stream, int* status_out);
+
+/* ------------------------------------------------------------------ generic tensor-core product
+ * D[b] = alpha * sum_s A_s[b] * B_s[b]^T (+ beta * C[b]), 16-bit operands, FP32 accumulation in tensor
+ * memory.  This is the one contraction kernel under every operator below; it is exported for tests and
+ * for callers that want to fuse differently.  Replaces torch.mm/bmm(out_dtype=float32)
+ * (src/toner/linalg.py:18, src/toner/fast/muon.py:9-33), mm16 / apply16_raw (src/toner/fast/roots.py:95-119)
+ * and the Triton symmetric product (src/toner/fast/symm16.py:16-127). */
+typedef struct toner_operand {
+  const void* base;         /* first element of z-slice 0 (FP16 or BF16) */
+  const void* const* list;  /* optional HOST array of `batch` device pointers: separately allocated matrices */
+  int32_t rows, cols;       /* stored shape of one slice, cols contiguous */
+  int64_t ld;               /* elements between stored rows (multiple of 8) */
+  int64_t z_stride;         /* elements between z-slices */
+  int32_t nz;               /* number of z-slices reachable from base */
+  int32_t mn_major;         /* 0: stored as (M or N) x K;  1: stored as K x (M or N), i.e. a transposed view */
+  int32_t seg_z[3];         /* z-slice of batch 0 for each K segment */
+  int32_t z_step;           /* batch b reads z-slice seg_z[s] + b * z_step (0: every batch reads the same slice) */
+} toner_operand;
+
+typedef struct toner_gemm_desc {
+  toner_operand a, b;
+  int32_t m, n, k, batch;
+  int32_t segs;             /* 1..3 operand-plane pairs accumulated into one result */
+  int32_t fmt;              /* operand format: 0 FP16, 1 BF16 */
+  int32_t tri;              /* 1: result symmetric (m == n); compute only tiles meeting the upper triangle */
+  int32_t mirror;           /* with tri: also store the transposed element (full symmetric result) */
+  int32_t packed;           /* with tri: C / D are packed upper triangles, row r starts at r*n - r(r+1)/2 + r */
+  float alpha, beta;
+  const float* alpha_a;     /* optional per-batch factors multiplied into alpha */
+  const float* alpha_b;     /*   alpha_b is read at alpha_b[b * alpha_b_step] (0 means 1) */
+  const float* beta_v;      /* optional per-batch factor multiplied into beta */
+  int32_t alpha_b_step;
+  const float* c; int64_t ldc, c_bs;
+  float* d;       int64_t ldd, d_bs;       /* optional FP32 result */
+  void* d16;      int64_t ld16, d16_bs;    /* optional 16-bit copy of the result */
+  int32_t d16_fmt;                         /* 0 FP16, 1 BF16 */
+  float* sumsq;             /* optional per-batch accumulators (caller zeroes them): sum d^2, */
+  uint32_t* maxabs;         /*   max |d| as FP32 bits, */
+  uint32_t* maxaff;         /*   max |aff_a*[r==c] + aff_b*d| as FP32 bits */
+  float aff_a, aff_b;
+  int32_t tile_n;           /* 0 = choose; else 128 or 256 */
+  int32_t promote;          /* > 0: k-blocks (64 deep) per tensor-core accumulation chain; chains are summed in
+                               FP32 registers with round-to-nearest (the tensor core truncates).  0: one chain */
+} toner_gemm_desc;
+
+int toner_gemm(const toner_gemm_desc* desc, void* stream);
+
+/* ------------------------------------------------------------------ input statistics
+ * Upper-triangle SYRK  S_b = X_b^T X_b  over BF16 row buffers, FP32 accumulation.
+ *   mode 0  PACKED      out (k, n(n+1)/2) = S           replaces syrk_list_packed(acc=False)  src/toner/fast/syrk.py:192-217
+ *   mode 1  PACKED_ACC  out += S                        replaces syrk_list_packed(acc=True)   src/toner/fast/syrk.py:144-146,192-217
+ *   mode 2  EMA_FULL    out (k, n, n) = beta*out + gamma*S, mirrored   replaces syrk_ema     src/toner/fast/syrk.py:250-304
+ * Row buffers: either `x_list` (HOST array of k device pointers, as list_offsets() addresses separately
+ * allocated buffers, src/toner/fast/syrk.py:62-69) or a stack at `x_base` with `x_batch_stride` elements
+ * between buffers.  Each buffer is (rows, n) BF16 with `ld` elements between rows; n and ld multiples of 8. */
+int toner_syrk_upper(const void* const* x_list, const void* x_base, int64_t x_batch_stride, int32_t k,
+                     int32_t rows, int32_t n, int64_t ld, float* out, int32_t mode, float beta, float gamma,
+                     void* stream);
+
+/* C_b <- beta*C_b + gamma*S_b with S_b read from its packed upper triangle and mirrored.
+ * Replaces unpack_ema_ (src/toner/fast/syrk.py:220-247); general-path EMA src/toner/reference.py:79. */
+int toner_unpack_ema(const float* packed, float* ema, int32_t k, int32_t n, float beta, float gamma, void* stream);
+
+/* ------------------------------------------------------------------ FP32-accurate operand preparation
+ * Split an FP32 stack into FP16 hi/lo planes of x*scale, scale = power of two putting max|x| of each
+ * matrix in [2^13, 2^14); planes layout [2][batch][rows][cols] (hi plane first), inv_scale[b] = 1/scale.
+ * Optionally the source is  aff_a*I + aff_b*x  (used to form T = alpha*I - beta*M on the fly).
+ * `x_list` (DEVICE array of batch pointers) may replace x for separately allocated matrices.
+ * `maxabs` (DEVICE, FP32 bits, batch entries) must hold max|source|; pass NULL to have it computed here
+ * into the first `batch` words of `scratch` (DEVICE, >= 4*batch bytes).
+ * Replaces _hi_lo / _cols_hi_scaled / rows_lo (src/toner/fast/roots.py:47-81). */
+int toner_split16(const float* x, const float* const* x_list, int32_t batch, int32_t rows, int32_t cols,
+                  int64_t ld, int64_t bs, float aff_a, float aff_b, const uint32_t* maxabs, void* scratch,
+                  void* planes, float* inv_scale, void* stream);
+
+/* ------------------------------------------------------------------ factor engine
+ * Inverse roots of the damped, trace-normalised statistics, as the general path computes them with eigh
+ * (input_factors, src/toner/linalg.py:54-89) and the fast path with exact_eigh_powers / its cached-basis
+ * iteration (src/toner/fast/roots.py:293-336,466-482):
+ *     A_b = sym(C_b) / mean(diag C_b) + damping * I
+ *     root_lo[b] = A_b^(-1/p)          root_hi[b] = A_b^(-q/p)   (q a power of two dividing p; q == 1: not written)
+ *     fro2_lo[b] = ||root_lo[b]||_F^2  (gives the decay normalisation n / ||R||_F^2, src/toner/linalg.py:87-88)
+ * Method: coupled Newton iteration T = a I - b M, X <- X T, M <- T^p M with minimax-scaled (a, b), batched
+ * over the k statistics, all products FP32-accurate on tensor cores (FP16 hi/lo planes, three plane products
+ * per accumulator).  `iters` <= 0 selects toner_inv_roots_iterations(n, damping, p), which depends only on
+ * its arguments (e.g. 9 for p = 8, 10 for p = 4, 12 for p = 2 at n = 5632, damping 1e-3).
+ * status[b] (DEVICE, optional): 0 converged, 1 residual max|I - M| above 0.05 before the last step,
+ * 2 non-finite.  The caller decides what to do with a non-zero status (the Python host recomputes that
+ * statistic with an eigendecomposition, as the reference's fallback does, src/toner/fast/engine.py:714-731).
+ * Workspace: toner_inv_roots_workspace_bytes(chunk, n) lets `chunk` statistics be processed at once; a
+ * smaller workspace makes the call loop over chunks (it must hold at least one statistic). */
+size_t toner_inv_roots_workspace_bytes(int32_t chunk, int32_t n);
+int toner_inv_roots_iterations(int32_t n, float damping, int32_t p);
+int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
+                    float* root_lo, float* root_hi, float* fro2_lo, int32_t* status, void* workspace,
+                    size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ Newton-Schulz polar iteration
+ * x = u / (||u||_F + eps); `steps` times  A = x x^T (on the short side),  x <- a x + (b A + c A A) x  with
+ * (a, b, c) = (3.4445, -4.7750, 2.0315); every product takes BF16-rounded operands and accumulates /
+ * outputs FP32 ("tpu" mode), x itself is carried in FP32.  Tall matrices are iterated through x^T x and
+ * x (b A + c A A), which is the same arithmetic as transposing first.
+ * Replaces newton_schulz_batched (src/toner/fast/muon.py:36-50) and newton_schulz(mode="tpu")
+ * (src/toner/linalg.py:22-51).  u and x_out are (batch, m, n) stacks and may alias; m, n multiples of 8.
+ * maxabs_out (optional, DEVICE, batch words): max |x| of the result as FP32 bits. */
+size_t toner_ns_polar_workspace_bytes(int32_t batch, int32_t m, int32_t n);
+int toner_ns_polar(const float* u, int32_t batch, int32_t m, int32_t n, int32_t steps, float eps, float* x_out,
+                   uint32_t* maxabs_out, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ elementwise update kernels
+ * Stacks are `count` matrices of `per` elements each (per a multiple of 4); gradient and weight tensors
+ * are caller-owned and separately allocated, so they come as DEVICE arrays of `count` device pointers. */
+
+/* out[b] = sum of squares of matrix b; bitwise reproducible (fixed reduction tree, no float atomics).
+ * Stands in for Tensor.norm()/matrix_norm (src/toner/reference.py:207,309-311; src/toner/linalg.py:41).
+ * scratch: toner_sumsq_scratch_bytes(batch) bytes. */
+size_t toner_sumsq_scratch_bytes(int32_t batch);
+int toner_sumsq(const float* x, int32_t batch, int32_t rows, int32_t cols, int64_t ld, int64_t bs, float* scratch,
+                float* out, void* stream);
+
+/* m <- mu*m + g ; u = nesterov ? g + mu*m : m ; maxabs[b] = max|u| (FP32 bits, optional).
+ * Replaces src/toner/reference.py:197-202 and _muont_in's momentum (src/toner/fast/engine.py:35-39). */
+int toner_muont_momentum(const float* const* grad_ptrs, float* m, float* u, int32_t count, int64_t per, float mu,
+                         int32_t nesterov, uint32_t* maxabs, void* stream);
+
+/* Per-matrix scalars of the MuonT update, from ||R_out||_F^2 of the statistic first + b*step:
+ * c1[b] = lr*wd*n/||R||^2 (shaped decay W R^2 / mean diag R^2), c2[b] = lr*scale*sqrt(n)/||R|| (R-hat).
+ * Replaces the scalar part of _muont_out (src/toner/fast/engine.py:42-51; src/toner/reference.py:206-215). */
+int toner_muont_coeffs(const float* fro2, int32_t first, int32_t step, int32_t count, int32_t n, float lr, float wd,
+                       float scale, float* c1, float* c2, void* stream);
+
+/* a[b] *= b[b]: folds a per-matrix scalar into an operand's inverse scale. */
+int toner_scale_vec(float* a, const float* b, int32_t count, void* stream);
+
+/* m <- beta1*m + (1-beta1)*g.  Replaces src/toner/reference.py:304 / _adamt (src/toner/fast/engine.py:21). */
+int toner_adamt_first_moment(const float* const* grad_ptrs, float* m, int32_t count, int64_t per, float beta1,
+                             void* stream);
+
+/* v <- beta2*v + (1-beta2)*t^2 ; num <- num / (sqrt(v/bc2) + eps) in place (num holds (m/bc1) R);
+ * maxabs[b] = max|num| afterwards.  Replaces src/toner/reference.py:306-308 / engine.py:23-24. */
+int toner_adamt_ratio(const float* t, float* v, float* num, int32_t count, int64_t per, float beta2, float bc2,
+                      float eps, uint32_t* maxabs, void* stream);
+
+/* c1[b] = lr*wd*n/||R||^2 ; c2[b] = -lr*||U||_F / max(||U R||_F, 1e-30) from the two sums of squares.
+ * Replaces the scalar part of src/toner/reference.py:309-313 / engine.py:26-32. */
+int toner_adamt_coeffs(const float* fro2, int32_t first, int32_t step, int32_t count, int32_t n, float lr, float wd,
+                       const float* ss_before, const float* ss_after, float* c1, float* c2, void* stream);
+
+/* out = a*x + b*y over n FP32 elements (16-byte aligned pointers).  The general path's statistic EMA
+ * C <- beta*C + (1-beta)*S on full matrices (src/toner/reference.py:79). */
+int toner_axpby(const float* x, const float* y, float* out, int64_t n, float a, float b, void* stream);
+
+/* out_b = coeff[b] * x_b (used for the AdamT change when weight_decay is zero: -lr ||U||/||U R|| U R). */
+int toner_scale_stack(const float* x, const float* coeff, float* out, int32_t count, int64_t per, void* stream);
+
+/* W_b += delta_b.  Replaces torch._foreach_add_ (src/toner/fast/engine.py:875). */
+int toner_apply_delta(float* const* weight_ptrs, const float* delta, int32_t count, int64_t per, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TONER_B200_H_ */

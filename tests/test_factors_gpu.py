@@ -1,0 +1,98 @@
+"""Factor engine (toner_inv_roots) against the CPU oracle's eigh factors and against FP64 truth.
+
+The FP32 eigh oracle is itself up to ~1e-3 away from the exact factor on ill-conditioned statistics
+(its eigenvalue error is ~1e-7 of the largest eigenvalue, against a damping floor of 1e-3), so each
+case measures the oracle's own distance from FP64 truth and allows for it."""
+
+import math
+
+import pytest
+import torch
+
+from oracle import toner_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DAMPING = 1e-3
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from toner_b200 import ops as _ops
+    return _ops
+
+
+def spd(n, cond, seed):
+    g = torch.Generator().manual_seed(seed)
+    q, _ = torch.linalg.qr(torch.randn(n, n, generator=g, dtype=torch.float64))
+    lam = torch.exp(torch.rand(n, generator=g, dtype=torch.float64) * math.log(cond))
+    return ((q * lam) @ q.T).float()
+
+
+def check_roots(ops, stats, p, q, tol_truth=5e-4):
+    ema = torch.stack(stats).cuda()
+    lo, hi, fro2, status = ops.inv_roots(ema, DAMPING, p, q)
+    ops.assert_healthy()
+    assert status.tolist() == [0] * len(stats)
+    for b, c in enumerate(stats):
+        s_lo, s_hi = 1.0 / p, q / p
+        inner, outer, decay = orc.input_factors(c, s_hi, s_lo, DAMPING)
+        for got, strength, oracle in ((lo[b], s_lo, outer), (hi[b] if q > 1 else lo[b], s_hi, inner)):
+            truth = orc.inverse_root_truth(c, strength, DAMPING)
+            e_truth = orc.rel_fro(got.cpu(), truth)
+            o_truth = orc.rel_fro(oracle, truth)
+            e_oracle = orc.rel_fro(got.cpu(), oracle)
+            # FP16 hi/lo operands carry 22 bits against FP32's 24: allow a few times the oracle's own error
+            assert e_truth < max(tol_truth, 3 * o_truth), (b, strength, e_truth, o_truth)
+            assert e_oracle < max(2e-3, 3 * o_truth), (b, strength, e_oracle, o_truth)
+        assert abs(fro2[b].item() - orc.fro(outer) ** 2) / orc.fro(outer) ** 2 < 1e-3
+        assert torch.equal(lo[b], lo[b].T)
+
+
+@pytest.mark.parametrize("p,q", [(8, 4), (4, 1), (2, 1)])
+def test_conditioning_sweep(ops, p, q):
+    check_roots(ops, [spd(256, cond, 7) for cond in (1e2, 1e4, 1e6)], p, q)
+
+
+def test_muont_powers_at_768(ops):
+    check_roots(ops, [spd(768, 1e4, 3), spd(768, 1e6, 4)], 8, 4)
+
+
+def test_rank_deficient_and_spiked_statistics(ops):
+    """A Gram of 40 rows in 256 dimensions (216 zero eigenvalues sit on the damping floor), and a
+    statistic with one dominant direction, as a mean activation gives."""
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(40, 256, generator=g)
+    low_rank = x.T @ x / 40
+    v = torch.randn(256, 1, generator=g)
+    spiked = spd(256, 1e3, 5)
+    spiked = spiked + (v @ v.T) * spiked.diagonal().mean() * 20
+    # The 216 floor eigenvalues are 2.5e-5 of ||A||_F: 22-bit operands resolve them to ~1e-3 relative, which
+    # the fourth power (A^-1/2 from A^-1/8) quadruples.  The FP32 eigh oracle is a few times closer here.
+    check_roots(ops, [low_rank, spiked], 8, 4, tol_truth=3e-3)
+
+
+def test_zero_statistic_gives_scaled_identity(ops):
+    ema = torch.zeros(1, 128, 128, device="cuda")
+    lo, hi, fro2, status = ops.inv_roots(ema, DAMPING, 4, 1)
+    ops.assert_healthy()
+    want = torch.eye(128) * DAMPING ** -0.25  # (0 / 1e-30 + damping)^(-1/4), as the eigh rule gives
+    assert status.item() == 0
+    assert orc.rel_fro(lo[0].cpu(), want) < 1e-5
+
+
+def test_chunked_workspace_gives_identical_roots(ops):
+    stats = torch.stack([spd(256, 1e3, s) for s in range(5)]).cuda()
+    full = ops.inv_roots(stats, DAMPING, 4, 1)[0]
+    small_ws = torch.empty(ops.inv_roots_workspace_bytes(2, 256), device="cuda", dtype=torch.uint8)
+    chunked = ops.inv_roots(stats, DAMPING, 4, 1, workspace=small_ws)[0]
+    ops.assert_healthy()
+    assert torch.equal(full, chunked)
+
+
+def test_iteration_counts_are_stated(ops):
+    assert ops.inv_roots_iterations(5632, 1e-3, 8) == 9
+    assert ops.inv_roots_iterations(5632, 1e-3, 4) == 10
+    assert ops.inv_roots_iterations(5632, 1e-3, 2) in (12, 13)
+    assert ops.inv_roots_iterations(768, 1e-3, 8) <= 9

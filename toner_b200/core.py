@@ -1,0 +1,297 @@
+"""Step arithmetic shared by the general optimizers and the layer-sharded engine.
+
+Everything numerical happens in the CUDA library (``ops``); this module sequences the launches for
+one *factor set* (a stack of equally sized input statistics) and one *matrix group* (a stack of
+equally shaped weights whose statistics sit at regular positions in a factor set).
+
+Numerical specification followed (reference files):
+  factors   src/toner/linalg.py:54-89      A = sym(C)/mean(diag C) + damping I, R_s = A^-s,
+                                           decay = R_out^2 n / ||R_out||_F^2
+  MuonT     src/toner/reference.py:186-215 m <- mu m + g, d = g + mu m, P = NS(d R_in),
+                                           W <- W - lr wd W decay - lr sqrt(max(1, out/in)) P R_out sqrt(n)/||R_out||_F
+  AdamT     src/toner/reference.py:287-313
+The two right-multiplications of the MuonT update are fused the way the reference's engine does it
+(src/toner/fast/engine.py:42-51):  delta = -((lr wd n/||R||^2) W R + (lr s sqrt(n)/||R||) P) R.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from . import ops
+
+
+class Scratch:
+    """Named persistent device buffers.  Stable addresses keep the library's TMA tensor maps cached."""
+
+    def __init__(self) -> None:
+        self._buffers: Dict[Tuple, torch.Tensor] = {}
+
+    def get(self, name: str, shape: Sequence[int], dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+        key = (name, tuple(shape), dtype, str(device))
+        buf = self._buffers.get(key)
+        if buf is None:
+            buf = torch.empty(tuple(shape), dtype=dtype, device=device)
+            self._buffers[key] = buf
+        return buf
+
+    def bytes_like(self, name: str, nbytes: int, device: torch.device) -> torch.Tensor:
+        """A byte workspace that only ever grows."""
+        key = (name, "bytes", str(device))
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < nbytes:
+            buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+            self._buffers[key] = buf
+        return buf
+
+
+def root_orders(strength_a: float, strength_b: float) -> Tuple[int, int]:
+    """Map two inverse-power strengths to (p, q): the weaker is A^(-1/p), the stronger A^(-q/p).
+
+    The Newton factor engine computes inverse p-th roots for p a power of two; other strengths are
+    rejected (the reference's fast path is narrower still: 1/8, 1/4, 1/2, src/toner/fast/adapter.py:169-171)."""
+    nz = [s for s in (strength_a, strength_b) if s != 0]
+    for s in nz:
+        inv = 1.0 / s
+        if s < 0 or abs(inv - round(inv)) > 1e-9 or int(round(inv)) & (int(round(inv)) - 1) or round(inv) > 32:
+            raise ValueError("strengths must be 0 or 1/p with p a power of two up to 32 "
+                             "(the factor engine is a coupled Newton inverse p-th root)")
+    if not nz:
+        return 1, 1
+    p = int(round(1.0 / min(nz)))
+    q = int(round(max(nz) * p))
+    return p, q
+
+
+class FactorSet:
+    """EMAs of k input statistics of width n and their inverse-power factors, stacked.
+
+    ``strengths`` = (inner, outer).  After :meth:`compute`, ``planes(which)`` gives the FP16 hi/lo planes
+    (2, k, n, n) and inverse scales (k,) of the requested factor, ``fro2_outer`` the squared Frobenius norm
+    of the outer factor."""
+
+    def __init__(self, k: int, n: int, device: torch.device, strengths: Tuple[float, float], damping: float,
+                 scratch: Optional[Scratch] = None, chunk: Optional[int] = None) -> None:
+        if n % 8:
+            raise ValueError("statistic width must be a multiple of 8 (TMA row pitch of the 16-bit operands)")
+        self.k, self.n, self.device, self.damping = k, n, device, float(damping)
+        self.inner_strength, self.outer_strength = float(strengths[0]), float(strengths[1])
+        self.p, self.q = root_orders(*strengths)
+        self.scratch = scratch or Scratch()
+        self.ema = torch.zeros(k, n, n, device=device, dtype=torch.float32)
+        self.weight = 0.0
+        self.root_lo = torch.empty(k, n, n, device=device, dtype=torch.float32)
+        self.root_hi = torch.empty(k, n, n, device=device, dtype=torch.float32) if self.q > 1 else None
+        self.fro2_lo = torch.empty(k, device=device, dtype=torch.float32)
+        self.fro2_hi = torch.empty(k, device=device, dtype=torch.float32) if self.q > 1 else None
+        self.status = torch.zeros(k, device=device, dtype=torch.int32)
+        self.status_host = torch.zeros(k, dtype=torch.int32).pin_memory()
+        self.status_event: Optional[torch.cuda.Event] = None
+        self.lo_planes = torch.empty(2, k, n, n, device=device, dtype=torch.float16)
+        self.lo_inv = torch.empty(k, device=device, dtype=torch.float32)
+        if self.q > 1:
+            self.hi_planes = torch.empty(2, k, n, n, device=device, dtype=torch.float16)
+            self.hi_inv = torch.empty(k, device=device, dtype=torch.float32)
+        else:
+            self.hi_planes, self.hi_inv = self.lo_planes, self.lo_inv
+        per = ops.inv_roots_workspace_bytes(1, n)
+        if chunk is None:
+            chunk = max(1, min(k, (6 << 30) // per))
+        self.workspace = self.scratch.bytes_like("inv_roots", ops.inv_roots_workspace_bytes(chunk, n), device)
+        self.iterations = ops.inv_roots_iterations(n, self.damping, self.p)
+        self.fallbacks = 0
+
+    # -- which stored root serves a given strength
+    def _is_hi(self, strength: float) -> bool:
+        return self.q > 1 and strength == max(self.inner_strength, self.outer_strength)
+
+    def planes(self, which: str) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+        s = self.inner_strength if which == "inner" else self.outer_strength
+        if s == 0:
+            return None, None  # identity factor: the product is skipped
+        return (self.hi_planes, self.hi_inv) if self._is_hi(s) else (self.lo_planes, self.lo_inv)
+
+    def root(self, which: str) -> Optional[torch.Tensor]:
+        s = self.inner_strength if which == "inner" else self.outer_strength
+        if s == 0:
+            return None
+        return self.root_hi if self._is_hi(s) else self.root_lo
+
+    @property
+    def fro2_outer(self) -> torch.Tensor:
+        if self.outer_strength == 0:
+            raise ValueError("outer strength 0 has no factor norm")
+        return self.fro2_hi if self._is_hi(self.outer_strength) else self.fro2_lo
+
+    def compute(self) -> None:
+        """Enqueue the Newton factor computation and the operand split of the results."""
+        if self.inner_strength == 0 and self.outer_strength == 0:
+            return
+        ops.inv_roots(self.ema, self.damping, self.p, self.q, root_lo=self.root_lo, root_hi=self.root_hi,
+                      fro2_lo=self.fro2_lo, status=self.status, workspace=self.workspace)
+        self._split()
+        self.status_host.copy_(self.status, non_blocking=True)
+        self.status_event = torch.cuda.Event()
+        self.status_event.record(torch.cuda.current_stream())
+
+    def _split(self) -> None:
+        tmp = self.scratch.get("split_max", (self.k,), torch.int32, self.device)
+        ops.split16(self.root_lo, planes=self.lo_planes, inv_scale=self.lo_inv, scratch=tmp)
+        if self.q > 1:
+            ops.split16(self.root_hi, planes=self.hi_planes, inv_scale=self.hi_inv, scratch=tmp)
+            ops.sumsq(self.root_hi, out=self.fro2_hi,
+                      scratch=self.scratch.bytes_like("sumsq", 256 * self.k, self.device))
+
+    def finish(self) -> int:
+        """Wait for the convergence flags only; recompute flagged statistics by eigendecomposition (the
+        reference's exact fallback, src/toner/fast/engine.py:714-731).  Returns how many were flagged."""
+        if self.status_event is None:
+            return 0
+        self.status_event.synchronize()
+        self.status_event = None
+        bad = [i for i, s in enumerate(self.status_host.tolist()) if s != 0]
+        if not bad:
+            return 0
+        self.fallbacks += len(bad)
+        for i in bad:
+            c = self.ema[i]
+            c = 0.5 * (c + c.T)
+            lam, vec = torch.linalg.eigh(c.double())
+            lam = lam.clamp_min(0)
+            unit = lam / lam.mean().clamp_min(1e-30)
+            self.root_lo[i] = ((vec * (unit + self.damping).pow(-1.0 / self.p)) @ vec.T).float()
+            if self.q > 1:
+                self.root_hi[i] = ((vec * (unit + self.damping).pow(-float(self.q) / self.p)) @ vec.T).float()
+        ops.sumsq(self.root_lo, out=self.fro2_lo, scratch=self.scratch.bytes_like("sumsq", 256 * self.k, self.device))
+        self._split()
+        return len(bad)
+
+
+class MatrixGroup:
+    """Equally shaped weights whose input statistics are entries first, first+step, ... of a FactorSet."""
+
+    def __init__(self, weights: Sequence[torch.Tensor], factors: FactorSet, first: int, step: int, kind: str) -> None:
+        self.weights = list(weights)
+        w0 = self.weights[0]
+        self.count = len(self.weights)
+        self.out_features, self.in_features = w0.shape
+        if self.in_features != factors.n:
+            raise ValueError("weight input width does not match its statistic")
+        if self.out_features % 8 or self.in_features % 8:
+            raise ValueError("matrix dimensions must be multiples of 8 (TMA row pitch of the 16-bit operands)")
+        for w in self.weights:
+            if w.shape != w0.shape or w.dtype != torch.float32 or not w.is_contiguous() or w.device != w0.device:
+                raise ValueError("a matrix group needs equally shaped, contiguous FP32 weights on one device")
+        self.factors, self.first, self.step, self.kind = factors, first, step, kind
+        self.device = w0.device
+        shape = (self.count, self.out_features, self.in_features)
+        self.m = torch.zeros(shape, device=self.device, dtype=torch.float32)
+        self.v = torch.zeros(shape, device=self.device, dtype=torch.float32) if kind == "adamt" else None
+        self.weight_ptrs = ops.pointer_table(self.weights)
+        self._grad_key: Optional[Tuple[int, ...]] = None
+        self._grad_ptrs: Optional[torch.Tensor] = None
+
+    def grad_ptrs(self, grads: Sequence[torch.Tensor]) -> torch.Tensor:
+        for g in grads:
+            if g.dtype != torch.float32 or not g.is_contiguous() or g.shape != self.weights[0].shape:
+                raise ValueError("gradients must be contiguous FP32 tensors of the weight's shape")
+        key = tuple(g.data_ptr() for g in grads)
+        if key != self._grad_key:
+            self._grad_ptrs = ops.pointer_table(grads)
+            self._grad_key = key
+        return self._grad_ptrs
+
+
+def _product(a_planes, a_inv, group: MatrixGroup, which: str, d, **kw) -> None:
+    """d[b] = A[b] @ R[first + b*step] in split precision, R the inner or outer factor (symmetric)."""
+    f = group.factors
+    r_planes, r_inv = f.planes(which)
+    count, m, n = group.count, group.out_features, group.in_features
+    a = ops.operand(a_planes, seg_z=(0, 0, count))
+    b = ops.operand(r_planes, seg_z=(group.first, f.k + group.first, group.first), z_step=group.step)
+    ops.gemm(a, b, m=m, n=n, k=n, batch=count, fmt=0, segs=3, d=d, alpha_a=a_inv,
+             alpha_b=r_inv[group.first:], alpha_b_step=group.step, promote=ops.PROMOTE_ACCURATE, **kw)
+
+
+def muont_group_delta(group: MatrixGroup, grads: Sequence[torch.Tensor], delta: torch.Tensor, scratch: Scratch, *,
+                      lr: float, weight_decay: float, momentum: float, nesterov: bool, ns_steps: int,
+                      ns_eps: float) -> None:
+    """Write the MuonT parameter change of every matrix of the group into ``delta`` (count, out, in)."""
+    f, dev = group.factors, group.device
+    count, m, n = group.count, group.out_features, group.in_features
+    shape = (count, m, n)
+    work = scratch.get("work", shape, torch.float32, dev)
+    planes = scratch.get("planes", (2,) + shape, torch.float16, dev)
+    inv = scratch.get("inv", (count,), torch.float32, dev)
+    maxabs = scratch.get("maxabs", (count,), torch.int32, dev)
+    c1 = scratch.get("c1", (count,), torch.float32, dev)
+    c2 = scratch.get("c2", (count,), torch.float32, dev)
+    ops.muont_momentum(group.grad_ptrs(grads), group.m, work, momentum, nesterov, maxabs)
+    if f.inner_strength != 0:
+        ops.split16(work, planes=planes, inv_scale=inv, maxabs=maxabs)
+        _product(planes, inv, group, "inner", work)
+    ns_ws = scratch.bytes_like("ns", ops.ns_polar_workspace_bytes(count, m, n), dev)
+    ops.ns_polar(work, ns_steps, ns_eps, out=work, maxabs=maxabs, workspace=ns_ws)
+    scale = max(1.0, m / n) ** 0.5
+    if f.outer_strength == 0:
+        # identity outer factor: delta = -(lr wd W + lr scale P)
+        raise ValueError("outer_strength 0 is not supported by the CUDA path")
+    ops.muont_coeffs(f.fro2_outer, group.first, group.step, count, n, lr, weight_decay, scale, c1, c2)
+    if weight_decay != 0:
+        ops.split16_list(group.weight_ptrs, count, m, n, planes, inv, maxabs)
+        ops.scale_vec(inv, c1)
+        maxabs.zero_()
+        _product(planes, inv, group, "outer", work, c=work, beta=1.0, beta_v=c2, maxabs=maxabs)  # V = c1 W R + c2 P
+        ops.split16(work, planes=planes, inv_scale=inv, maxabs=maxabs)
+    else:
+        ops.split16(work, planes=planes, inv_scale=inv, maxabs=maxabs)
+        ops.scale_vec(inv, c2)  # V = c2 P
+    _product(planes, inv, group, "outer", delta, alpha=-1.0)
+
+
+def adamt_group_delta(group: MatrixGroup, grads: Sequence[torch.Tensor], delta: torch.Tensor, scratch: Scratch, *,
+                      lr: float, weight_decay: float, betas: Tuple[float, float], eps: float, t: int) -> None:
+    """Write the AdamT parameter change of every matrix of the group into ``delta``."""
+    f, dev = group.factors, group.device
+    count, m, n = group.count, group.out_features, group.in_features
+    shape = (count, m, n)
+    b1, b2 = betas
+    bc1, bc2 = 1 - b1 ** t, 1 - b2 ** t
+    work = scratch.get("work", shape, torch.float32, dev)
+    work2 = scratch.get("work2", shape, torch.float32, dev)
+    planes = scratch.get("planes", (2,) + shape, torch.float16, dev)
+    inv = scratch.get("inv", (count,), torch.float32, dev)
+    maxabs = scratch.get("maxabs", (count,), torch.int32, dev)
+    c1 = scratch.get("c1", (count,), torch.float32, dev)
+    c2 = scratch.get("c2", (count,), torch.float32, dev)
+    ss0 = scratch.get("ss0", (count,), torch.float32, dev)
+    ss1 = scratch.get("ss1", (count,), torch.float32, dev)
+    ssq_ws = scratch.bytes_like("sumsq", 256 * count, dev)
+    gp = group.grad_ptrs(grads)
+    ops.adamt_first_moment(gp, group.m, b1)
+    ops.split16_list(gp, count, m, n, planes, inv, maxabs)
+    _product(planes, inv, group, "inner", work)                       # t = g R
+    ops.split16(group.m, planes=planes, inv_scale=inv, scratch=maxabs)
+    _product(planes, inv, group, "inner", work2, alpha=1.0 / bc1)     # (m / bc1) R
+    ops.adamt_ratio(work, group.v, work2, b2, bc2, eps, maxabs)       # U, in work2
+    ops.sumsq(work2, out=ss0, scratch=ssq_ws)
+    ops.split16(work2, planes=planes, inv_scale=inv, maxabs=maxabs)
+    _product(planes, inv, group, "inner", work)                       # U R
+    ops.sumsq(work, out=ss1, scratch=ssq_ws)
+    ops.adamt_coeffs(f.fro2_outer, group.first, group.step, count, n, lr, weight_decay, ss0, ss1, c1, c2)
+    if weight_decay != 0:
+        ops.split16_list(group.weight_ptrs, count, m, n, planes, inv, maxabs)
+        ops.scale_vec(inv, c1)
+        maxabs.zero_()
+        _product(planes, inv, group, "outer", work2, maxabs=maxabs)   # c1 W R
+        ops.split16(work2, planes=planes, inv_scale=inv, maxabs=maxabs)
+        _product(planes, inv, group, "outer", delta, alpha=-1.0, c=work, beta=1.0, beta_v=c2)
+    else:
+        ops.scale_stack(work, c2, delta)                              # delta = c2 * U R
+
+
+def apply_group_delta(group: MatrixGroup, delta: torch.Tensor) -> None:
+    ops.apply_delta(group.weight_ptrs, delta)

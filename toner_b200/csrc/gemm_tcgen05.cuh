@@ -1,0 +1,449 @@
+// Batched 16-bit-operand GEMM with FP32 accumulation in tensor memory, for sm_100a.
+//
+//   D[b] = alpha_b * sum_seg A_seg[b] * B_seg[b]^T   (+ beta_b * C[b])
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer: 128-byte-swizzled operand tiles into a shared-memory ring
+//   warp 1      allocates tensor memory and issues tcgen05.mma (one thread), accumulating in TMEM
+//   warps 2..9  epilogue: tcgen05.ld the accumulator (double-buffered, so it overlaps the next chain's
+//               MMAs), sum chains in registers, apply the affine epilogue, store FP32 / 16-bit results
+// The tensor core adds every 16-deep partial sum into its FP32 accumulator by truncation; over long K
+// that bias reaches 1e-5 relative.  Where FP32 accuracy matters (`promote`), accumulation chains are
+// kept short in TMEM and summed with round-to-nearest by the epilogue warps.
+// Operands may be stored K-major (k contiguous) or MN-major (m or n contiguous: a transposed view, as
+// in X^T X); symmetric results can be computed from the tiles that meet the upper triangle only and
+// mirrored on store.  "Segments" concatenate several operand planes along K into one accumulator,
+// which is how the FP32-accurate product  Ah*Bh + Ah*Bl + Al*Bh  of FP16 hi/lo splits is formed.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace toner {
+
+constexpr int kBM = 128;          // tile rows (UMMA M)
+constexpr int kBK = 64;           // 16-bit elements per k-block: one 128-byte swizzle row
+constexpr int kUmmaK = 16;        // K per tcgen05.mma for 16-bit operands
+constexpr int kMaxSegs = 3;
+constexpr int kGemmThreads = 320;      // TMA warp, MMA warp, eight epilogue warps
+constexpr long long kWaitCycles = 4000000000LL;  // about two seconds; a healthy wait is microseconds
+
+enum GemmStatus : int { kOk = 0, kTimeoutProducer = 101, kTimeoutMma = 102, kTimeoutEpilogue = 103 };
+
+struct GemmParams {
+  // operands: arrays of 3-D tensor maps (inner, outer, z) in global memory
+  const CUtensorMap* a_maps;
+  const CUtensorMap* b_maps;
+  int a_map_stride, b_map_stride;  // map index   = batch * map_stride
+  int a_z_stride, b_z_stride;      // z coordinate = batch * z_stride + seg_z[seg]
+  int a_mn, b_mn;                  // 1: stored MN-major (outer index is k), 0: K-major (outer index is m / n)
+  int a_seg_z[kMaxSegs], b_seg_z[kMaxSegs];
+  int segs;
+  int M, N, K, batch;
+  int fmt;  // operand format: 0 FP16, 1 BF16
+  int tri;  // 1: M == N, only tiles meeting the upper triangle are computed
+  int promote;  // > 0: k-blocks per tensor-core accumulation chain; chains are summed in FP32 registers
+  // epilogue: d = alpha * acc + beta * C ; alpha, beta optionally scaled per batch from device arrays
+  float alpha, beta;
+  const float* alpha_a;
+  const float* alpha_b;
+  const float* beta_v;
+  int alpha_b_step;
+  const float* C;
+  long long ldc, c_bs;
+  float* D;
+  long long ldd, d_bs;
+  void* D16;
+  long long ld16, d16_bs;
+  int d16_fmt;  // 0 FP16, 1 BF16
+  int packed;   // C and D are packed upper triangles (row r starts at r*N - r(r-1)/2 - r ... see packed_off)
+  int mirror;   // tri: also store the transposed element
+  int vec_ok;   // leading dimensions and batch strides allow 16-byte vector access
+  float* sumsq;           // per batch: sum of d^2 over the full (mirrored) result
+  unsigned int* maxabs;   // per batch: max |d| as FP32 bits
+  unsigned int* maxaff;   // per batch: max |aff_a * [r==c] + aff_b * d| as FP32 bits
+  float aff_a, aff_b;
+  int* status;  // set non-zero if a bounded wait ran out
+};
+
+__host__ __device__ inline long long packed_off(long long r, long long c, long long n) {
+  return r * n - r * (r + 1) / 2 + c;
+}
+
+__host__ __device__ inline int gemm_tiles_per_batch(int M, int N, int BN, int tri) {
+  const int tm = (M + kBM - 1) / kBM, tn = (N + BN - 1) / BN;
+  if (!tri) return tm * tn;
+  int total = 0;
+  for (int i = 0; i < tm; ++i) {
+    const int first = (i * kBM) / BN;
+    if (first < tn) total += tn - first;
+  }
+  return total;
+}
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kTileBytes = kStages * kStageBytes;
+  static constexpr int kBarBytes = 256;
+  static constexpr int kTotal = kTileBytes + kBarBytes + 1024;  // 1024: alignment slack
+  static constexpr int kTmemCols = 2 * BN;
+};
+
+__device__ __forceinline__ void tile_coord(const GemmParams& p, int BN, int t, int tiles_per_batch, int tiles_n,
+                                           int& b, int& tm, int& tn) {
+  b = t / tiles_per_batch;
+  int r = t - b * tiles_per_batch;
+  if (!p.tri) {
+    tm = r / tiles_n;
+    tn = r - tm * tiles_n;
+    return;
+  }
+  tm = 0;
+  for (;;) {
+    const int first = (tm * kBM) / BN;
+    const int cnt = tiles_n - first;
+    if (r < cnt) {
+      tn = first + r;
+      return;
+    }
+    r -= cnt;
+    ++tm;
+  }
+}
+
+__device__ __forceinline__ void report(int* status, int code) {
+  if (status) atomicCAS(status, 0, code);
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
+  using S = GemmSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* const smem = smem_raw + (base - raw);
+  // barrier block after the tiles
+  const uint32_t bars = base + S::kTileBytes;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (S::kStages + s); };
+  auto tfull_bar = [&](int s) { return bars + 8u * (2 * S::kStages + s); };
+  auto tempty_bar = [&](int s) { return bars + 8u * (2 * S::kStages + 2 + s); };
+  volatile uint32_t* const tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + S::kTileBytes + 8 * (2 * S::kStages + 4));
+  volatile int* const abort_flag = reinterpret_cast<volatile int*>(smem + S::kTileBytes + 8 * (2 * S::kStages + 4) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int tiles_per_batch = gemm_tiles_per_batch(p.M, p.N, BN, p.tri);
+  const int total_tiles = tiles_per_batch * p.batch;
+  const int kb_per_seg = (p.K + kBK - 1) / kBK;
+  const int num_kb = kb_per_seg * p.segs;
+  // Accumulation chains: with promote > 0 the MMA warp starts a fresh TMEM accumulator every `promote`
+  // k-blocks (never across a segment boundary) and the epilogue warps sum the chains in registers.
+  const int chunks_per_seg = p.promote > 0 ? (kb_per_seg + p.promote - 1) / p.promote : 1;
+  const int chunks_per_tile = p.promote > 0 ? chunks_per_seg * p.segs : 1;
+  auto chunk_range = [&](int ch, int& kb_begin, int& kb_end) {
+    if (p.promote <= 0) {
+      kb_begin = 0;
+      kb_end = num_kb;
+      return;
+    }
+    const int seg = ch / chunks_per_seg, c = ch - seg * chunks_per_seg;
+    kb_begin = seg * kb_per_seg + c * p.promote;
+    kb_end = min(kb_begin + p.promote, (seg + 1) * kb_per_seg);
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(tfull_bar(s), 1);
+      ptx::mbar_init(tempty_bar(s), 8);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), S::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int b, tm, tn;
+        tile_coord(p, BN, t, tiles_per_batch, tiles_n, b, tm, tn);
+        const CUtensorMap* amap = p.a_maps + (long long)b * p.a_map_stride;
+        const CUtensorMap* bmap = p.b_maps + (long long)b * p.b_map_stride;
+        ptx::fence_tensormap_acquire(amap);
+        ptx::fence_tensormap_acquire(bmap);
+        const int m0 = tm * kBM, n0 = tn * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, kWaitCycles) || *abort_flag) {
+            report(p.status, kTimeoutProducer);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const int seg = kb / kb_per_seg;
+          const int k0 = (kb - seg * kb_per_seg) * kBK;
+          const uint32_t sa = base + stage * S::kStageBytes;
+          const uint32_t sb = sa + S::kABytes;
+          const int za = b * p.a_z_stride + p.a_seg_z[seg];
+          const int zb = b * p.b_z_stride + p.b_seg_z[seg];
+          ptx::mbar_expect_tx(full_bar(stage), S::kStageBytes);
+          if (p.a_mn) {
+#pragma unroll
+            for (int s = 0; s < kBM / 64; ++s) ptx::tma_load_3d(sa + s * 8192, amap, full_bar(stage), m0 + s * 64, k0, za);
+          } else {
+            ptx::tma_load_3d(sa, amap, full_bar(stage), k0, m0, za);
+          }
+          if (p.b_mn) {
+#pragma unroll
+            for (int s = 0; s < BN / 64; ++s) ptx::tma_load_3d(sb + s * 8192, bmap, full_bar(stage), n0 + s * 64, k0, zb);
+          } else {
+            ptx::tma_load_3d(sb, bmap, full_bar(stage), k0, n0, zb);
+          }
+          if (++stage == S::kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // give copies already in flight time to land before the CTA gives its shared memory back
+        for (int s = 0; s < S::kStages; ++s) ptx::mbar_wait(full_bar(s), 0, 2000000LL);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | ((uint32_t)p.fmt << 7) | ((uint32_t)p.fmt << 10) | ((uint32_t)p.a_mn << 15) |
+                             ((uint32_t)p.b_mn << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+      // K-major: 8-row groups 1024 B apart, k advances 32 B inside the swizzled row.
+      // MN-major: 64-element slabs 8192 B apart (LBO), 8-k-row groups 1024 B apart (SBO), k advances 16 rows = 2048 B.
+      const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
+      const uint32_t a_step = p.a_mn ? 2048u : 32u, b_step = p.b_mn ? 2048u : 32u;
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t gchunk = 0;  // accumulator hand-offs so far; buffer = gchunk & 1
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int ch = 0; ch < chunks_per_tile && ok; ++ch, ++gchunk) {
+          int kb_begin, kb_end;
+          chunk_range(ch, kb_begin, kb_end);
+          const int buf = gchunk & 1u;
+          if (!ptx::mbar_wait(tempty_bar(buf), ((gchunk >> 1) & 1u) ^ 1u, kWaitCycles) || *abort_flag) {
+            report(p.status, kTimeoutMma);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+          for (int kb = kb_begin; kb < kb_end; ++kb) {
+            if (!ptx::mbar_wait(full_bar(stage), phase, kWaitCycles) || *abort_flag) {
+              report(p.status, kTimeoutMma);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            const uint32_t sa = base + stage * S::kStageBytes;
+            const uint32_t sb = sa + S::kABytes;
+#pragma unroll
+            for (int k = 0; k < kBK / kUmmaK; ++k) {
+              const uint64_t da = ptx::smem_desc(sa + k * a_step, a_lbo, 1024u);
+              const uint64_t db = ptx::smem_desc(sb + k * b_step, b_lbo, 1024u);
+              ptx::mma_f16(d_tmem, da, db, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
+            }
+            ptx::mma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+            if (++stage == S::kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          if (ok) ptx::mma_commit(tfull_bar(buf));  // this chain's partial sum is complete
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    // Warp w may read TMEM lanes [32*(w&3), +32); two warps share a lane group and split the columns.
+    constexpr int NCH = BN / 64;  // 32-column chunks per warp
+    const int lane_group = warp & 3;
+    const int half = (warp - 2) >> 2;
+    float racc[NCH * 32];  // running sums, added with round-to-nearest (the tensor core truncates)
+    uint32_t gchunk = 0;
+    bool alive = true;
+    for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
+      int b, tm, tn;
+      tile_coord(p, BN, t, tiles_per_batch, tiles_n, b, tm, tn);
+      const int m0 = tm * kBM, n0 = tn * BN;
+      const int row_first = m0 + lane_group * 32;
+      const int r = row_first + lane;
+      const bool row_ok = r < p.M;
+      // chunks of columns this warp never needs: beyond N, or wholly below the diagonal (warp-uniform)
+      bool need[NCH];
+#pragma unroll
+      for (int cc = 0; cc < NCH; ++cc) {
+        const int c0 = n0 + half * (BN / 2) + cc * 32;
+        need[cc] = (c0 < p.N) && !(p.tri && c0 + 31 < row_first);
+      }
+      for (int ch = 0; ch < chunks_per_tile; ++ch, ++gchunk) {
+        const int buf = gchunk & 1u;
+        // every lane observes the barrier itself, so each one is ordered after the MMAs' TMEM writes
+        const int waited = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), (gchunk >> 1) & 1u, kWaitCycles) ? 1 : 0);
+        if (!waited || *abort_flag) {
+          if (lane == 0) {
+            report(p.status, kTimeoutEpilogue);
+            *abort_flag = 1;
+          }
+          alive = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN + half * (BN / 2));
+#pragma unroll
+        for (int cc = 0; cc < NCH; ++cc) {
+          if (!need[cc]) continue;
+          uint32_t acc[32];
+          ptx::tmem_ld32(taddr + (uint32_t)(cc * 32), acc);
+          ptx::tmem_ld_wait();
+          if (ch == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) racc[cc * 32 + j] = __uint_as_float(acc[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) racc[cc * 32 + j] += __uint_as_float(acc[j]);
+          }
+        }
+        // buffer drained: hand it back to the MMA warp
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+      }
+      if (!alive) break;
+
+      float alpha = p.alpha, beta = p.beta;
+      if (p.alpha_a) alpha *= __ldg(p.alpha_a + b);
+      if (p.alpha_b) alpha *= __ldg(p.alpha_b + (long long)b * p.alpha_b_step);
+      if (p.beta_v) beta *= __ldg(p.beta_v + b);
+      const bool use_c = (p.C != nullptr) && (beta != 0.f);
+      const float* Cb = p.C ? p.C + (long long)b * p.c_bs : nullptr;
+      float* Db = p.D ? p.D + (long long)b * p.d_bs : nullptr;
+      __half* Hb = (p.D16 && p.d16_fmt == 0) ? reinterpret_cast<__half*>(p.D16) + (long long)b * p.d16_bs : nullptr;
+      __nv_bfloat16* Bb = (p.D16 && p.d16_fmt == 1) ? reinterpret_cast<__nv_bfloat16*>(p.D16) + (long long)b * p.d16_bs : nullptr;
+      const long long crow = p.packed ? packed_off(r, 0, p.N) : (long long)r * p.ldc;
+      const long long drow = p.packed ? packed_off(r, 0, p.N) : (long long)r * p.ldd;
+      const long long hrow = (long long)r * p.ld16;
+      float ssq = 0.f, mabs = 0.f, maff = 0.f;
+
+#pragma unroll
+      for (int cc = 0; cc < NCH; ++cc) {
+        if (!need[cc]) continue;
+        const int c0 = n0 + half * (BN / 2) + cc * 32;
+#pragma unroll
+        for (int j4 = 0; j4 < 8; ++j4) {
+          const int c = c0 + j4 * 4;
+          float v[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[e] = alpha * racc[cc * 32 + j4 * 4 + e];
+          const bool full4 = row_ok && (c + 3 < p.N) && (!p.tri || c >= r);
+          if (full4 && p.vec_ok) {
+            if (use_c) {
+              const float4 cv = *reinterpret_cast<const float4*>(Cb + crow + c);
+              v[0] += beta * cv.x; v[1] += beta * cv.y; v[2] += beta * cv.z; v[3] += beta * cv.w;
+            }
+            if (Db) *reinterpret_cast<float4*>(Db + drow + c) = make_float4(v[0], v[1], v[2], v[3]);
+            if (Hb) {
+              __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+              uint2 u;
+              u.x = *reinterpret_cast<uint32_t*>(&h0);
+              u.y = *reinterpret_cast<uint32_t*>(&h1);
+              *reinterpret_cast<uint2*>(Hb + hrow + c) = u;
+            }
+            if (Bb) {
+              __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
+              uint2 u;
+              u.x = *reinterpret_cast<uint32_t*>(&h0);
+              u.y = *reinterpret_cast<uint32_t*>(&h1);
+              *reinterpret_cast<uint2*>(Bb + hrow + c) = u;
+            }
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int ce = c + e;
+              const bool ok = row_ok && ce < p.N && (!p.tri || ce >= r);
+              if (ok) {
+                if (use_c) v[e] += beta * Cb[crow + ce];
+                if (Db) Db[drow + ce] = v[e];
+                if (Hb) Hb[hrow + ce] = __float2half_rn(v[e]);
+                if (Bb) Bb[hrow + ce] = __float2bfloat16_rn(v[e]);
+              } else {
+                v[e] = 0.f;  // masked: contributes nothing to the statistics or the mirror
+              }
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int ce = c + e;
+            const bool ok = row_ok && ce < p.N && (!p.tri || ce >= r);
+            if (!ok) continue;
+            const bool off = p.tri && ce > r;
+            if (off && p.mirror) {  // consecutive lanes hold consecutive rows: these stores coalesce
+              if (Db) Db[(long long)ce * p.ldd + r] = v[e];
+              if (Hb) Hb[(long long)ce * p.ld16 + r] = __float2half_rn(v[e]);
+              if (Bb) Bb[(long long)ce * p.ld16 + r] = __float2bfloat16_rn(v[e]);
+            }
+            ssq += (off ? 2.f : 1.f) * v[e] * v[e];
+            mabs = fmaxf(mabs, fabsf(v[e]));
+            maff = fmaxf(maff, fabsf((ce == r ? p.aff_a : 0.f) + p.aff_b * v[e]));
+          }
+        }
+      }
+
+      if (p.sumsq || p.maxabs || p.maxaff) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+          mabs = fmaxf(mabs, __shfl_xor_sync(0xffffffffu, mabs, o));
+          maff = fmaxf(maff, __shfl_xor_sync(0xffffffffu, maff, o));
+        }
+        if (lane == 0) {
+          if (p.sumsq) atomicAdd(p.sumsq + b, ssq);  // order of these additions is not fixed
+          if (p.maxabs) atomicMax(p.maxabs + b, __float_as_uint(mabs));
+          if (p.maxaff) atomicMax(p.maxaff + b, __float_as_uint(maff));
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, S::kTmemCols);
+  }
+}
+
+}  // namespace toner

@@ -1,0 +1,67 @@
+// Host runtime shared by the C-ABI entry points: per-device context, tensor-map cache, GEMM launcher.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/toner_b200.h"
+#include "gemm_tcgen05.cuh"
+
+namespace toner {
+
+// Return codes of the C-ABI (0 = ok, > 0 = host-side argument / runtime error).
+enum : int {
+  kErrArg = 1,         // null / misaligned pointer, bad size
+  kErrCuda = 2,        // a CUDA runtime call failed (see toner_last_error)
+  kErrDriver = 3,      // cuTensorMapEncodeTiled unavailable or failed
+  kErrWorkspace = 4,   // caller-provided workspace too small
+  kErrUnsupported = 5  // shape or option outside what the kernels cover
+};
+
+void set_error(const std::string& msg);
+int fail(int code, const std::string& msg);
+
+#define TONER_CUDA(expr)                                                                         \
+  do {                                                                                           \
+    cudaError_t err__ = (expr);                                                                  \
+    if (err__ != cudaSuccess)                                                                    \
+      return ::toner::fail(::toner::kErrCuda, std::string(#expr) + ": " + cudaGetErrorString(err__)); \
+  } while (0)
+
+struct Context {
+  int device = -1;
+  int num_sms = 0;
+  CUtensorMap* arena_dev = nullptr;   // tensor maps live here; slots are never rewritten between resets
+  CUtensorMap* arena_host = nullptr;  // pinned mirror used as the copy source
+  int arena_cap = 0, arena_used = 0;
+  int* status_dev = nullptr;          // set by a kernel whose bounded wait ran out
+  void* map_cache = nullptr;          // std::unordered_map<std::string, int>*
+};
+
+// Context of the current device (created on first use).  Returns nullptr and sets the error on failure.
+Context* context();
+
+// Device pointer to `count` consecutive tensor maps describing `op` (one per batch when op.list is
+// given, else one).  box_rows is the outer box extent for K-major operands (tile rows); MN-major
+// operands always use 64 x 64 boxes.
+int get_maps(Context* ctx, const toner_operand& op, int batch, int box_rows, cudaStream_t stream, const CUtensorMap** out);
+
+int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream);
+
+// FP16 hi/lo split of an FP32 stack (see toner_split16).
+int split16(const float* x, const float* const* x_list, int batch, int rows, int cols, long long ld, long long bs,
+            float aff_a, float aff_b, const uint32_t* maxabs, void* scratch, void* planes, float* inv_scale,
+            cudaStream_t stream);
+
+// out[b] = sum of squares of matrix b, bitwise reproducible.  scratch: sumsq_scratch_bytes(batch).
+size_t sumsq_scratch_bytes(int batch);
+int sumsq_det(const float* x, int batch, int rows, int cols, long long ld, long long bs, float* scratch, float* out,
+              cudaStream_t stream);
+
+// k-blocks per accumulation chain used for FP32-accurate (split-precision) products
+constexpr int kPromoteAccurate = 2;
+
+}  // namespace toner

@@ -1,0 +1,249 @@
+// Statistic path: upper-triangle SYRK (on the tcgen05 GEMM), packed-triangle EMA, FP16 hi/lo splitting.
+#include <cuda_fp16.h>
+
+#include "runtime.cuh"
+
+namespace toner {
+
+// ------------------------------------------------------------------ packed triangle -> full EMA
+// One 32x32 tile pair per block: the upper tile is updated in place from the packed triangle, the lower
+// tile is its transpose written through shared memory, so every global access is row-contiguous.
+__global__ void __launch_bounds__(256) unpack_ema_kernel(const float* __restrict__ packed, float* __restrict__ ema, int n,
+                                                         float beta, float gamma) {
+  const int ti = blockIdx.y, tj = blockIdx.x;
+  if (ti > tj) return;
+  __shared__ float tile[32][33];
+  const long long b = blockIdx.z;
+  const float* P = packed + b * ((long long)n * (n + 1) / 2);
+  float* C = ema + b * (long long)n * n;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int lr = ty + 8 * i;
+    const int r = ti * 32 + lr, c = tj * 32 + tx;
+    float v = 0.f;
+    if (r < n && c < n && r <= c) {
+      const float s = P[packed_off(r, c, n)];
+      v = fmaf(beta, C[(long long)r * n + c], gamma * s);
+      C[(long long)r * n + c] = v;
+    }
+    tile[lr][tx] = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int lr = ty + 8 * i;
+    const int r = tj * 32 + lr, c = ti * 32 + tx;  // element of the lower triangle, value from (c, r)
+    if (r < n && c < n && r > c) C[(long long)r * n + c] = tile[tx][lr];
+  }
+}
+
+// ------------------------------------------------------------------ max |aff_a*I + aff_b*x| per matrix
+__global__ void __launch_bounds__(256) maxabs_kernel(const float* __restrict__ x, const float* const* __restrict__ x_list,
+                                                     int rows, int cols, long long ld, long long bs, float aff_a,
+                                                     float aff_b, unsigned int* __restrict__ out) {
+  const int b = blockIdx.y;
+  const float* X = x_list ? x_list[b] : x + (long long)b * bs;
+  const long long total = (long long)rows * cols;
+  float m = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
+    const float v = aff_b * X[(long long)r * ld + c] + (r == c ? aff_a : 0.f);
+    m = fmaxf(m, fabsf(v));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) atomicMax(out + b, __float_as_uint(m));
+}
+
+// scale = 2^(13 - floor(log2 maxabs)); 1 when the matrix is all zero or its maximum is not finite
+__device__ __forceinline__ float split_scale(unsigned int maxabs_bits) {
+  const float a = __uint_as_float(maxabs_bits);
+  if (!(a > 0.f) || !isfinite(a)) return 1.f;
+  int e;
+  frexpf(a, &e);  // a = f * 2^e, f in [0.5, 1)  =>  floor(log2 a) = e - 1
+  return ldexpf(1.f, 13 - (e - 1));
+}
+
+__global__ void __launch_bounds__(256) split16_kernel(const float* __restrict__ x, const float* const* __restrict__ x_list,
+                                                      int batch, int rows, int cols, long long ld, long long bs,
+                                                      float aff_a, float aff_b, const unsigned int* __restrict__ maxabs,
+                                                      __half* __restrict__ planes, float* __restrict__ inv_scale) {
+  const int b = blockIdx.y;
+  const float* X = x_list ? x_list[b] : x + (long long)b * bs;
+  const float s = split_scale(maxabs[b]);
+  if (blockIdx.x == 0 && threadIdx.x == 0 && inv_scale) inv_scale[b] = 1.f / s;
+  const long long per = (long long)rows * cols;
+  __half* hi = planes + (long long)b * per;
+  __half* lo = planes + ((long long)batch + b) * per;
+  const bool vec = (cols % 4 == 0) && (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(X) & 15u) == 0);
+  if (vec) {
+    const long long total4 = per / 4;
+    const int c4 = cols / 4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+      const int r = (int)(i / c4), c = (int)(i - (long long)r * c4) * 4;
+      const float4 q = *reinterpret_cast<const float4*>(X + (long long)r * ld + c);
+      float v[4] = {q.x, q.y, q.z, q.w};
+      __half h[4], l[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float w = (aff_b * v[e] + ((c + e) == r ? aff_a : 0.f)) * s;
+        h[e] = __float2half_rn(w);
+        l[e] = __float2half_rn(w - __half2float(h[e]));
+      }
+      *reinterpret_cast<uint2*>(hi + (long long)r * cols + c) = *reinterpret_cast<uint2*>(h);
+      *reinterpret_cast<uint2*>(lo + (long long)r * cols + c) = *reinterpret_cast<uint2*>(l);
+    }
+  } else {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x) {
+      const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
+      const float w = (aff_b * X[(long long)r * ld + c] + (c == r ? aff_a : 0.f)) * s;
+      const __half h = __float2half_rn(w);
+      hi[i] = h;
+      lo[i] = __float2half_rn(w - __half2float(h));
+    }
+  }
+}
+
+// ------------------------------------------------------------------ deterministic sum of squares
+// Fixed grid, fixed reduction tree: the same input always gives the same bits (float atomics would not).
+constexpr int kSumsqBlocks = 64;
+
+__global__ void __launch_bounds__(256) sumsq_partial_kernel(const float* __restrict__ x, int rows, int cols, long long ld,
+                                                            long long bs, float* __restrict__ partial) {
+  const int b = blockIdx.y;
+  const float* X = x + (long long)b * bs;
+  const long long total = (long long)rows * cols;
+  const long long per = (total + gridDim.x - 1) / gridDim.x;
+  const long long lo = per * blockIdx.x, hi = (lo + per < total) ? lo + per : total;
+  float s = 0.f;
+  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const long long r = i / cols, c = i - r * cols;
+    const float v = X[r * ld + c];
+    s = fmaf(v, v, s);
+  }
+  __shared__ float red[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < 8; ++w) t += red[w];
+    partial[(long long)b * gridDim.x + blockIdx.x] = t;
+  }
+}
+
+__global__ void sumsq_final_kernel(const float* __restrict__ partial, int blocks, int batch, float* __restrict__ out) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  float t = 0.f;
+  for (int i = 0; i < blocks; ++i) t += partial[(long long)b * blocks + i];
+  out[b] = t;
+}
+
+size_t sumsq_scratch_bytes(int batch) { return (size_t)batch * kSumsqBlocks * sizeof(float); }
+
+int sumsq_det(const float* x, int batch, int rows, int cols, long long ld, long long bs, float* scratch, float* out,
+              cudaStream_t stream) {
+  sumsq_partial_kernel<<<dim3(kSumsqBlocks, batch), 256, 0, stream>>>(x, rows, cols, ld, bs, scratch);
+  sumsq_final_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(scratch, kSumsqBlocks, batch, out);
+  TONER_CUDA(cudaGetLastError());
+  return 0;
+}
+
+static int blocks_for(long long work, int per_block, int cap) {
+  long long b = (work + per_block - 1) / per_block;
+  if (b < 1) b = 1;
+  if (b > cap) b = cap;
+  return (int)b;
+}
+
+int split16(const float* x, const float* const* x_list, int batch, int rows, int cols, long long ld, long long bs,
+            float aff_a, float aff_b, const uint32_t* maxabs, void* scratch, void* planes, float* inv_scale,
+            cudaStream_t stream) {
+  Context* ctx = context();
+  if (!ctx) return kErrCuda;
+  if ((!x && !x_list) || !planes || batch <= 0 || rows <= 0 || cols <= 0) return fail(kErrArg, "split16: bad arguments");
+  if (cols % 8 != 0) return fail(kErrArg, "split16: cols must be a multiple of 8 (TMA row pitch)");
+  const long long per = (long long)rows * cols;
+  const int bx = blocks_for(per / 4 + 1, 256 * 4, 8 * ctx->num_sms / (batch < 8 ? batch : 8) + 1);
+  if (!maxabs) {
+    if (!scratch) return fail(kErrArg, "split16: maxabs or scratch is required");
+    unsigned int* m = static_cast<unsigned int*>(scratch);
+    TONER_CUDA(cudaMemsetAsync(m, 0, sizeof(unsigned int) * batch, stream));
+    maxabs_kernel<<<dim3(bx, batch), 256, 0, stream>>>(x, x_list, rows, cols, ld, bs, aff_a, aff_b, m);
+    TONER_CUDA(cudaGetLastError());
+    maxabs = m;
+  }
+  split16_kernel<<<dim3(bx, batch), 256, 0, stream>>>(x, x_list, batch, rows, cols, ld, bs, aff_a, aff_b, maxabs,
+                                                     static_cast<__half*>(planes), inv_scale);
+  TONER_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace toner
+
+extern "C" {
+
+int toner_syrk_upper(const void* const* x_list, const void* x_base, int64_t x_batch_stride, int32_t k, int32_t rows,
+                     int32_t n, int64_t ld, float* out, int32_t mode, float beta, float gamma, void* stream) {
+  using namespace toner;
+  if ((!x_list && !x_base) || !out) return fail(kErrArg, "syrk: null pointer");
+  if (k <= 0 || rows <= 0 || n <= 0) return fail(kErrArg, "syrk: sizes must be positive");
+  if (n % 8 != 0 || ld % 8 != 0) return fail(kErrArg, "syrk: n and ld must be multiples of 8");
+  if (mode < 0 || mode > 2) return fail(kErrArg, "syrk: mode must be 0 (PACKED), 1 (PACKED_ACC) or 2 (EMA_FULL)");
+  toner_gemm_desc d = {};
+  toner_operand op = {};
+  op.base = x_base;
+  op.list = x_list;
+  op.rows = rows;
+  op.cols = n;
+  op.ld = ld;
+  op.z_stride = x_batch_stride;
+  op.nz = x_list ? 1 : k;
+  op.z_step = 1;
+  op.mn_major = 1;  // the buffer is (rows = k-index) x (n = m/n-index): X^T X reads it transposed on both sides
+  d.a = op;
+  d.b = op;
+  d.m = n; d.n = n; d.k = rows; d.batch = k;
+  d.segs = 1;
+  d.fmt = 1;
+  d.tri = 1;
+  const long long tri_elems = (long long)n * (n + 1) / 2;
+  if (mode == 2) {
+    d.mirror = 1;
+    d.alpha = gamma; d.beta = beta;
+    d.c = out; d.ldc = n; d.c_bs = (long long)n * n;
+    d.d = out; d.ldd = n; d.d_bs = (long long)n * n;
+  } else {
+    d.packed = 1;
+    d.alpha = 1.f;
+    d.d = out; d.ldd = n; d.d_bs = tri_elems;
+    if (mode == 1) {
+      d.beta = 1.f;
+      d.c = out; d.ldc = n; d.c_bs = tri_elems;
+    }
+  }
+  return launch_gemm(d, static_cast<cudaStream_t>(stream));
+}
+
+int toner_unpack_ema(const float* packed, float* ema, int32_t k, int32_t n, float beta, float gamma, void* stream) {
+  using namespace toner;
+  if (!context()) return kErrCuda;
+  if (!packed || !ema || k <= 0 || n <= 0) return fail(kErrArg, "unpack_ema: bad arguments");
+  const int t = (n + 31) / 32;
+  if (k > 65535) return fail(kErrArg, "unpack_ema: k too large");
+  unpack_ema_kernel<<<dim3(t, t, k), 256, 0, static_cast<cudaStream_t>(stream)>>>(packed, ema, n, beta, gamma);
+  TONER_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int toner_split16(const float* x, const float* const* x_list, int32_t batch, int32_t rows, int32_t cols, int64_t ld,
+                  int64_t bs, float aff_a, float aff_b, const uint32_t* maxabs, void* scratch, void* planes,
+                  float* inv_scale, void* stream) {
+  return toner::split16(x, x_list, batch, rows, cols, ld, bs, aff_a, aff_b, maxabs, scratch, planes, inv_scale,
+                        static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
