@@ -31,6 +31,7 @@ extern "C" {
 int toner_init(int device);               /* create the context of `device` (optional: created on first use) */
 const char* toner_last_error(void);       /* text of the last host-side failure on this thread */
 int toner_sm_count(void);                 /* SM count of the current device (0 on failure) */
+long long toner_launch_count(void);       /* kernels launched by this library so far (for launch accounting) */
 /* Synchronise `stream`, then read and clear the device status word that kernels set when one of their
  * bounded waits runs out (0 = healthy). */
 int toner_device_status(void* stream, int* status_out);
@@ -119,7 +120,7 @@ int toner_split16(const float* x, const float* const* x_list, int32_t batch, int
  * Method: coupled Newton iteration T = a I - b M, X <- X T, M <- T^p M with minimax-scaled (a, b), batched
  * over the k statistics, all products FP32-accurate on tensor cores (FP16 hi/lo planes, three plane products
  * per accumulator).  `iters` <= 0 selects toner_inv_roots_iterations(n, damping, p), which depends only on
- * its arguments (e.g. 9 for p = 8, 10 for p = 4, 12 for p = 2 at n = 5632, damping 1e-3).
+ * its arguments (10 for p = 8, 11 for p = 4, 12 for p = 2 at n = 5632, damping 1e-3).
  * status[b] (DEVICE, optional): 0 converged, 1 residual max|I - M| above 0.05 before the last step,
  * 2 non-finite.  The caller decides what to do with a non-zero status (the Python host recomputes that
  * statistic with an eigendecomposition, as the reference's fallback does, src/toner/fast/engine.py:714-731).

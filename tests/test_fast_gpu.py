@@ -1,0 +1,152 @@
+"""FastMuonT / FastAdamT through their public lifecycle (capture_microbatch -> begin -> step) against the
+CPU oracle's general path fed with the same sampled rows and gradients."""
+
+import pytest
+import torch
+
+from oracle import toner_oracle as orc
+
+pytestmark = pytest.mark.gpu
+HID, MLP, SEQ, MB, ACC, LAYERS = 256, 512, 64, 2, 2, 2
+
+
+@pytest.fixture()
+def fast():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    import toner_b200.fast as f
+    return f
+
+
+def make(fast, layout, kind, **kw):
+    from toner_b200.synthetic import make_stack
+    stack = make_stack(layout, LAYERS, HID, MLP, torch.device("cuda"), seed=0)
+    wrap = fast.ProjectionBlock if layout == "llama" else fast.NanoGPTBlock
+    cls = fast.FastMuonT if kind == "muont" else fast.FastAdamT
+    opt = cls([wrap.from_module(b) for b in stack], 0.02 if kind == "muont" else 2e-3, weight_decay=0.1,
+              micro_batch_size=MB, sequence_length=SEQ, accumulation_steps=ACC, statistic_head=8, statistic_stride=4, **kw)
+    return stack, opt
+
+
+def forward(stack, x):
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        for b in stack:
+            x = b(x)
+    return x
+
+
+def role_modules(block, layout):
+    if layout == "llama":
+        return {"attn": [block.q, block.k, block.v], "o": [block.o], "mlp": [block.gate, block.up], "down": [block.down]}
+    return {"attn": [block.attn.q, block.attn.k, block.attn.v], "o": [block.attn.proj], "mlp": [block.mlp.fc],
+            "down": [block.mlp.proj]}
+
+
+@pytest.mark.parametrize("layout,kind", [("llama", "muont"), ("nanogpt", "muont"), ("llama", "adamt")])
+def test_two_steps_match_oracle(fast, layout, kind):
+    extra = dict(ns_steps=2) if kind == "muont" else dict(betas=(0.9, 0.95))
+    stack, opt = make(fast, layout, kind, **extra)
+    try:
+        positions = orc.sample_positions(SEQ, 8, 4)
+        params = [(li, k, m) for li, b in enumerate(stack) for k, ms in role_modules(b, layout).items() for m in ms]
+        ref_w = {id(m): m.weight.detach().cpu().clone() for _, _, m in params}
+        states = {id(m): (orc.MuonTState() if kind == "muont" else orc.AdamTState()) for _, _, m in params}
+        gen = torch.Generator().manual_seed(5)
+        for step in range(2):
+            captured = {}
+            hooks = []
+            for li, k, m in params:  # record what each projection really read (after autocast rounding)
+                def rec(mod, inp, key=(li, k)):
+                    captured.setdefault(key, []).append(inp[0].detach().to(torch.bfloat16).cpu())
+                hooks.append(m.register_forward_pre_hook(rec))
+            for mb in range(ACC):
+                x = torch.randn(MB, SEQ, HID, generator=gen).cuda()
+                with opt.capture_microbatch():
+                    forward(stack, x)
+            for h in hooks:
+                h.remove()
+            opt.begin()
+            for _, _, m in params:
+                m.weight.grad = (torch.randn(m.weight.shape, generator=gen) * 1e-3).cuda()
+            opt.step()
+            worst = 0.0
+            for li, k, m in params:
+                rows = torch.cat([t[:, positions].reshape(-1, t.shape[-1]) for t in captured[(li, k)][::len(role_modules(stack[li], layout)[k])]])
+                st = states[id(m)]
+                st.ema, st.weight = orc.ema_update(st.ema, st.weight, orc.gram(rows) / rows.shape[0], 0.95)
+                g = m.weight.grad.cpu()
+                before = ref_w[id(m)]
+                if kind == "muont":
+                    after = orc.muont_step(before, g, st, lr=0.02, weight_decay=0.1, momentum=0.95, ns_steps=2, ns_mode="tpu")
+                else:
+                    after = orc.adamt_step(before, g, st, lr=2e-3, weight_decay=0.1, betas=(0.9, 0.95), eps=1e-15)
+                ref_w[id(m)] = after
+                worst = max(worst, orc.rel_fro(m.weight.detach().cpu(), after))
+            # AdamT's first updates are close to sign(g R): entries of g R near zero flip under any factor
+            # difference, and each flip moves a weight by 2 lr.  With lr/|w| ~ 0.1 here that is ~1e-2 on the weights.
+            assert worst < (2e-3 if kind == "muont" else 3e-2), (layout, kind, step, worst)
+            if kind == "adamt":  # the moments themselves are smooth functions of the factors
+                for li, k, m in params[:3]:
+                    role = [r for r, info in opt._core.roles.items() if any(w is m.weight for w in info["all"])][0]
+                    info = opt._core.roles[role]
+                    j = [i for i, w in enumerate(info["all"]) if w is m.weight][0]
+                    assert orc.rel_fro(info["group"].m[j].cpu(), states[id(m)].exp_avg) < 1e-5
+                    assert orc.rel_fro(info["group"].v[j].cpu(), states[id(m)].exp_avg_sq) < 5e-3
+        d = opt.diagnostics
+        assert d["fallbacks"] == 0 and set(d["gpu_ms"]) <= {"stats", "roots", "update"}
+        from toner_b200 import ops
+        ops.assert_healthy()
+    finally:
+        opt.close()
+
+
+def test_lifecycle_errors_and_checkpoint_round_trip(fast):
+    stack, opt = make(fast, "llama", "muont", ns_steps=2)
+    try:
+        with pytest.raises(RuntimeError):
+            fast.FastMuonT([fast.ProjectionBlock.from_module(stack[0])], 0.02, micro_batch_size=MB, sequence_length=SEQ)
+        with pytest.raises(RuntimeError):
+            opt.begin()                                   # nothing captured yet
+        with pytest.raises(RuntimeError):
+            opt.state_dict()                              # no completed step
+        with pytest.raises(ValueError):
+            with opt.capture_microbatch():
+                forward(stack, torch.randn(MB, SEQ + 1, HID).cuda())   # wrong shape
+        with pytest.raises(RuntimeError):
+            with opt.capture_microbatch():
+                stack[0](torch.randn(MB, SEQ, HID, device="cuda", dtype=torch.bfloat16))   # not every projection ran
+        gen = torch.Generator().manual_seed(1)
+        for _ in range(ACC):
+            with opt.capture_microbatch():
+                forward(stack, torch.randn(MB, SEQ, HID, generator=gen).cuda())
+        with pytest.raises(RuntimeError):
+            with opt.capture_microbatch():
+                pass                                      # one microbatch too many
+        with pytest.raises(RuntimeError):
+            opt.step()                                    # gradients missing
+        for p in opt.param_groups[0]["params"]:
+            p.grad = torch.randn_like(p) * 1e-3
+        with pytest.raises(ValueError):
+            opt.step(closure=lambda: None)
+        opt.step()                                        # begin() is implied
+        ckpt = opt.state_dict()
+        assert ckpt["format"] == "toner.fast.v3" and ckpt["core"]["t"] == 1
+        assert set(ckpt["core"]["ema"]) == {f"{i}.{k}" for i in range(LAYERS) for k in ("attn", "o", "mlp", "down")}
+        assert set(ckpt["core"]["moments"]) == {f"body.blocks.{i}.{r}.weight" for i in range(LAYERS)
+                                                for r in ("q", "k", "v", "o", "gate", "up", "down")}
+        with pytest.raises(RuntimeError):
+            opt.load_state_dict(ckpt)                     # not a fresh optimizer
+    finally:
+        opt.close()
+    stack2, opt2 = make(fast, "llama", "muont", ns_steps=2)
+    try:
+        bad = dict(ckpt, config=dict(ckpt["config"], ns_steps=3))
+        with pytest.raises(ValueError):
+            opt2.load_state_dict(bad)
+        opt2.load_state_dict(ckpt)
+        core = opt2._core
+        assert core.t == 1 and abs(core.weight - 0.05) < 1e-9
+        assert torch.equal(core.groups["d"].factors.ema[0].cpu(), ckpt["core"]["ema"]["0.attn"])
+        assert torch.equal(core.roles["q"]["group"].m[1].cpu(), ckpt["core"]["moments"]["body.blocks.1.q.weight"]["m"])
+    finally:
+        opt2.close()

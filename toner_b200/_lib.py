@@ -51,6 +51,7 @@ SIGNATURES = {
     "toner_init": (C.c_int, [C.c_int]),
     "toner_last_error": (C.c_char_p, []),
     "toner_sm_count": (C.c_int, []),
+    "toner_launch_count": (C.c_longlong, []),
     "toner_device_status": (C.c_int, [_vp, C.POINTER(C.c_int)]),
     "toner_gemm": (C.c_int, [C.POINTER(GemmDesc), _vp]),
     "toner_syrk_upper": (C.c_int, [C.POINTER(_vp), _vp, _i64, _i32, _i32, _i32, _i64, _vp, _i32, _f32, _f32, _vp]),

@@ -7,7 +7,8 @@
 //   X_K ~ M_0^{-1/p}  =>  A^{-1/p} = X_K ||A||_F^{-1/p}
 // (a_k, b_k) map the interval [l_k, 1] known to contain the spectrum of M_k onto [l_{k+1}, 1] with
 // l_{k+1} as large as a linear T allows (the ends of the interval and the interior maximum of
-// mu (a - b mu)^p are levelled); once l_k is close to 1 they become the Newton values ((p+1)/p, 1/p).
+// mu (a - b mu)^p are levelled, subject to a cap on b/a that bounds the dynamic range of T^p); once
+// l_k is close to 1 they become the Newton values ((p+1)/p, 1/p).
 // The schedule depends only on (n, damping, p), so the iteration count is fixed and stated.
 #include <cmath>
 #include <vector>
@@ -20,22 +21,31 @@ struct NewtonStep {
   double a, b, lower;
 };
 
+// Dynamic range allowed for T^p.  The unconstrained minimax step sends the top of the spectrum (mu = 1)
+// down to the new lower bound, i.e. T = a I - b M gets an eigenvalue (a - b) << a and T^p spans
+// (a / (a - b))^p; a component that small relative to ||T^p|| is lost in operand rounding and can come
+// out negative, after which the iteration diverges.  Capping b / a keeps every eigen-component of T^p
+// above 1e-3 of its norm, at the price of one more iteration.
+constexpr double kMaxPowerRange = 1e3;
+
 // Minimax-scaled schedule; returns the steps and the final lower bound of the spectrum.
 static std::vector<NewtonStep> newton_schedule(double l0, int p, int iters, double* lower_out) {
   std::vector<NewtonStep> out;
+  const double max_ratio = 1.0 - std::pow(kMaxPowerRange, -1.0 / p);
   double l = l0;
   for (int k = 0; k < iters; ++k) {
     NewtonStep s;
     s.lower = l;
     const double r = std::pow(l, 1.0 / p);
-    const double ratio = (l < 1.0 - 1e-9) ? (1.0 - r) / (1.0 - r * l) : 0.0;  // b/a levelling f(l) = f(1)
-    const double mu_star = ratio > 0 ? 1.0 / (ratio * (p + 1)) : 2.0;         // interior maximum of f
+    double ratio = (l < 1.0 - 1e-9) ? (1.0 - r) / (1.0 - r * l) : 0.0;  // b/a levelling f(l) = f(1)
+    if (ratio > max_ratio) ratio = max_ratio;
+    const double mu_star = ratio > 0 ? 1.0 / (ratio * (p + 1)) : 2.0;   // interior maximum of f
     if (mu_star < 1.0 && mu_star > l) {
-      const double fmax = mu_star * std::pow((double)p / (p + 1), p);          // with a = 1
-      const double fend = std::pow(1.0 - ratio, p);
-      s.a = std::pow(fmax, -1.0 / p);                                          // rescale so that max f = 1
+      const double fmax = mu_star * std::pow((double)p / (p + 1), p);    // with a = 1
+      const double f_low = l * std::pow(1.0 - ratio * l, p), f_top = std::pow(1.0 - ratio, p);
+      s.a = std::pow(fmax, -1.0 / p);                                    // rescale so that max f = 1
       s.b = s.a * ratio;
-      l = fend / fmax;
+      l = (f_low < f_top ? f_low : f_top) / fmax;
     } else {
       s.a = (p + 1.0) / p;
       s.b = 1.0 / p;
@@ -275,12 +285,15 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
     const float* C = ema + (long long)k0 * nn;
     const int t32 = (n + 31) / 32;
     trace_kernel<<<kc, 256, 0, stream>>>(C, n, trace);
+    count_launch();
     damp_kernel<<<dim3(t32, t32, kc), 256, 0, stream>>>(C, M, n, damping, trace);
+    count_launch();
     {
       int rc0 = sumsq_det(M, kc, n, n, n, nn, partials, sumsq_a, stream);
       if (rc0) return rc0;
     }
     scale_stats_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(M, n, sumsq_a, (float)sched[0].a, (float)-sched[0].b, max_m, max_t);
+    count_launch();
     TONER_CUDA(cudaGetLastError());
 
     auto planes_op = [&](const __half* planes, int hi_lo_first) {
@@ -317,6 +330,7 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
       if (it == 0) {
         affine_copy_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(M, X, n, a, -b);  // X_1 = T_0
         TONER_CUDA(cudaGetLastError());
+        count_launch();
         TONER_CUDA(cudaMemcpyAsync(max_x, max_t, sm, cudaMemcpyDeviceToDevice, stream));
       } else {
         rc = split16(X, nullptr, kc, n, n, n, nn, 0.f, 1.f, max_x, nullptr, Xp, inv_x, stream);
@@ -325,8 +339,10 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
           // fold ||A||_F^{-1/p} into the product, take the residual of M before it stops being updated
           TONER_CUDA(zero(resid));
           residual_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(M, n, resid);
+          count_launch();
           finish_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(resid, sumsq_a, inv_x, scale_lo, scale_hi,
                                                             status ? status + k0 : nullptr, kc, p, q, 0.05f);
+          count_launch();
           TONER_CUDA(cudaGetLastError());
           TONER_CUDA(zero(max_x));
           rc = sym_product(Xp, inv_x, Tp, inv_t, root_lo + (long long)k0 * nn, max_x, nullptr, 0.f, 1.f, nullptr);

@@ -1,6 +1,7 @@
 // Per-device context, TMA tensor-map cache and the GEMM launcher.
 #include "runtime.cuh"
 
+#include <atomic>
 #include <cstring>
 #include <mutex>
 #include <unordered_map>
@@ -11,6 +12,9 @@ namespace toner {
 static thread_local std::string g_error;
 static std::mutex g_mutex;
 static Context g_ctx[16];
+
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 void set_error(const std::string& msg) { g_error = msg; }
 int fail(int code, const std::string& msg) {
@@ -187,8 +191,10 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
   const int grid = (int)(total < ctx->num_sms ? total : ctx->num_sms);
   if (bn == 256) {
     gemm_tcgen05_kernel<256><<<grid, kGemmThreads, GemmSmem<256>::kTotal, stream>>>(p);
+    count_launch();
   } else {
     gemm_tcgen05_kernel<128><<<grid, kGemmThreads, GemmSmem<128>::kTotal, stream>>>(p);
+    count_launch();
   }
   TONER_CUDA(cudaGetLastError());
   return 0;
@@ -207,6 +213,8 @@ int toner_init(int device) {
 const char* toner_last_error(void) {
   return toner::g_error.c_str();
 }
+
+long long toner_launch_count(void) { return toner::g_launches.load(std::memory_order_relaxed); }
 
 int toner_sm_count(void) {
   toner::Context* c = toner::context();

@@ -41,6 +41,9 @@ struct Context {
   void* map_cache = nullptr;          // std::unordered_map<std::string, int>*
 };
 
+// Number of kernels this library has launched (all devices, all streams).
+void count_launch(int n = 1);
+
 // Context of the current device (created on first use).  Returns nullptr and sets the error on failure.
 Context* context();
 

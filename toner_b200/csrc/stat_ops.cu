@@ -147,7 +147,9 @@ size_t sumsq_scratch_bytes(int batch) { return (size_t)batch * kSumsqBlocks * si
 int sumsq_det(const float* x, int batch, int rows, int cols, long long ld, long long bs, float* scratch, float* out,
               cudaStream_t stream) {
   sumsq_partial_kernel<<<dim3(kSumsqBlocks, batch), 256, 0, stream>>>(x, rows, cols, ld, bs, scratch);
+  count_launch();
   sumsq_final_kernel<<<(batch + 127) / 128, 128, 0, stream>>>(scratch, kSumsqBlocks, batch, out);
+  count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;
 }
@@ -173,11 +175,13 @@ int split16(const float* x, const float* const* x_list, int batch, int rows, int
     unsigned int* m = static_cast<unsigned int*>(scratch);
     TONER_CUDA(cudaMemsetAsync(m, 0, sizeof(unsigned int) * batch, stream));
     maxabs_kernel<<<dim3(bx, batch), 256, 0, stream>>>(x, x_list, rows, cols, ld, bs, aff_a, aff_b, m);
+    count_launch();
     TONER_CUDA(cudaGetLastError());
     maxabs = m;
   }
   split16_kernel<<<dim3(bx, batch), 256, 0, stream>>>(x, x_list, batch, rows, cols, ld, bs, aff_a, aff_b, maxabs,
                                                      static_cast<__half*>(planes), inv_scale);
+  count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;
 }
@@ -235,6 +239,7 @@ int toner_unpack_ema(const float* packed, float* ema, int32_t k, int32_t n, floa
   const int t = (n + 31) / 32;
   if (k > 65535) return fail(kErrArg, "unpack_ema: k too large");
   unpack_ema_kernel<<<dim3(t, t, k), 256, 0, static_cast<cudaStream_t>(stream)>>>(packed, ema, n, beta, gamma);
+  count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;
 }

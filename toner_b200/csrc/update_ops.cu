@@ -192,6 +192,7 @@ int toner_axpby(const float* x, const float* y, float* out, int64_t n, float a, 
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out)) & 15u)
     return fail(kErrArg, "axpby: pointers must be 16-byte aligned");
   axpby_kernel<<<ew_grid(n / 4 + 1, ctx->num_sms), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, out, n, a, b);
+  count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;
 }
@@ -201,6 +202,7 @@ int toner_scale_stack(const float* x, const float* coeff, float* out, int32_t co
   if (!ctx) return kErrCuda;
   if (!x || !coeff || !out || count <= 0 || per <= 0 || per % 4) return fail(kErrArg, "scale_stack: bad arguments");
   scale_stack_kernel<<<dim3(ew_grid(per / 4, ctx->num_sms), count), 256, 0, static_cast<cudaStream_t>(stream)>>>(x, coeff, out, per);
+  count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;
 }
@@ -240,6 +242,7 @@ int toner_ns_polar(const float* u, int32_t batch, int32_t m, int32_t n, int32_t 
   int rc = sumsq_det(u, batch, m, n, n, mn, partial, ss, stream);
   if (rc) return rc;
   ns_scale_kernel<<<dim3(ew_grid(mn / 4, ctx->num_sms), batch), 256, 0, stream>>>(u, ss, eps, mn, x_out, xb[0]);
+  count_launch();
   TONER_CUDA(cudaGetLastError());
 
   const float ca = 3.4445f, cb = -4.7750f, cc = 2.0315f;  // src/toner/linalg.py:9
@@ -325,6 +328,7 @@ int toner_muont_momentum(const float* const* grad_ptrs, float* m, float* u, int3
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (maxabs) TONER_CUDA(cudaMemsetAsync(maxabs, 0, sizeof(uint32_t) * count, stream));
   muont_momentum_kernel<<<dim3(ew_grid(per / 4, ctx->num_sms), count), 256, 0, stream>>>(grad_ptrs, m, u, per, mu, nesterov, maxabs);
+  count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;
 }
@@ -334,6 +338,7 @@ int toner_muont_coeffs(const float* fro2, int32_t first, int32_t step, int32_t c
   if (!context()) return kErrCuda;
   if (!fro2 || !c1 || !c2 || count <= 0) return fail(kErrArg, "muont_coeffs: bad arguments");
   muont_coeff_kernel<<<(count + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(fro2, first, step, count, n, lr, wd, scale, c1, c2);
+  count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;
 }
@@ -342,6 +347,7 @@ int toner_scale_vec(float* a, const float* b, int32_t count, void* stream) {
   if (!context()) return kErrCuda;
   if (!a || !b || count <= 0) return fail(kErrArg, "scale_vec: bad arguments");
   mul_vec_kernel2<<<(count + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(a, b, count);
+  count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;
 }
@@ -352,6 +358,7 @@ int toner_adamt_first_moment(const float* const* grad_ptrs, float* m, int32_t co
   if (!grad_ptrs || !m || count <= 0) return fail(kErrArg, "adamt_first_moment: bad arguments");
   if (int rc = check_stack("adamt_first_moment", per)) return rc;
   adamt_m_kernel<<<dim3(ew_grid(per / 4, ctx->num_sms), count), 256, 0, static_cast<cudaStream_t>(stream)>>>(grad_ptrs, m, per, beta1);
+  count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;
 }
@@ -365,6 +372,7 @@ int toner_adamt_ratio(const float* t, float* v, float* num, int32_t count, int64
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (maxabs) TONER_CUDA(cudaMemsetAsync(maxabs, 0, sizeof(uint32_t) * count, stream));
   adamt_ratio_kernel<<<dim3(ew_grid(per / 4, ctx->num_sms), count), 256, 0, stream>>>(t, v, num, per, beta2, bc2, eps, maxabs);
+  count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;
 }
@@ -374,6 +382,7 @@ int toner_adamt_coeffs(const float* fro2, int32_t first, int32_t step, int32_t c
   if (!context()) return kErrCuda;
   if (!fro2 || !ss_before || !ss_after || !c1 || !c2 || count <= 0) return fail(kErrArg, "adamt_coeffs: bad arguments");
   adamt_coeff_kernel<<<(count + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(fro2, first, step, count, n, lr, wd, ss_before, ss_after, c1, c2);
+  count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;
 }
@@ -384,6 +393,7 @@ int toner_apply_delta(float* const* weight_ptrs, const float* delta, int32_t cou
   if (!weight_ptrs || !delta || count <= 0) return fail(kErrArg, "apply_delta: bad arguments");
   if (int rc = check_stack("apply_delta", per)) return rc;
   apply_delta_kernel<<<dim3(ew_grid(per / 4, ctx->num_sms), count), 256, 0, static_cast<cudaStream_t>(stream)>>>(weight_ptrs, delta, per);
+  count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;
 }

@@ -1,0 +1,304 @@
+"""Layer-sharded asynchronous Toner step for uniform transformer blocks.
+
+Work split on one multi-GPU box (one process per GPU):
+
+* every rank holds the sampled BF16 input rows of *all* layers for its own tokens and computes the
+  partial Grams of every statistic with the SYRK kernel (data parallel);
+* layers are owned by ranks in contiguous blocks; owners receive the summed Grams (NCCL
+  reduce-scatter of packed FP32 triangles, issued chunk by chunk so that it overlaps the SYRK of the
+  next chunk), keep the statistic EMAs, compute the inverse-root factors and the parameter changes of
+  their layers;
+* the changes are all-gathered per projection role (NCCL, asynchronous, overlapping the next role's
+  products) and every rank adds all of them to its replica of the weights.
+
+``begin()`` runs statistics and factors on a high-priority side stream so that they overlap the
+last backward pass; ``step()`` joins it.  The only host synchronisation in ``step()`` is the wait
+for the factors' convergence flags.
+
+Interface and ownership rules follow the reference's FastTonerCore (src/toner/fast/engine.py:173-345,
+556-644, 774-880); the arithmetic is the one documented in ``toner_b200.core``.
+"""
+
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import core, ops
+
+KINDS_D = ("attn", "o", "mlp")  # statistics of hidden width, per layer, in this order
+ROLE_KIND = {"q": "attn", "k": "attn", "v": "attn", "o": "o", "attn_proj": "o", "gate": "mlp", "up": "mlp",
+             "fc": "mlp", "down": "down", "mlp_proj": "down"}
+
+
+def layer_counts(layers: int, world: int, weights: Optional[Sequence[float]] = None) -> List[int]:
+    """Layers owned by each rank, as contiguous blocks: equal split, or proportional to ``weights`` by
+    largest remainder (src/toner/fast/engine.py:66-83)."""
+    if not weights:
+        if layers % world:
+            raise ValueError("layers must split evenly over the ranks (or give owner weights)")
+        return [layers // world] * world
+    w = [max(0.0, float(x)) for x in weights]
+    if len(w) != world or sum(w) <= 0:
+        raise ValueError("owner weights need one non-negative weight per rank")
+    raw = [layers * x / sum(w) for x in w]
+    cnt = [int(x) for x in raw]
+    by_remainder = sorted(range(world), key=lambda r: raw[r] - cnt[r], reverse=True)
+    for r in by_remainder[: layers - sum(cnt)]:
+        cnt[r] += 1
+    return cnt
+
+
+class StatGroup:
+    """All statistics of one width: row buffers for every layer, EMAs and factors for the owned ones."""
+
+    def __init__(self, name: str, keys: List[Tuple[int, str]], n: int, rows: int, per_rank: int, rank: int, world: int,
+                 device: torch.device, strengths: Tuple[float, float], damping: float, scratch: core.Scratch) -> None:
+        self.name, self.keys, self.n, self.rows = name, keys, n, rows
+        self.k_all, self.per, self.rank, self.world = len(keys), per_rank, rank, world
+        self.lo = rank * per_rank
+        self.own = keys[self.lo: self.lo + per_rank]
+        self.tri = n * (n + 1) // 2
+        # one stacked row buffer: statistic s of this rank's tokens is rows_buf[s]
+        self.rows_buf = torch.empty(self.k_all, rows, n, device=device, dtype=torch.bfloat16)
+        self.factors = core.FactorSet(per_rank, n, device, strengths, damping, scratch)
+        self.partial: Optional[torch.Tensor] = None   # (chunks, world, cs, tri) packed partial Grams (world > 1)
+        self.summed: Optional[torch.Tensor] = None    # (per, tri) summed Grams of the owned statistics
+        self.chunk_stats = per_rank
+
+    def plan_chunks(self, chunks: int) -> None:
+        """Split the owned block into `chunks` pieces; chunk c of every rank is reduced together."""
+        chunks = max(1, min(chunks, self.per))
+        while self.per % chunks:
+            chunks -= 1
+        self.chunks = chunks
+        self.chunk_stats = self.per // chunks
+        dev = self.rows_buf.device
+        self.partial = torch.empty(chunks, self.world, self.chunk_stats, self.tri, device=dev, dtype=torch.float32)
+        self.summed = torch.empty(chunks, self.chunk_stats, self.tri, device=dev, dtype=torch.float32)
+        # row buffers feeding chunk c, in (rank, j) order: statistic r*per + c*cs + j
+        self.chunk_lists = [[self.rows_buf[r * self.per + c * self.chunk_stats + j]
+                             for r in range(self.world) for j in range(self.chunk_stats)] for c in range(chunks)]
+
+
+class FastTonerCore:
+    """MuonT or AdamT over the projection matrices of L uniform blocks, sharded by layer."""
+
+    def __init__(self, named: Dict[str, torch.Tensor], bindings: Dict[str, Tuple[int, str, str]], kind: str, *,
+                 layers: int, hid: int, mlp: int, local_rows: int, args, world: int, rank: int,
+                 device: torch.device) -> None:
+        if kind not in ("adamt", "muont"):
+            raise ValueError("kind must be 'adamt' or 'muont'")
+        self.kind, self.args, self.world, self.rank, self.device = kind, args, world, rank, device
+        self.L = layers
+        self.rows_total = local_rows * world
+        self.decay = float(args.statistic_momentum)
+        self.layer_counts = layer_counts(layers, world)
+        self.per_layers = self.layer_counts[rank]
+        self.owner_of_layer = [r for r, c in enumerate(self.layer_counts) for _ in range(c)]
+        self.scratch = core.Scratch()
+        strengths = (float(args.inner_strength), float(args.outer_strength))
+        damping = float(getattr(args, "damping", 1e-3))
+        self.groups = {
+            "d": StatGroup("d", [(i, k) for i in range(layers) for k in KINDS_D], hid, local_rows,
+                           len(KINDS_D) * self.per_layers, rank, world, device, strengths, damping, self.scratch),
+            "f": StatGroup("f", [(i, "down") for i in range(layers)], mlp, local_rows, self.per_layers, rank, world,
+                           device, strengths, damping, self.scratch),
+        }
+        self.weight = 0.0
+        # matrices by role; the owned layers of a role form one MatrixGroup
+        self.names = list(named.keys())
+        self.params = list(named.values())
+        self.param_groups = [{"params": self.params, "lr": 0.0, "weight_decay": float(args.weight_decay)}]
+        roles: Dict[str, List[Tuple[int, str, torch.Tensor]]] = {}
+        for name, p in named.items():
+            layer, role, stat_kind = bindings[name]
+            if stat_kind != ROLE_KIND[role]:
+                raise ValueError(f"Invalid input-statistic binding for matrix {name}")
+            roles.setdefault(role, []).append((layer, name, p))
+        self.roles = {}
+        lo_layer = sum(self.layer_counts[:rank])
+        for role, items in roles.items():
+            items.sort(key=lambda it: it[0])
+            if [it[0] for it in items] != list(range(layers)):
+                raise ValueError(f"role {role} must have exactly one matrix per layer")
+            all_w = [it[2] for it in items]
+            own_w = all_w[lo_layer: lo_layer + self.per_layers]
+            stat_kind = ROLE_KIND[role]
+            if stat_kind == "down":
+                g, first, step = self.groups["f"], 0, 1
+            else:
+                g, first, step = self.groups["d"], KINDS_D.index(stat_kind), len(KINDS_D)
+            group = core.MatrixGroup(own_w, g.factors, first, step, kind)
+            shape = (self.per_layers,) + tuple(all_w[0].shape)
+            delta = torch.empty(shape, device=device, dtype=torch.float32)
+            gathered = torch.empty((world,) + shape, device=device, dtype=torch.float32) if world > 1 else None
+            self.roles[role] = dict(group=group, all=all_w, names=[it[1] for it in items], delta=delta,
+                                    gathered=gathered, all_ptrs=ops.pointer_table(all_w))
+        self.t = 0
+        self.steps = 0
+        self.extra = 0
+        self.timing: Dict[str, float] = {}
+        self.gpu_ms: Dict[str, float] = {}
+        self.main_stream = torch.cuda.current_stream(device)
+        self.side = torch.cuda.Stream(device=device, priority=-1)
+        self.pg = dist.new_group(backend="nccl") if world > 1 else None
+        if world > 1:
+            for g in self.groups.values():
+                g.plan_chunks(int(getattr(args, "stat_chunks", 4)))
+        self.begun = False
+        self._ev: Optional[List[torch.cuda.Event]] = None
+        self._ev_last: Optional[List[torch.cuda.Event]] = None
+        self.ev_done: Optional[torch.cuda.Event] = None
+
+    @property
+    def fallbacks(self) -> int:
+        return sum(g.factors.fallbacks for g in self.groups.values())
+
+    # ------------------------------------------------------------------ statistics (side stream)
+    def _stats(self) -> None:
+        """Partial Grams of every statistic from this rank's rows, summed over ranks at the owners, EMA."""
+        b = self.decay
+        gamma = (1 - b) / self.rows_total
+        if self.world == 1:
+            for g in self.groups.values():
+                ops.syrk_upper(g.rows_buf, g.factors.ema, ops.EMA_FULL, b, gamma)   # SYRK with the EMA fused
+        else:
+            pending = []
+            for g in self.groups.values():
+                for c in range(g.chunks):
+                    ops.syrk_upper(g.chunk_lists[c], g.partial[c].view(-1, g.tri), ops.PACKED)
+                    # NCCL waits for the SYRK just enqueued and runs on its own stream: the next chunk's SYRK overlaps it
+                    work = dist.reduce_scatter_tensor(g.summed[c], g.partial[c], group=self.pg, async_op=True)
+                    pending.append((g, c, work))
+            for g, c, work in pending:
+                work.wait()
+                cs = g.chunk_stats
+                ops.unpack_ema(g.summed[c], g.factors.ema[c * cs:(c + 1) * cs], b, gamma)
+        self.weight = b * self.weight + (1 - b)
+
+    @torch.no_grad()
+    def begin(self) -> None:
+        """Statistics and factors on the side stream; call right after the last microbatch's forward."""
+        t0 = time.perf_counter()
+        ev_fwd = torch.cuda.Event()
+        ev_fwd.record(self.main_stream)
+        self._ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ev_fwd)
+            self._ev[0].record(self.side)
+            self._stats()
+            self._ev[1].record(self.side)
+            for g in self.groups.values():
+                g.factors.compute()
+            self._ev[2].record(self.side)
+            self.ev_done = torch.cuda.Event()
+            self.ev_done.record(self.side)
+        self.begun = True
+        self.timing["begin_host"] = time.perf_counter() - t0
+
+    # ------------------------------------------------------------------ updates (main stream)
+    @torch.no_grad()
+    def step(self) -> None:
+        a = self.args
+        lr, wd = self.param_groups[0]["lr"], self.param_groups[0]["weight_decay"]
+        if self._ev_last is not None and self._ev_last[3].query():
+            e = self._ev_last
+            self.gpu_ms = {"stats": e[0].elapsed_time(e[1]), "roots": e[1].elapsed_time(e[2]),
+                           "update": e[2].elapsed_time(e[3])}
+        t0 = time.perf_counter()
+        if not self.begun:
+            self.begin()
+        self.begun = False
+        flagged = 0
+        with torch.cuda.stream(self.side):
+            for g in self.groups.values():
+                flagged += g.factors.finish()       # host waits for the convergence flags only
+        self.main_stream.wait_stream(self.side)
+        t1 = time.perf_counter()
+        self.t += 1
+        works = []
+        for role, info in self.roles.items():
+            group: core.MatrixGroup = info["group"]
+            if group.count:
+                grads = [p.grad for p in group.weights]
+                if self.kind == "muont":
+                    core.muont_group_delta(group, grads, info["delta"], self.scratch, lr=lr, weight_decay=wd,
+                                           momentum=float(a.momentum), nesterov=bool(a.nesterov),
+                                           ns_steps=int(a.ns_steps), ns_eps=float(a.ns_eps))
+                else:
+                    core.adamt_group_delta(group, grads, info["delta"], self.scratch, lr=lr, weight_decay=wd,
+                                           betas=(float(a.beta1), float(a.beta2)), eps=float(a.eps), t=self.t)
+            if self.world > 1:
+                works.append((info, dist.all_gather_into_tensor(info["gathered"], info["delta"], group=self.pg,
+                                                                async_op=True)))
+            else:
+                ops.apply_delta(info["all_ptrs"], info["delta"])
+        for info, work in works:
+            work.wait()
+            ops.apply_delta(info["all_ptrs"], info["gathered"].view((-1,) + tuple(info["delta"].shape[1:])))
+        self._ev[3].record(self.main_stream)
+        self._ev_last = self._ev
+        self.steps += 1
+        self.timing.update(roots_host=t1 - t0, update_host=time.perf_counter() - t1)
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for p in self.params:
+            p.grad = None
+
+    # ------------------------------------------------------------------ checkpoint state
+    def _gather(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return t
+        full = torch.empty((self.world,) + tuple(t.shape), device=t.device, dtype=t.dtype)
+        dist.all_gather_into_tensor(full, t.contiguous(), group=self.pg)
+        return full.view((-1,) + tuple(t.shape[1:]))
+
+    @torch.no_grad()
+    def full_state(self):
+        """Collective: statistic EMAs and parameter moments gathered on rank zero (None elsewhere)."""
+        self.main_stream.wait_stream(self.side)
+        ema = {}
+        for g in self.groups.values():
+            full = self._gather(g.factors.ema)
+            if self.rank == 0:
+                for (i, k), c in zip(g.keys, full.unbind(0)):
+                    ema[f"{i}.{k}"] = c.cpu()
+            del full
+        moments: Dict[str, Dict[str, torch.Tensor]] = {}
+        for role, info in self.roles.items():
+            group = info["group"]
+            for key, stack in (("m", group.m), ("v", group.v)):
+                if stack is None:
+                    continue
+                full = self._gather(stack)
+                if self.rank == 0:
+                    for name, val in zip(info["names"], full.unbind(0)):
+                        moments.setdefault(name, {})[key] = val.cpu()
+                del full
+        if self.rank != 0:
+            return None
+        return {"ema": ema, "weight": self.weight, "moments": moments, "t": self.t}
+
+    @torch.no_grad()
+    def load_full_state(self, sd) -> None:
+        """Every rank picks its owned statistics and moments by name (any world size)."""
+        for g in self.groups.values():
+            for j, (i, k) in enumerate(g.own):
+                g.factors.ema[j].copy_(sd["ema"][f"{i}.{k}"])
+        self.weight = sd["weight"]
+        self.t = sd["t"]
+        lo_layer = sum(self.layer_counts[:self.rank])
+        for role, info in self.roles.items():
+            group = info["group"]
+            names = info["names"][lo_layer: lo_layer + self.per_layers]
+            missing = [nm for nm in names if nm not in sd["moments"]]
+            if missing:
+                raise ValueError(f"checkpoint has no Toner moments for {missing[:3]}...")
+            for j, nm in enumerate(names):
+                group.m[j].copy_(sd["moments"][nm]["m"])
+                if group.v is not None:
+                    group.v[j].copy_(sd["moments"][nm]["v"])

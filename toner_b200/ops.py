@@ -37,6 +37,11 @@ def sm_count() -> int:
     return _lib.load().toner_sm_count()
 
 
+def launch_count() -> int:
+    """Kernels launched by the CUDA library so far."""
+    return int(_lib.load().toner_launch_count())
+
+
 def device_status() -> int:
     """Synchronise the current stream and return (and clear) the kernels' status word; 0 is healthy."""
     out = C.c_int(0)

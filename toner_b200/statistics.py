@@ -37,28 +37,32 @@ class ActivationStatistics:
 
     def __init__(self, layers: Mapping[str, nn.Linear], *, head: int = 32, stride: int = 16,
                  distributed: bool = True, process_group=None) -> None:
-        if not layers:
-            raise ValueError("Select at least one nn.Linear layer.")
-        if head < 0 or stride < 1:
-            raise ValueError("head must be nonnegative and stride positive.")
+        if len(layers) == 0:
+            raise ValueError("no layers given: pass a mapping name -> nn.Linear")
+        if stride < 1 or head < 0:
+            raise ValueError("sampling needs head >= 0 and stride >= 1")
         self.layers = dict(layers)
-        self.head, self.stride = head, stride
-        self.distributed, self.process_group = distributed, process_group
-        self._active = False
-        self._closed = False
-        self._sums: Dict[str, torch.Tensor] = {}
-        self._counts: Dict[str, int] = {}
+        self.head = head
+        self.stride = stride
+        self.distributed = distributed
+        self.process_group = process_group
+        self._active = self._closed = False
+        self._sums: Dict[str, torch.Tensor] = {}     # packed upper triangles, summed over microbatches
+        self._counts: Dict[str, int] = {}            # rows behind each sum
         self._positions: Dict[tuple, torch.Tensor] = {}
-        seen = set()
+        weights_seen = set()
         for name, layer in self.layers.items():
             if not isinstance(layer, nn.Linear):
-                raise TypeError(f"{name}: expected nn.Linear.")
-            if id(layer.weight) in seen:
-                raise ValueError("Shared/tied weights require an explicit statistic; do not register them twice.")
-            seen.add(id(layer.weight))
+                raise TypeError(f"layer '{name}' is a {type(layer).__name__}, not an nn.Linear")
             if layer.in_features % 8:
-                raise ValueError(f"{name}: toner_b200 needs input widths that are multiples of 8")
-        self._handles = [layer.register_forward_pre_hook(self._make_hook(name)) for name, layer in self.layers.items()]
+                raise ValueError(f"layer '{name}': toner_b200 needs input widths that are multiples of 8")
+            if id(layer.weight) in weights_seen:
+                raise ValueError(f"layer '{name}' shares its weight with another registered layer; a tied weight "
+                                 "needs one explicit statistic")
+            weights_seen.add(id(layer.weight))
+        self._handles = []
+        for name, layer in self.layers.items():
+            self._handles.append(layer.register_forward_pre_hook(self._make_hook(name)))
 
     # ------------------------------------------------------------------ capture
     def _gram_into(self, name: str, rows: torch.Tensor) -> None:
@@ -89,29 +93,31 @@ class ActivationStatistics:
         def collect(module, inputs):
             if not self._active:
                 return
-            if not inputs or not torch.is_tensor(inputs[0]):
-                raise TypeError(f"{name}: capture expects a positional tensor input.")
-            x = inputs[0].detach()
+            x = inputs[0] if inputs else None
+            if not torch.is_tensor(x):
+                raise TypeError(f"layer '{name}' was called without a positional tensor input")
+            x = x.detach()
             if x.ndim < 2 or x.shape[-1] != module.in_features:
-                raise ValueError(f"{name}: expected rows of {module.in_features} input features.")
+                raise ValueError(f"layer '{name}': input rows must have {module.in_features} features")
             if not x.is_cuda:
-                raise ValueError(f"{name}: toner_b200 captures CUDA activations only (there is no CPU path)")
-            if x.ndim > 2:
-                seq = x.shape[-2]
-                key = (seq, x.device)
-                if key not in self._positions:
-                    positions = sample_positions(seq, self.head, self.stride)
-                    if not positions:
-                        raise ValueError(f"{name}: sampling selects no input positions.")
-                    self._positions[key] = torch.tensor(positions, device=x.device, dtype=torch.long)
-                x = x.index_select(-2, self._positions[key])
-            # Linear's autocast happens after its pre-hook: use the values its GEMM will actually read.
+                raise ValueError(f"layer '{name}': toner_b200 captures CUDA activations only (there is no CPU path)")
+            if x.ndim > 2:  # (..., sequence, features): keep the sampled positions of every sequence
+                key = (x.shape[-2], x.device)
+                idx = self._positions.get(key)
+                if idx is None:
+                    chosen = sample_positions(x.shape[-2], self.head, self.stride)
+                    if not chosen:
+                        raise ValueError(f"layer '{name}': the sampling rule keeps no position of a length-"
+                                         f"{x.shape[-2]} sequence")
+                    idx = self._positions[key] = torch.tensor(chosen, device=x.device, dtype=torch.long)
+                x = x.index_select(-2, idx)
+            # The pre-hook runs before Linear's autocast: round to what its GEMM will actually read.
             if torch.is_autocast_enabled(x.device.type):
                 x = x.to(torch.get_autocast_dtype(x.device.type))
-            x = x.reshape(-1, x.shape[-1]).contiguous()
-            if not x.shape[0]:
-                raise ValueError(f"{name}: cannot estimate a statistic from zero rows.")
-            self._gram_into(name, x)
+            rows = x.reshape(-1, x.shape[-1]).contiguous()
+            if rows.shape[0] == 0:
+                raise ValueError(f"layer '{name}': no rows to estimate a statistic from")
+            self._gram_into(name, rows)
 
         return collect
 
@@ -119,30 +125,30 @@ class ActivationStatistics:
     def capture(self):
         """Capture one forward; an exception discards the whole pending step."""
         if self._closed:
-            raise RuntimeError("The statistic collector is closed.")
+            raise RuntimeError("capture() after close()")
         if self._active:
-            raise RuntimeError("Nested capture contexts would double-count activations.")
+            raise RuntimeError("capture() is already active; nesting would count activations twice")
         self._active = True
+        failed = True
         try:
             yield self
-        except BaseException:
-            self._active = False
-            self.clear()
-            raise
+            failed = False
         finally:
             self._active = False
+            if failed:  # a forward that raised may have captured only some layers: drop the pending step
+                self.clear()
 
     # ------------------------------------------------------------------ commit
     @torch.no_grad()
     def commit(self, optimizer) -> None:
         """Pool the sums over ranks, update the optimizer's statistic EMAs once, clear the captures."""
-        if self._active:
-            raise RuntimeError("Exit capture() before committing statistics.")
         if self._closed:
-            raise RuntimeError("The statistic collector is closed.")
-        missing = [name for name in self.layers if name not in self._sums]
-        if missing:
-            raise RuntimeError(f"No captured inputs for: {', '.join(missing)}")
+            raise RuntimeError("commit() after close()")
+        if self._active:
+            raise RuntimeError("commit() inside capture(); leave the context first")
+        absent = sorted(set(self.layers) - set(self._sums))
+        if absent:
+            raise RuntimeError("nothing was captured for layer(s): " + ", ".join(absent))
         pooled = self.distributed and dist.is_available() and dist.is_initialized()
         means = {}
         for name, layer in self.layers.items():
@@ -163,13 +169,12 @@ class ActivationStatistics:
     def clear(self) -> None:
         """Discard captured sums, for example after skipping a training step."""
         if self._active:
-            raise RuntimeError("Cannot clear statistics during capture.")
-        self._sums.clear()
-        self._counts.clear()
+            raise RuntimeError("clear() inside capture()")
+        self._sums = {}
+        self._counts = {}
 
     def close(self) -> None:
-        for handle in self._handles:
-            handle.remove()
-        self._handles.clear()
+        while self._handles:
+            self._handles.pop().remove()
         self.clear()
         self._closed = True

@@ -1,0 +1,81 @@
+"""Synthetic transformer-block stacks and inputs for tests and benchmarks.
+
+Only the projection modules matter to the optimizers: a "block" here is a bag of ``nn.Linear`` layers
+with the attribute names the adapters expect, and a cheap forward that feeds every projection an input
+of the right shape (so the capture hooks run) without paying for attention.
+"""
+
+from __future__ import annotations
+
+from typing import List
+
+import torch
+from torch import nn
+
+
+class LlamaProjections(nn.Module):
+    """q, k, v, o, gate, up, down of one Llama-style block (bias-free)."""
+
+    def __init__(self, hidden: int, mlp: int, device, std: float = 0.02) -> None:
+        super().__init__()
+        for name, (o, i) in dict(q=(hidden, hidden), k=(hidden, hidden), v=(hidden, hidden), o=(hidden, hidden),
+                                 gate=(mlp, hidden), up=(mlp, hidden), down=(hidden, mlp)).items():
+            lin = nn.Linear(i, o, bias=False, device=device)
+            nn.init.normal_(lin.weight, 0.0, std)
+            setattr(self, name, lin)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Shape-correct stand-in for a block: every projection runs once on a plausible input."""
+        a = self.q(x) + self.k(x) + self.v(x)
+        x = x + self.o(a)
+        h = torch.nn.functional.silu(self.gate(x)) * self.up(x)
+        return x + self.down(h)
+
+
+class NanoGPTAttention(nn.Module):
+    def __init__(self, hidden: int, device, std: float) -> None:
+        super().__init__()
+        for name in ("q", "k", "v", "proj"):
+            lin = nn.Linear(hidden, hidden, bias=True, device=device)
+            nn.init.normal_(lin.weight, 0.0, std)
+            setattr(self, name, lin)
+
+
+class NanoGPTMlp(nn.Module):
+    def __init__(self, hidden: int, mlp: int, device, std: float) -> None:
+        super().__init__()
+        self.fc = nn.Linear(hidden, mlp, bias=True, device=device)
+        self.proj = nn.Linear(mlp, hidden, bias=True, device=device)
+        nn.init.normal_(self.fc.weight, 0.0, std)
+        nn.init.normal_(self.proj.weight, 0.0, std)
+
+
+class NanoGPTProjections(nn.Module):
+    """attn.{q,k,v,proj} and mlp.{fc,proj} of one modded-nanoGPT block (squared-ReLU MLP)."""
+
+    def __init__(self, hidden: int, mlp: int, device, std: float = 0.02) -> None:
+        super().__init__()
+        self.attn = NanoGPTAttention(hidden, device, std)
+        self.mlp = NanoGPTMlp(hidden, mlp, device, std)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        a = self.attn.q(x) + self.attn.k(x) + self.attn.v(x)
+        x = x + self.attn.proj(a)
+        return x + self.mlp.proj(torch.relu(self.mlp.fc(x)).square())
+
+
+def make_stack(layout: str, layers: int, hidden: int, mlp: int, device, seed: int = 0) -> List[nn.Module]:
+    torch.manual_seed(seed)
+    cls = LlamaProjections if layout == "llama" else NanoGPTProjections
+    return [cls(hidden, mlp, device) for _ in range(layers)]
+
+
+def fill_rows(buf: torch.Tensor, seed: int) -> None:
+    """Activation-like BF16 rows: unit-variance noise plus a shared mean direction (as residual streams have)."""
+    g = torch.Generator(device=buf.device).manual_seed(seed)
+    k, rows, n = buf.shape
+    mean = torch.randn(1, 1, n, device=buf.device, generator=g) * 0.5
+    step = max(1, min(k, (1 << 28) // max(1, rows * n)))
+    for s in range(0, k, step):
+        e = min(k, s + step)
+        buf[s:e].copy_(torch.randn(e - s, rows, n, device=buf.device, generator=g) + mean)
