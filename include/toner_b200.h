@@ -78,6 +78,9 @@ typedef struct toner_gemm_desc {
   int32_t tile_n;           /* 0 = choose; else 128 or 256 */
   int32_t promote;          /* > 0: k-blocks (64 deep) per tensor-core accumulation chain; chains are summed in
                                FP32 registers with round-to-nearest (the tensor core truncates).  0: one chain */
+  int32_t raster;           /* tile columns per rasterisation group for full schedules (0: default 8) */
+  int32_t promote_all;      /* 0: chain only the first segment (later segments of a split product are 2^-11 of
+                               it and form one chain each); 1: chain every segment */
 } toner_gemm_desc;
 
 int toner_gemm(const toner_gemm_desc* desc, void* stream);

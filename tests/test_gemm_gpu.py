@@ -124,7 +124,7 @@ def test_promoted_chains_match_one_chain(ops, promote):
     want = ref_mm(a[0], b[0], False, False) + ref_mm(a[1], b[1], False, False)
     d = torch.empty(batch, m, n, device="cuda")
     ops.gemm(ops.operand(a, seg_z=(0, batch, 0)), ops.operand(b, seg_z=(0, batch, 0)), m=m, n=n, k=k, batch=batch,
-             fmt=1, segs=2, d=d, promote=promote)
+             fmt=1, segs=2, d=d, promote=promote, promote_all=(promote == 3))
     ops.assert_healthy()
     close(d, want, 2 * k)
 

@@ -41,7 +41,7 @@ class GemmDesc(C.Structure):
         ("d16", C.c_void_p), ("ld16", C.c_int64), ("d16_bs", C.c_int64), ("d16_fmt", C.c_int32),
         ("sumsq", C.c_void_p), ("maxabs", C.c_void_p), ("maxaff", C.c_void_p),
         ("aff_a", C.c_float), ("aff_b", C.c_float),
-        ("tile_n", C.c_int32), ("promote", C.c_int32),
+        ("tile_n", C.c_int32), ("promote", C.c_int32), ("raster", C.c_int32), ("promote_all", C.c_int32),
     ]
 
 

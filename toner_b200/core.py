@@ -143,7 +143,7 @@ class FactorSet:
         if self.q > 1:
             ops.split16(self.root_hi, planes=self.hi_planes, inv_scale=self.hi_inv, scratch=tmp)
             ops.sumsq(self.root_hi, out=self.fro2_hi,
-                      scratch=self.scratch.bytes_like("sumsq", 256 * self.k, self.device))
+                      scratch=self.scratch.bytes_like("sumsq", ops.sumsq_scratch_bytes(self.k), self.device))
 
     def finish(self) -> int:
         """Wait for the convergence flags only; recompute flagged statistics by eigendecomposition (the
@@ -165,7 +165,7 @@ class FactorSet:
             self.root_lo[i] = ((vec * (unit + self.damping).pow(-1.0 / self.p)) @ vec.T).float()
             if self.q > 1:
                 self.root_hi[i] = ((vec * (unit + self.damping).pow(-float(self.q) / self.p)) @ vec.T).float()
-        ops.sumsq(self.root_lo, out=self.fro2_lo, scratch=self.scratch.bytes_like("sumsq", 256 * self.k, self.device))
+        ops.sumsq(self.root_lo, out=self.fro2_lo, scratch=self.scratch.bytes_like("sumsq", ops.sumsq_scratch_bytes(self.k), self.device))
         self._split()
         return len(bad)
 
@@ -269,7 +269,7 @@ def adamt_group_delta(group: MatrixGroup, grads: Sequence[torch.Tensor], delta: 
     c2 = scratch.get("c2", (count,), torch.float32, dev)
     ss0 = scratch.get("ss0", (count,), torch.float32, dev)
     ss1 = scratch.get("ss1", (count,), torch.float32, dev)
-    ssq_ws = scratch.bytes_like("sumsq", 256 * count, dev)
+    ssq_ws = scratch.bytes_like("sumsq", ops.sumsq_scratch_bytes(count), dev)
     gp = group.grad_ptrs(grads)
     ops.adamt_first_moment(gp, group.m, b1)
     ops.split16_list(gp, count, m, n, planes, inv, maxabs)

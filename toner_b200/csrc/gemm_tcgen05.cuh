@@ -5,7 +5,7 @@
 // One persistent CTA per SM, warp-specialised:
 //   warp 0      TMA producer: 128-byte-swizzled operand tiles into a shared-memory ring
 //   warp 1      allocates tensor memory and issues tcgen05.mma (one thread), accumulating in TMEM
-//   warps 2..9  epilogue: tcgen05.ld the accumulator (double-buffered, so it overlaps the next chain's
+//   warps 4..11 epilogue: tcgen05.ld the accumulator (double-buffered, so it overlaps the next chain's
 //               MMAs), sum chains in registers, apply the affine epilogue, store FP32 / 16-bit results
 // The tensor core adds every 16-deep partial sum into its FP32 accumulator by truncation; over long K
 // that bias reaches 1e-5 relative.  Where FP32 accuracy matters (`promote`), accumulation chains are
@@ -30,7 +30,7 @@ constexpr int kBM = 128;          // tile rows (UMMA M)
 constexpr int kBK = 64;           // 16-bit elements per k-block: one 128-byte swizzle row
 constexpr int kUmmaK = 16;        // K per tcgen05.mma for 16-bit operands
 constexpr int kMaxSegs = 3;
-constexpr int kGemmThreads = 320;      // TMA warp, MMA warp, eight epilogue warps
+constexpr int kGemmThreads = 384;      // warpgroup 0: TMA warp, MMA warp, two idle; warpgroups 1-2: epilogue
 constexpr long long kWaitCycles = 4000000000LL;  // about two seconds; a healthy wait is microseconds
 
 enum GemmStatus : int { kOk = 0, kTimeoutProducer = 101, kTimeoutMma = 102, kTimeoutEpilogue = 103 };
@@ -48,6 +48,8 @@ struct GemmParams {
   int fmt;  // operand format: 0 FP16, 1 BF16
   int tri;  // 1: M == N, only tiles meeting the upper triangle are computed
   int promote;  // > 0: k-blocks per tensor-core accumulation chain; chains are summed in FP32 registers
+  int promote_all;  // 0: only the first segment is chained (split products); 1: every segment
+  int raster;   // tile columns per rasterisation group (full schedules): keeps a group's B panels in L2
   // epilogue: d = alpha * acc + beta * C ; alpha, beta optionally scaled per batch from device arrays
   float alpha, beta;
   const float* alpha_a;
@@ -103,8 +105,16 @@ __device__ __forceinline__ void tile_coord(const GemmParams& p, int BN, int t, i
   b = t / tiles_per_batch;
   int r = t - b * tiles_per_batch;
   if (!p.tri) {
-    tm = r / tiles_n;
-    tn = r - tm * tiles_n;
+    // Column groups of `raster` tiles, rows swept inside a group: the tiles in flight at any moment share
+    // a few B panels (resident in L2 for the whole sweep) and stream A panels once per group.
+    const int tiles_m = tiles_per_batch / tiles_n;
+    const int g = p.raster > 0 ? p.raster : tiles_n;
+    const int per_group = g * tiles_m;
+    const int group = r / per_group;
+    const int in_group = r - group * per_group;
+    const int width = min(g, tiles_n - group * g);
+    tm = in_group / width;
+    tn = group * g + (in_group - tm * width);
     return;
   }
   tm = 0;
@@ -147,20 +157,27 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
   const int kb_per_seg = (p.K + kBK - 1) / kBK;
   const int num_kb = kb_per_seg * p.segs;
   // Accumulation chains: with promote > 0 the MMA warp starts a fresh TMEM accumulator every `promote`
-  // k-blocks (never across a segment boundary) and the epilogue warps sum the chains in registers.
-  const int chunks_per_seg = p.promote > 0 ? (kb_per_seg + p.promote - 1) / p.promote : 1;
-  const int chunks_per_tile = p.promote > 0 ? chunks_per_seg * p.segs : 1;
+  // k-blocks of the FIRST segment and the epilogue warps sum the chains in registers.  Later segments
+  // (the hi*lo cross terms of a split product, 2^-11 of the first) form one chain each: truncation
+  // inside them is far below the result's last bit.  promote_all chains every segment the same way.
+  const int chunks_seg0 = p.promote > 0 ? (kb_per_seg + p.promote - 1) / p.promote : 1;
+  const int chunks_rest = (p.promote > 0 && p.promote_all) ? chunks_seg0 : 1;
+  const int chunks_per_tile = p.promote > 0 ? chunks_seg0 + (p.segs - 1) * chunks_rest : 1;
   auto chunk_range = [&](int ch, int& kb_begin, int& kb_end) {
     if (p.promote <= 0) {
       kb_begin = 0;
       kb_end = num_kb;
       return;
     }
-    const int seg = ch / chunks_per_seg, c = ch - seg * chunks_per_seg;
-    kb_begin = seg * kb_per_seg + c * p.promote;
-    kb_end = min(kb_begin + p.promote, (seg + 1) * kb_per_seg);
+    int seg = 0, c = ch;
+    if (ch >= chunks_seg0) {
+      seg = 1 + (ch - chunks_seg0) / chunks_rest;
+      c = (ch - chunks_seg0) - (seg - 1) * chunks_rest;
+    }
+    const bool chained = (seg == 0) || p.promote_all;
+    kb_begin = seg * kb_per_seg + (chained ? c * p.promote : 0);
+    kb_end = chained ? min(kb_begin + p.promote, (seg + 1) * kb_per_seg) : (seg + 1) * kb_per_seg;
   };
-
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::kStages; ++s) {
       ptx::mbar_init(full_bar(s), 1);
@@ -182,6 +199,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (warp < 4) {
+  ptx::reg_dec<56>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -196,35 +215,35 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         ptx::fence_tensormap_acquire(amap);
         ptx::fence_tensormap_acquire(bmap);
         const int m0 = tm * kBM, n0 = tn * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, kWaitCycles) || *abort_flag) {
-            report(p.status, kTimeoutProducer);
-            *abort_flag = 1;
-            ok = false;
-            break;
-          }
-          const int seg = kb / kb_per_seg;
-          const int k0 = (kb - seg * kb_per_seg) * kBK;
-          const uint32_t sa = base + stage * S::kStageBytes;
-          const uint32_t sb = sa + S::kABytes;
+        for (int seg = 0; seg < p.segs && ok; ++seg) {
           const int za = b * p.a_z_stride + p.a_seg_z[seg];
           const int zb = b * p.b_z_stride + p.b_seg_z[seg];
-          ptx::mbar_expect_tx(full_bar(stage), S::kStageBytes);
-          if (p.a_mn) {
+          for (int k0 = 0; k0 < p.K; k0 += kBK) {
+            if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, kWaitCycles) || *abort_flag) {
+              report(p.status, kTimeoutProducer);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            const uint32_t sa = base + stage * S::kStageBytes;
+            const uint32_t sb = sa + S::kABytes;
+            ptx::mbar_expect_tx(full_bar(stage), S::kStageBytes);
+            if (p.a_mn) {
 #pragma unroll
-            for (int s = 0; s < kBM / 64; ++s) ptx::tma_load_3d(sa + s * 8192, amap, full_bar(stage), m0 + s * 64, k0, za);
-          } else {
-            ptx::tma_load_3d(sa, amap, full_bar(stage), k0, m0, za);
-          }
-          if (p.b_mn) {
+              for (int s = 0; s < kBM / 64; ++s) ptx::tma_load_3d(sa + s * 8192, amap, full_bar(stage), m0 + s * 64, k0, za);
+            } else {
+              ptx::tma_load_3d(sa, amap, full_bar(stage), k0, m0, za);
+            }
+            if (p.b_mn) {
 #pragma unroll
-            for (int s = 0; s < BN / 64; ++s) ptx::tma_load_3d(sb + s * 8192, bmap, full_bar(stage), n0 + s * 64, k0, zb);
-          } else {
-            ptx::tma_load_3d(sb, bmap, full_bar(stage), k0, n0, zb);
-          }
-          if (++stage == S::kStages) {
-            stage = 0;
-            phase ^= 1u;
+              for (int s = 0; s < BN / 64; ++s) ptx::tma_load_3d(sb + s * 8192, bmap, full_bar(stage), n0 + s * 64, k0, zb);
+            } else {
+              ptx::tma_load_3d(sb, bmap, full_bar(stage), k0, n0, zb);
+            }
+            if (++stage == S::kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
         }
       }
@@ -285,12 +304,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         }
       }
     }
+  }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..9)
+    ptx::reg_inc<224>();
+    // ------------------------------------------------------------ epilogue (warps 4..11)
     // Warp w may read TMEM lanes [32*(w&3), +32); two warps share a lane group and split the columns.
     constexpr int NCH = BN / 64;  // 32-column chunks per warp
     const int lane_group = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = (warp - 4) >> 2;
     float racc[NCH * 32];  // running sums, added with round-to-nearest (the tensor core truncates)
     uint32_t gchunk = 0;
     bool alive = true;
@@ -323,17 +344,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         ptx::tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN + half * (BN / 2));
 #pragma unroll
-        for (int cc = 0; cc < NCH; ++cc) {
-          if (!need[cc]) continue;
-          uint32_t acc[32];
-          ptx::tmem_ld32(taddr + (uint32_t)(cc * 32), acc);
-          ptx::tmem_ld_wait();
+        for (int cc = 0; cc < NCH; cc += 2) {  // two TMEM loads in flight per wait
+          uint32_t acc0[32], acc1[32];
+          const bool n0_ = need[cc], n1_ = (cc + 1 < NCH) && need[cc + 1];
+          if (n0_) ptx::tmem_ld32(taddr + (uint32_t)(cc * 32), acc0);
+          if (n1_) ptx::tmem_ld32(taddr + (uint32_t)((cc + 1) * 32), acc1);
+          if (n0_ || n1_) ptx::tmem_ld_wait();
           if (ch == 0) {
+            if (n0_) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) racc[cc * 32 + j] = __uint_as_float(acc[j]);
+              for (int j = 0; j < 32; ++j) racc[cc * 32 + j] = __uint_as_float(acc0[j]);
+            }
+            if (n1_) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) racc[(cc + 1) * 32 + j] = __uint_as_float(acc1[j]);
+            }
           } else {
+            if (n0_) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) racc[cc * 32 + j] += __uint_as_float(acc[j]);
+              for (int j = 0; j < 32; ++j) racc[cc * 32 + j] += __uint_as_float(acc0[j]);
+            }
+            if (n1_) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) racc[(cc + 1) * 32 + j] += __uint_as_float(acc1[j]);
+            }
           }
         }
         // buffer drained: hand it back to the MMA warp

@@ -47,6 +47,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long lo
   return true;
 }
 
+// ---------------------------------------------------------------- register reallocation between warpgroups
+// All four warps of a warpgroup execute these together.  The kernel is compiled for 168 registers per
+// thread (12 warps); the control warpgroup gives registers back and the epilogue warpgroups take them.
+template <int N>
+__device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ---------------------------------------------------------------- proxies / fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

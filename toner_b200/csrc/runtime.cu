@@ -170,6 +170,8 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
   p.fmt = d.fmt;
   p.tri = d.tri ? 1 : 0;
   p.promote = d.promote > 0 ? d.promote : 0;
+  p.promote_all = d.promote_all ? 1 : 0;
+  p.raster = d.tri ? 0 : (d.raster > 0 ? d.raster : 8);
   p.alpha = d.alpha; p.beta = d.beta;
   p.alpha_a = d.alpha_a; p.alpha_b = d.alpha_b; p.beta_v = d.beta_v;
   p.alpha_b_step = d.alpha_b_step > 0 ? d.alpha_b_step : 1;

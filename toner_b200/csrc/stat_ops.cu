@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(256) split16_kernel(const float* __restrict__ 
 
 // ------------------------------------------------------------------ deterministic sum of squares
 // Fixed grid, fixed reduction tree: the same input always gives the same bits (float atomics would not).
-constexpr int kSumsqBlocks = 64;
+constexpr int kSumsqBlocks = 296;  // two per SM on a 148-SM part; fixed so that results do not depend on the device
 
 __global__ void __launch_bounds__(256) sumsq_partial_kernel(const float* __restrict__ x, int rows, int cols, long long ld,
                                                             long long bs, float* __restrict__ partial) {

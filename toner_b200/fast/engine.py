@@ -52,6 +52,22 @@ def layer_counts(layers: int, world: int, weights: Optional[Sequence[float]] = N
     return cnt
 
 
+def chunk_plan(per_rank: int, chunks: int) -> int:
+    """Number of chunks actually used: the largest divisor of `per_rank` not above the request."""
+    chunks = max(1, min(int(chunks), per_rank))
+    while per_rank % chunks:
+        chunks -= 1
+    return chunks
+
+
+def chunk_members(world: int, per_rank: int, chunks: int, c: int) -> List[int]:
+    """Statistic indices reduced together in chunk c, in (rank, j) order: statistic r*per + c*cs + j lands
+    at row r*cs + j of the chunk's send buffer, so a reduce-scatter hands rank r rows [r*cs, (r+1)*cs), i.e.
+    its own statistics c*cs .. (c+1)*cs - 1."""
+    cs = per_rank // chunks
+    return [r * per_rank + c * cs + j for r in range(world) for j in range(cs)]
+
+
 class StatGroup:
     """All statistics of one width: row buffers for every layer, EMAs and factors for the owned ones."""
 
@@ -71,17 +87,15 @@ class StatGroup:
 
     def plan_chunks(self, chunks: int) -> None:
         """Split the owned block into `chunks` pieces; chunk c of every rank is reduced together."""
-        chunks = max(1, min(chunks, self.per))
-        while self.per % chunks:
-            chunks -= 1
+        chunks = chunk_plan(self.per, chunks)
         self.chunks = chunks
         self.chunk_stats = self.per // chunks
         dev = self.rows_buf.device
         self.partial = torch.empty(chunks, self.world, self.chunk_stats, self.tri, device=dev, dtype=torch.float32)
         self.summed = torch.empty(chunks, self.chunk_stats, self.tri, device=dev, dtype=torch.float32)
         # row buffers feeding chunk c, in (rank, j) order: statistic r*per + c*cs + j
-        self.chunk_lists = [[self.rows_buf[r * self.per + c * self.chunk_stats + j]
-                             for r in range(self.world) for j in range(self.chunk_stats)] for c in range(chunks)]
+        self.chunk_lists = [[self.rows_buf[s] for s in chunk_members(self.world, self.per, chunks, c)]
+                            for c in range(chunks)]
 
 
 class FastTonerCore:

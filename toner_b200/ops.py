@@ -108,7 +108,7 @@ def gemm(a: Operand, b: Operand, *, m: int, n: int, k: int, batch: int, fmt: int
          beta_v: Optional[torch.Tensor] = None, tri: bool = False, mirror: bool = False, packed: bool = False,
          sumsq: Optional[torch.Tensor] = None, maxabs: Optional[torch.Tensor] = None,
          maxaff: Optional[torch.Tensor] = None, aff: Tuple[float, float] = (0.0, 1.0), tile_n: int = 0, promote: int = 0,
-         alpha_b_step: int = 1) -> None:
+         alpha_b_step: int = 1, promote_all: bool = False, raster: int = 0) -> None:
     """Launch the tcgen05 GEMM (toner_gemm).  d / c are FP32 (batch, m, n) stacks (or packed triangles)."""
     desc = GemmDesc()
     desc.a, desc.b = a, b
@@ -139,6 +139,8 @@ def gemm(a: Operand, b: Operand, *, m: int, n: int, k: int, batch: int, fmt: int
     desc.aff_a, desc.aff_b = aff
     desc.tile_n = tile_n
     desc.promote = promote
+    desc.promote_all = int(promote_all)
+    desc.raster = raster
     desc.alpha_b_step = alpha_b_step
     check(_lib.load().toner_gemm(C.byref(desc), _stream()), "toner_gemm")
 
@@ -278,6 +280,10 @@ def ns_polar(u: torch.Tensor, steps: int = 10, eps: float = 1e-5, *, out: Option
     return out
 
 
+def sumsq_scratch_bytes(batch: int) -> int:
+    return int(_lib.load().toner_sumsq_scratch_bytes(batch))
+
+
 def sumsq(x: torch.Tensor, out: Optional[torch.Tensor] = None, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Reproducible per-matrix sum of squares of a (batch, rows, cols) FP32 stack (toner_sumsq)."""
     _need_cuda(x)
@@ -287,7 +293,7 @@ def sumsq(x: torch.Tensor, out: Optional[torch.Tensor] = None, scratch: Optional
     if out is None:
         out = torch.empty(batch, device=x.device, dtype=torch.float32)
     if scratch is None:
-        scratch = torch.empty(_lib.load().toner_sumsq_scratch_bytes(batch), device=x.device, dtype=torch.uint8)
+        scratch = torch.empty(sumsq_scratch_bytes(batch), device=x.device, dtype=torch.uint8)
     check(_lib.load().toner_sumsq(x.data_ptr(), batch, rows, cols, x.stride(1), x.stride(0), scratch.data_ptr(),
                                   out.data_ptr(), _stream()), "toner_sumsq")
     return out
