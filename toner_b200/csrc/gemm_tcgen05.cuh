@@ -96,7 +96,8 @@ struct GemmSmem {
   static constexpr int kStages = (BN == 256) ? 4 : 6;
   static constexpr int kTileBytes = kStages * kStageBytes;
   static constexpr int kBarBytes = 256;
-  static constexpr int kTotal = kTileBytes + kBarBytes + 1024;  // 1024: alignment slack
+  static constexpr int kEpiBytes = 8 * 32 * 33 * 4;  // one padded 32 x 32 FP32 staging block per epilogue warp
+  static constexpr int kTotal = kTileBytes + kBarBytes + kEpiBytes + 1024;  // 1024: alignment slack
   static constexpr int kTmemCols = 2 * BN;
 };
 
@@ -134,7 +135,144 @@ __device__ __forceinline__ void report(int* status, int code) {
   if (status) atomicCAS(status, 0, code);
 }
 
-template <int BN>
+// Per-tile epilogue state (uniform over the warp).
+struct EpilogueTile {
+  const float* Cb;
+  float* Db;
+  uint16_t* Hb;  // 16-bit copy of the result (FP16 or BF16 bits)
+  float alpha, beta;
+  bool use_c;
+};
+
+constexpr int kEpiStride = 33;                      // floats per staged row: 32 + 1 keeps both access patterns conflict-free
+constexpr int kEpiWarpBytes = 32 * kEpiStride * 4;  // one 32 x 32 block per epilogue warp
+
+__device__ __forceinline__ uint16_t to_bits16(float v, int bf16) {
+  const __half h = __float2half_rn(v);
+  const __nv_bfloat16 g = __float2bfloat16_rn(v);
+  return bf16 ? *reinterpret_cast<const uint16_t*>(&g) : *reinterpret_cast<const uint16_t*>(&h);
+}
+
+__device__ __forceinline__ uint2 pack4_16(float a, float b, float c, float d, int bf16) {
+  const __half2 h0 = __floats2half2_rn(a, b), h1 = __floats2half2_rn(c, d);
+  const __nv_bfloat162 g0 = __floats2bfloat162_rn(a, b), g1 = __floats2bfloat162_rn(c, d);
+  uint2 u;
+  u.x = bf16 ? *reinterpret_cast<const uint32_t*>(&g0) : *reinterpret_cast<const uint32_t*>(&h0);
+  u.y = bf16 ? *reinterpret_cast<const uint32_t*>(&g1) : *reinterpret_cast<const uint32_t*>(&h1);
+  return u;
+}
+
+// The epilogue writes the result in 32 x 32 blocks staged in shared memory (thread t's row of the
+// accumulator at stage[t * kEpiStride ...]), so that the loops below are rolled -- the code stays a few
+// KB and resident in the instruction cache -- and every global access of a warp is made of contiguous runs.
+
+// Interior block: wholly inside the matrix, 16-byte aligned rows, no element needing diagonal treatment
+// (for a symmetric result the block lies strictly above the diagonal, so all of it is mirrored and counts
+// twice in the sum of squares).  Lane = (row within a group of four, four consecutive columns): one warp
+// access covers four rows x 128 bytes.  The mirrored half is written the same way with rows and columns
+// exchanged.  The values read from C are fetched four row-groups at a time before any store, so that the
+// loads overlap (C and D may be the same matrix; every element is read before it is written).
+__device__ __forceinline__ void epilogue_block_vec(const GemmParams& p, const EpilogueTile& e, float* stage, int row_first,
+                                                   int c0, int lane, float& ssq, float& mabs) {
+  const int q = lane & 7, sub = lane >> 3;
+  const int col = c0 + 4 * q;
+  const bool mirror = p.tri && p.mirror;
+  float s = 0.f, m = 0.f;
+#pragma unroll 1
+  for (int half = 0; half < 2; ++half) {
+    float4 cv[4];
+    if (e.use_c) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int row = row_first + 16 * half + 4 * u + sub;
+        cv[u] = *reinterpret_cast<const float4*>(e.Cb + (long long)row * p.ldc + col);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int i = 16 * half + 4 * u + sub;
+      const int row = row_first + i;
+      float* src = stage + i * kEpiStride + 4 * q;
+      float v0 = e.alpha * src[0], v1 = e.alpha * src[1], v2 = e.alpha * src[2], v3 = e.alpha * src[3];
+      if (e.use_c) {
+        v0 = fmaf(e.beta, cv[u].x, v0); v1 = fmaf(e.beta, cv[u].y, v1);
+        v2 = fmaf(e.beta, cv[u].z, v2); v3 = fmaf(e.beta, cv[u].w, v3);
+      }
+      if (e.Db) *reinterpret_cast<float4*>(e.Db + (long long)row * p.ldd + col) = make_float4(v0, v1, v2, v3);
+      if (e.Hb) *reinterpret_cast<uint2*>(e.Hb + (long long)row * p.ld16 + col) = pack4_16(v0, v1, v2, v3, p.d16_fmt);
+      if (mirror) {
+        src[0] = v0; src[1] = v1; src[2] = v2; src[3] = v3;
+      }
+      s = fmaf(v0, v0, s); s = fmaf(v1, v1, s); s = fmaf(v2, v2, s); s = fmaf(v3, v3, s);
+      m = fmaxf(fmaxf(fmaxf(m, fabsf(v0)), fabsf(v1)), fmaxf(fabsf(v2), fabsf(v3)));
+    }
+  }
+  ssq += p.tri ? 2.f * s : s;
+  mabs = fmaxf(mabs, m);
+  if (mirror) {
+    __syncwarp();
+    const int tcol = row_first + 4 * q;  // source rows 4q .. 4q+3 become four consecutive target columns
+    const float* src = stage + (4 * q) * kEpiStride;
+#pragma unroll 2
+    for (int it = 0; it < 8; ++it) {
+      const int j = 4 * it + sub;  // source column = target row
+      const float v0 = src[j], v1 = src[kEpiStride + j], v2 = src[2 * kEpiStride + j], v3 = src[3 * kEpiStride + j];
+      const long long trow = c0 + j;
+      if (e.Db) *reinterpret_cast<float4*>(e.Db + trow * p.ldd + tcol) = make_float4(v0, v1, v2, v3);
+      if (e.Hb) *reinterpret_cast<uint2*>(e.Hb + trow * p.ld16 + tcol) = pack4_16(v0, v1, v2, v3, p.d16_fmt);
+    }
+  }
+  __syncwarp();
+}
+
+// Any other block (matrix edge, diagonal block of a symmetric result, packed or unaligned output): one
+// element per lane with full masking, lane = column, so rows -- also rows of a packed triangle -- are
+// still written as contiguous runs; the mirrored half with lane = source row.
+__device__ __forceinline__ void epilogue_block_scalar(const GemmParams& p, const EpilogueTile& e, float* stage, int row_first,
+                                                      int c0, int lane, float& ssq, float& mabs, float& maff) {
+  const int col = c0 + lane;
+  const bool col_ok = col < p.N;
+  const bool mirror = p.tri && p.mirror;
+  const int rows = min(32, p.M - row_first);
+#pragma unroll 1
+  for (int i = 0; i < rows; ++i) {
+    const int row = row_first + i;
+    float v = 0.f;
+    if (col_ok && !(p.tri && col < row)) {
+      v = e.alpha * stage[i * kEpiStride + lane];
+      const long long co = p.packed ? packed_off(row, col, p.N) : (long long)row * p.ldc + col;
+      const long long dof = p.packed ? packed_off(row, col, p.N) : (long long)row * p.ldd + col;
+      if (e.use_c) v = fmaf(e.beta, e.Cb[co], v);
+      if (e.Db) e.Db[dof] = v;
+      if (e.Hb) e.Hb[(long long)row * p.ld16 + col] = to_bits16(v, p.d16_fmt);
+      const float w = (p.tri && col > row) ? 2.f : 1.f;
+      ssq = fmaf(w * v, v, ssq);
+      mabs = fmaxf(mabs, fabsf(v));
+      maff = fmaxf(maff, fabsf(fmaf(p.aff_b, v, col == row ? p.aff_a : 0.f)));
+    }
+    if (mirror) stage[i * kEpiStride + lane] = v;  // final value; zero where masked
+  }
+  if (mirror) {
+    __syncwarp();
+    const int row = row_first + lane;  // this lane's source row becomes the target column
+    const int cols = min(32, p.N - c0);
+    if (row < p.M) {
+#pragma unroll 1
+      for (int j = 0; j < cols; ++j) {
+        const int c = c0 + j;
+        if (c > row) {
+          const float v = stage[lane * kEpiStride + j];
+          if (e.Db) e.Db[(long long)c * p.ldd + row] = v;
+          if (e.Hb) e.Hb[(long long)c * p.ld16 + row] = to_bits16(v, p.d16_fmt);
+        }
+      }
+    }
+  }
+  __syncwarp();
+}
+
+// kChained: the kernel sums several accumulation chains per tile in registers (p.promote > 0).
+template <int BN, bool kChained>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
   using S = GemmSmem<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -200,7 +338,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < 4) {
-  ptx::reg_dec<56>();
+  ptx::reg_dec<40>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -306,13 +444,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
     }
   }
   } else {
-    ptx::reg_inc<224>();
+    ptx::reg_inc<232>();
     // ------------------------------------------------------------ epilogue (warps 4..11)
     // Warp w may read TMEM lanes [32*(w&3), +32); two warps share a lane group and split the columns.
     constexpr int NCH = BN / 64;  // 32-column chunks per warp
     const int lane_group = warp & 3;
     const int half = (warp - 4) >> 2;
-    float racc[NCH * 32];  // running sums, added with round-to-nearest (the tensor core truncates)
+    float* const stage = reinterpret_cast<float*>(smem + S::kTileBytes + S::kBarBytes) + (warp - 4) * (32 * kEpiStride);
+    constexpr bool chained = kChained;
+    // Running sums of the accumulation chains (chained products only), added with round-to-nearest: the
+    // tensor core itself adds into its accumulator by truncation.
+    float racc[kChained ? NCH * 32 : 1];
     uint32_t gchunk = 0;
     bool alive = true;
     for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
@@ -320,17 +462,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
       tile_coord(p, BN, t, tiles_per_batch, tiles_n, b, tm, tn);
       const int m0 = tm * kBM, n0 = tn * BN;
       const int row_first = m0 + lane_group * 32;
-      const int r = row_first + lane;
-      const bool row_ok = r < p.M;
-      // chunks of columns this warp never needs: beyond N, or wholly below the diagonal (warp-uniform)
-      bool need[NCH];
-#pragma unroll
-      for (int cc = 0; cc < NCH; ++cc) {
-        const int c0 = n0 + half * (BN / 2) + cc * 32;
-        need[cc] = (c0 < p.N) && !(p.tri && c0 + 31 < row_first);
-      }
-      for (int ch = 0; ch < chunks_per_tile; ++ch, ++gchunk) {
-        const int buf = gchunk & 1u;
+      const int col_first = n0 + half * (BN / 2);
+      // 32-column blocks this warp never needs: beyond N, or wholly below the diagonal (warp-uniform)
+      auto needed = [&](int c0) { return (c0 < p.N) && !(p.tri && c0 + 31 < row_first); };
+      auto wait_chain = [&](int buf) {
         // every lane observes the barrier itself, so each one is ordered after the MMAs' TMEM writes
         const int waited = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), (gchunk >> 1) & 1u, kWaitCycles) ? 1 : 0);
         if (!waited || *abort_flag) {
@@ -338,122 +473,116 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
             report(p.status, kTimeoutEpilogue);
             *abort_flag = 1;
           }
-          alive = false;
-          break;
+          return false;
         }
         ptx::tc_fence_after();
-        const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN + half * (BN / 2));
-#pragma unroll
-        for (int cc = 0; cc < NCH; cc += 2) {  // two TMEM loads in flight per wait
-          uint32_t acc0[32], acc1[32];
-          const bool n0_ = need[cc], n1_ = (cc + 1 < NCH) && need[cc + 1];
-          if (n0_) ptx::tmem_ld32(taddr + (uint32_t)(cc * 32), acc0);
-          if (n1_) ptx::tmem_ld32(taddr + (uint32_t)((cc + 1) * 32), acc1);
-          if (n0_ || n1_) ptx::tmem_ld_wait();
-          if (ch == 0) {
-            if (n0_) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) racc[cc * 32 + j] = __uint_as_float(acc0[j]);
-            }
-            if (n1_) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) racc[(cc + 1) * 32 + j] = __uint_as_float(acc1[j]);
-            }
-          } else {
-            if (n0_) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) racc[cc * 32 + j] += __uint_as_float(acc0[j]);
-            }
-            if (n1_) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) racc[(cc + 1) * 32 + j] += __uint_as_float(acc1[j]);
-            }
-          }
-        }
-        // buffer drained: hand it back to the MMA warp
+        return true;
+      };
+      auto release = [&](int buf) {  // buffer drained: hand it back to the MMA warp
         ptx::tc_fence_before();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+      };
+      auto tmem_of = [&](int buf) {
+        return tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN + half * (BN / 2));
+      };
+
+      if (chained) {
+#pragma unroll
+        for (int j = 0; j < NCH * 32; ++j) racc[j] = 0.f;
+        for (int ch = 0; ch < chunks_per_tile; ++ch, ++gchunk) {
+          const int buf = gchunk & 1u;
+          if (!wait_chain(buf)) {
+            alive = false;
+            break;
+          }
+          const uint32_t taddr = tmem_of(buf);
+          // Software pipeline over the warp's blocks: the load of block cc+1 is in flight while block cc is added.
+          uint32_t s0[32], s1[32];
+          if (needed(col_first)) ptx::tmem_ld32(taddr, s0);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int cc = 0; cc < NCH; ++cc) {
+            uint32_t* cur = (cc & 1) ? s1 : s0;
+            uint32_t* nxt = (cc & 1) ? s0 : s1;
+            if (cc + 1 < NCH && needed(col_first + (cc + 1) * 32)) ptx::tmem_ld32(taddr + (uint32_t)((cc + 1) * 32), nxt);
+            if (needed(col_first + cc * 32)) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) racc[cc * 32 + j] += __uint_as_float(cur[j]);
+            }
+            if (cc + 1 < NCH) ptx::tmem_ld_wait();
+          }
+          release(buf);
+        }
+        if (!alive) break;
+      } else if (!wait_chain(gchunk & 1u)) {
+        alive = false;
+        break;
       }
-      if (!alive) break;
 
-      float alpha = p.alpha, beta = p.beta;
-      if (p.alpha_a) alpha *= __ldg(p.alpha_a + b);
-      if (p.alpha_b) alpha *= __ldg(p.alpha_b + (long long)b * p.alpha_b_step);
-      if (p.beta_v) beta *= __ldg(p.beta_v + b);
-      const bool use_c = (p.C != nullptr) && (beta != 0.f);
-      const float* Cb = p.C ? p.C + (long long)b * p.c_bs : nullptr;
-      float* Db = p.D ? p.D + (long long)b * p.d_bs : nullptr;
-      __half* Hb = (p.D16 && p.d16_fmt == 0) ? reinterpret_cast<__half*>(p.D16) + (long long)b * p.d16_bs : nullptr;
-      __nv_bfloat16* Bb = (p.D16 && p.d16_fmt == 1) ? reinterpret_cast<__nv_bfloat16*>(p.D16) + (long long)b * p.d16_bs : nullptr;
-      const long long crow = p.packed ? packed_off(r, 0, p.N) : (long long)r * p.ldc;
-      const long long drow = p.packed ? packed_off(r, 0, p.N) : (long long)r * p.ldd;
-      const long long hrow = (long long)r * p.ld16;
+      // ---- write the tile: one rolled loop over the warp's 32 x 32 blocks, staged through shared memory
+      EpilogueTile e;
+      e.alpha = p.alpha;
+      e.beta = p.beta;
+      if (p.alpha_a) e.alpha *= __ldg(p.alpha_a + b);
+      if (p.alpha_b) e.alpha *= __ldg(p.alpha_b + (long long)b * p.alpha_b_step);
+      if (p.beta_v) e.beta *= __ldg(p.beta_v + b);
+      e.use_c = (p.C != nullptr) && (e.beta != 0.f);
+      e.Cb = p.C ? p.C + (long long)b * p.c_bs : nullptr;
+      e.Db = p.D ? p.D + (long long)b * p.d_bs : nullptr;
+      e.Hb = p.D16 ? reinterpret_cast<uint16_t*>(p.D16) + (long long)b * p.d16_bs : nullptr;
       float ssq = 0.f, mabs = 0.f, maff = 0.f;
-
-#pragma unroll
+      const bool rows_inside = row_first + 32 <= p.M;
+      const uint32_t taddr = tmem_of(gchunk & 1u);
+      float* const mine = stage + lane * kEpiStride;
+#pragma unroll 1
       for (int cc = 0; cc < NCH; ++cc) {
-        if (!need[cc]) continue;
-        const int c0 = n0 + half * (BN / 2) + cc * 32;
+        const int c0 = col_first + cc * 32;
+        if (!needed(c0)) continue;
+        if (chained) {
+          switch (cc) {  // the running sums live in registers: static indices only
+            case 0:
 #pragma unroll
-        for (int j4 = 0; j4 < 8; ++j4) {
-          const int c = c0 + j4 * 4;
-          float v[4];
+              for (int j = 0; j < 32; ++j) mine[j] = racc[j];
+              break;
+            case 1:
 #pragma unroll
-          for (int e = 0; e < 4; ++e) v[e] = alpha * racc[cc * 32 + j4 * 4 + e];
-          const bool full4 = row_ok && (c + 3 < p.N) && (!p.tri || c >= r);
-          if (full4 && p.vec_ok) {
-            if (use_c) {
-              const float4 cv = *reinterpret_cast<const float4*>(Cb + crow + c);
-              v[0] += beta * cv.x; v[1] += beta * cv.y; v[2] += beta * cv.z; v[3] += beta * cv.w;
-            }
-            if (Db) *reinterpret_cast<float4*>(Db + drow + c) = make_float4(v[0], v[1], v[2], v[3]);
-            if (Hb) {
-              __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
-              uint2 u;
-              u.x = *reinterpret_cast<uint32_t*>(&h0);
-              u.y = *reinterpret_cast<uint32_t*>(&h1);
-              *reinterpret_cast<uint2*>(Hb + hrow + c) = u;
-            }
-            if (Bb) {
-              __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
-              uint2 u;
-              u.x = *reinterpret_cast<uint32_t*>(&h0);
-              u.y = *reinterpret_cast<uint32_t*>(&h1);
-              *reinterpret_cast<uint2*>(Bb + hrow + c) = u;
-            }
-          } else {
+              for (int j = 0; j < 32; ++j) mine[j] = racc[32 + j];
+              break;
+            case 2:
+              if (NCH > 2) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int ce = c + e;
-              const bool ok = row_ok && ce < p.N && (!p.tri || ce >= r);
-              if (ok) {
-                if (use_c) v[e] += beta * Cb[crow + ce];
-                if (Db) Db[drow + ce] = v[e];
-                if (Hb) Hb[hrow + ce] = __float2half_rn(v[e]);
-                if (Bb) Bb[hrow + ce] = __float2bfloat16_rn(v[e]);
-              } else {
-                v[e] = 0.f;  // masked: contributes nothing to the statistics or the mirror
+                for (int j = 0; j < 32; ++j) mine[j] = racc[(NCH > 2 ? 64 : 0) + j];
               }
-            }
-          }
+              break;
+            default:
+              if (NCH > 2) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int ce = c + e;
-            const bool ok = row_ok && ce < p.N && (!p.tri || ce >= r);
-            if (!ok) continue;
-            const bool off = p.tri && ce > r;
-            if (off && p.mirror) {  // consecutive lanes hold consecutive rows: these stores coalesce
-              if (Db) Db[(long long)ce * p.ldd + r] = v[e];
-              if (Hb) Hb[(long long)ce * p.ld16 + r] = __float2half_rn(v[e]);
-              if (Bb) Bb[(long long)ce * p.ld16 + r] = __float2bfloat16_rn(v[e]);
-            }
-            ssq += (off ? 2.f : 1.f) * v[e] * v[e];
-            mabs = fmaxf(mabs, fabsf(v[e]));
-            maff = fmaxf(maff, fabsf((ce == r ? p.aff_a : 0.f) + p.aff_b * v[e]));
+                for (int j = 0; j < 32; ++j) mine[j] = racc[(NCH > 2 ? 96 : 0) + j];
+              }
+              break;
           }
+        } else {
+          uint32_t raw[32];
+          ptx::tmem_ld32(taddr + (uint32_t)(cc * 32), raw);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) mine[j] = __uint_as_float(raw[j]);
+        }
+        __syncwarp();
+        // warp-uniform choice: interior blocks take the vector path
+        const bool holds_diag = (c0 <= row_first + 31) && (c0 + 31 >= row_first);
+        if (rows_inside && (c0 + 32 <= p.N) && p.vec_ok && !(holds_diag && (p.tri || p.maxaff))) {
+          epilogue_block_vec(p, e, stage, row_first, c0, lane, ssq, mabs);
+        } else {
+          epilogue_block_scalar(p, e, stage, row_first, c0, lane, ssq, mabs, maff);
         }
       }
+      if (!chained) {
+        release(gchunk & 1u);
+        ++gchunk;
+      }
+      maff = fmaxf(maff, fabsf(p.aff_b) * mabs);  // off the diagonal the affine map is a plain scaling
 
       if (p.sumsq || p.maxabs || p.maxaff) {
 #pragma unroll

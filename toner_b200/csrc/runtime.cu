@@ -68,8 +68,10 @@ Context* context() {
     return nullptr;
   }
   c.map_cache = new std::unordered_map<std::string, int>();
-  cudaFuncSetAttribute(gemm_tcgen05_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256>::kTotal);
-  cudaFuncSetAttribute(gemm_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<128>::kTotal);
+  cudaFuncSetAttribute(gemm_tcgen05_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256>::kTotal);
+  cudaFuncSetAttribute(gemm_tcgen05_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256>::kTotal);
+  cudaFuncSetAttribute(gemm_tcgen05_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<128>::kTotal);
+  cudaFuncSetAttribute(gemm_tcgen05_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<128>::kTotal);
   c.device = dev;
   return &c;
 }
@@ -191,13 +193,15 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
   const long long total = (long long)gemm_tiles_per_batch(d.m, d.n, bn, d.tri) * d.batch;
   if (total > 0x7fffffffLL) return fail(kErrArg, "gemm: too many tiles");
   const int grid = (int)(total < ctx->num_sms ? total : ctx->num_sms);
+  const bool chained = p.promote > 0;
   if (bn == 256) {
-    gemm_tcgen05_kernel<256><<<grid, kGemmThreads, GemmSmem<256>::kTotal, stream>>>(p);
-    count_launch();
+    if (chained) gemm_tcgen05_kernel<256, true><<<grid, kGemmThreads, GemmSmem<256>::kTotal, stream>>>(p);
+    else gemm_tcgen05_kernel<256, false><<<grid, kGemmThreads, GemmSmem<256>::kTotal, stream>>>(p);
   } else {
-    gemm_tcgen05_kernel<128><<<grid, kGemmThreads, GemmSmem<128>::kTotal, stream>>>(p);
-    count_launch();
+    if (chained) gemm_tcgen05_kernel<128, true><<<grid, kGemmThreads, GemmSmem<128>::kTotal, stream>>>(p);
+    else gemm_tcgen05_kernel<128, false><<<grid, kGemmThreads, GemmSmem<128>::kTotal, stream>>>(p);
   }
+  count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;
 }

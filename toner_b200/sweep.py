@@ -1,0 +1,254 @@
+"""Kernel sweep: times one kernel of the optimizer step in isolation and reports its roofline fraction.
+
+    python -m toner_b200.sweep syrk  --rows 65536 --n 2048 --k 4 [--mode ema|packed]
+    python -m toner_b200.sweep roots --n 2048 --k 4 --p 8 --q 4 [--cond 1e4]
+    python -m toner_b200.sweep ns    --m 2048 --n 8192 --batch 2
+    python -m toner_b200.sweep gemm  --n 8192 [--split] [--tri]
+    python -m toner_b200.sweep ema   --n 2048 --k 16
+    python -m toner_b200.sweep update --per 4194304 --count 24
+    python -m toner_b200.sweep all   (the shapes of the reference's kernel sweep, reduced to fit a few GB)
+
+Shapes follow the reference's own self-benchmarks (src/toner/fast/syrk.py:389-442, src/toner/fast/muon.py:165-199):
+BF16 N x d rows for SYRK, SPD d x d matrices Q diag(lambda) Q^T with log-uniform lambda for the roots, FP32
+d x 4d Gaussian matrices for Newton-Schulz.  Every input is synthetic and seeded.  Timing: CUDA events on
+the launching stream, `--warmup` untimed calls, `--reps` timed calls, inputs larger than L2 or an L2 flush
+between calls.  Each run prints one JSON line per kernel with the algorithmic work, the time, the achieved
+rate and its fraction of the peak in MEASURED_PEAKS.json (burst BF16 figure: the kernel is timed alone).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from toner_b200 import ops  # noqa: E402
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"tflops": p["bf16_tflops"], "hbm_gbs": p["hbm_gbs"], "source": "measured"}
+    return {"tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+_flush = None
+
+
+def flush_l2():
+    """Write a buffer larger than the 126 MB L2 so that the next call starts cold."""
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush.zero_()
+
+
+def timed(fn, warmup: int, reps: int, flush: bool):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    best = float("inf")
+    for _ in range(reps):
+        if flush:
+            flush_l2()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        total += ms
+        best = min(best, ms)
+    return total / reps, best
+
+
+def report(kernel, shape, ms, best, *, flops=None, bytes_=None, extra=None):
+    pk = peaks()
+    line = {"kernel": kernel, "shape": shape, "ms": round(ms, 4), "ms_best": round(best, 4)}
+    if flops is not None:
+        t = flops / ms / 1e9
+        line.update(bound="tensor", algorithmic_flops=int(flops), achieved=round(t, 1), unit="TFLOP/s", peak=pk["tflops"],
+                    frac=round(t / pk["tflops"], 4))
+    else:
+        g = bytes_ / ms / 1e6
+        line.update(bound="hbm", algorithmic_bytes=int(bytes_), achieved=round(g, 1), unit="GB/s", peak=pk["hbm_gbs"],
+                    frac=round(g / pk["hbm_gbs"], 4))
+    line["peak_source"] = pk["source"]
+    if extra:
+        line.update(extra)
+    ops.assert_healthy()
+    print(json.dumps(line), flush=True)
+    return line
+
+
+def rows_like(k, rows, n, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return torch.randn(k, rows, n, device="cuda", generator=g).to(torch.bfloat16)
+
+
+def spd_stack(k, n, cond, seed=0):
+    """Q diag(lambda) Q^T with Haar Q (QR of a Gaussian matrix, sign-fixed) and log-uniform lambda."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    out = torch.empty(k, n, n, device="cuda")
+    for i in range(k):
+        q, r = torch.linalg.qr(torch.randn(n, n, device="cuda", dtype=torch.float64, generator=g))
+        q = q * torch.sign(torch.diagonal(r)).unsqueeze(0)
+        lam = torch.exp(torch.rand(n, device="cuda", dtype=torch.float64, generator=g) * math.log(cond))
+        out[i] = ((q * lam) @ q.T).float()
+    return out
+
+
+def bench_syrk(a):
+    x = rows_like(a.k, a.rows, a.n)
+    small = x.numel() * 2 < (160 << 20)
+    if a.mode == "ema":
+        out = torch.zeros(a.k, a.n, a.n, device="cuda")
+        fn = lambda: ops.syrk_upper(x, out, ops.EMA_FULL, 0.95, 0.05 / a.rows)
+    else:
+        out = torch.zeros(a.k, a.n * (a.n + 1) // 2, device="cuda")
+        fn = lambda: ops.syrk_upper(x, out, ops.PACKED)
+    ms, best = timed(fn, a.warmup, a.reps, small)
+    flops = a.k * a.rows * a.n * (a.n + 1)
+    byts = a.k * (2 * a.rows * a.n + (12 * a.n * a.n if a.mode == "ema" else 2 * a.n * (a.n + 1)))
+    return report("syrk_" + a.mode, {"k": a.k, "rows": a.rows, "n": a.n}, ms, best, flops=flops,
+                  extra={"full_equivalent_tflops": round(2 * a.k * a.rows * a.n * a.n / ms / 1e9, 1),
+                         "algorithmic_bytes": int(byts)})
+
+
+def bench_roots(a):
+    c = spd_stack(a.k, a.n, a.cond)
+    iters = ops.inv_roots_iterations(a.n, 1e-3, a.p)
+    ws = torch.empty(ops.inv_roots_workspace_bytes(a.k, a.n), device="cuda", dtype=torch.uint8)
+    lo = torch.empty_like(c)
+    hi = torch.empty_like(c) if a.q > 1 else None
+    fn = lambda: ops.inv_roots(c, 1e-3, a.p, a.q, root_lo=lo, root_hi=hi, workspace=ws)
+    ms, best = timed(fn, a.warmup, a.reps, False)
+    log2p, log2q = int(math.log2(a.p)), int(math.log2(a.q))
+    products = (iters - 1) * (log2p + 2) - 1 + 1 + log2q  # X T and T^p M per step (no X product first, no M last)
+    flops = a.k * products * 2 * a.n ** 3
+    return report("inv_roots", {"k": a.k, "n": a.n, "p": a.p, "q": a.q, "cond": a.cond}, ms, best, flops=flops,
+                  extra={"iterations": iters, "damping": 1e-3, "products_per_statistic": products,
+                         "note": "single-pass dense count per product; each product runs 3 FP16 plane passes over "
+                                 "the tiles meeting the upper triangle"})
+
+
+def bench_ns(a):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    u = torch.randn(a.batch, a.m, a.n, device="cuda", generator=g)
+    out = torch.empty_like(u)
+    ws = torch.empty(ops.ns_polar_workspace_bytes(a.batch, a.m, a.n), device="cuda", dtype=torch.uint8)
+    fn = lambda: ops.ns_polar(u, a.steps, 1e-5, out=out, workspace=ws)
+    ms, best = timed(fn, a.warmup, a.reps, False)
+    s, l = min(a.m, a.n), max(a.m, a.n)
+    flops = a.batch * a.steps * (4 * s * s * l + 2 * s ** 3)
+    return report("ns_polar", {"batch": a.batch, "m": a.m, "n": a.n, "steps": a.steps}, ms, best, flops=flops,
+                  extra={"note": "dense count as the reference executes it; the two symmetric products run on the "
+                                 "tiles meeting the upper triangle only"})
+
+
+def bench_gemm(a):
+    n, batch = a.n, a.batch
+    g = torch.Generator(device="cuda").manual_seed(0)
+    d = torch.empty(batch, n, n, device="cuda")
+    if a.split:
+        x = torch.randn(batch, n, n, device="cuda", generator=g)
+        x = x + x.transpose(1, 2)
+        pl, inv = ops.split16(x)
+        A = ops.operand(pl, seg_z=(0, 0, batch))
+        B = ops.operand(pl, seg_z=(0, batch, 0))
+        fn = lambda: ops.gemm(A, B, m=n, n=n, k=n, batch=batch, fmt=0, segs=3, d=d, alpha_a=inv, alpha_b=inv,
+                              tri=a.tri, mirror=a.tri, promote=ops.PROMOTE_ACCURATE)
+        name = "gemm_split3" + ("_sym" if a.tri else "")
+    else:
+        x = torch.randn(batch, n, n, device="cuda", generator=g).to(torch.bfloat16)
+        y = torch.randn(batch, n, n, device="cuda", generator=g).to(torch.bfloat16)
+        A, B = ops.operand(x), ops.operand(y)
+        fn = lambda: ops.gemm(A, B, m=n, n=n, k=n, batch=batch, fmt=1, d=d, tri=a.tri, mirror=a.tri)
+        name = "gemm_bf16" + ("_sym" if a.tri else "")
+    ms, best = timed(fn, a.warmup, a.reps, n * n * batch * 2 < (80 << 20))
+    return report(name, {"n": n, "batch": batch}, ms, best, flops=batch * 2 * n ** 3,
+                  extra={"note": "single-pass dense count 2 n^3 per product"})
+
+
+def bench_ema(a):
+    tri = a.n * (a.n + 1) // 2
+    packed = torch.randn(a.k, tri, device="cuda")
+    ema = torch.zeros(a.k, a.n, a.n, device="cuda")
+    fn = lambda: ops.unpack_ema(packed, ema, 0.95, 0.05)
+    ms, best = timed(fn, a.warmup, a.reps, a.k * a.n * a.n * 4 < (160 << 20))
+    byts = a.k * 4 * (tri + tri + a.n * a.n)   # read packed, read the upper triangle of C, write all of C
+    return report("unpack_ema", {"k": a.k, "n": a.n}, ms, best, bytes_=byts)
+
+
+def bench_update(a):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    grads = [torch.randn(a.per, device="cuda", generator=g) for _ in range(a.count)]
+    weights = [torch.randn(a.per, device="cuda", generator=g) for _ in range(a.count)]
+    m = torch.zeros(a.count, a.per, device="cuda")
+    u = torch.empty_like(m)
+    mx = torch.zeros(a.count, device="cuda", dtype=torch.int32)
+    gp, wp = ops.pointer_table(grads), ops.pointer_table(weights)
+    small = a.count * a.per * 4 < (160 << 20)
+    ms, best = timed(lambda: ops.muont_momentum(gp, m, u, 0.95, True, mx), a.warmup, a.reps, small)
+    report("muont_momentum", {"count": a.count, "per": a.per}, ms, best, bytes_=16 * a.count * a.per)
+    ms, best = timed(lambda: ops.apply_delta(wp, u), a.warmup, a.reps, small)
+    return report("apply_delta", {"count": a.count, "per": a.per}, ms, best, bytes_=12 * a.count * a.per)
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("kernel", choices=["syrk", "roots", "ns", "gemm", "ema", "update", "all"])
+    ap.add_argument("--rows", type=int, default=65536)
+    ap.add_argument("--n", type=int, default=2048)
+    ap.add_argument("--m", type=int, default=2048)
+    ap.add_argument("--k", type=int, default=4)
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--p", type=int, default=8)
+    ap.add_argument("--q", type=int, default=4)
+    ap.add_argument("--cond", type=float, default=1e4)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--per", type=int, default=2048 * 2048)
+    ap.add_argument("--count", type=int, default=24)
+    ap.add_argument("--mode", default="ema", choices=["ema", "packed"])
+    ap.add_argument("--split", action="store_true")
+    ap.add_argument("--tri", action="store_true")
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--reps", type=int, default=10)
+    a = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("the kernel sweep needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(0)
+    table = {"syrk": bench_syrk, "roots": bench_roots, "ns": bench_ns, "gemm": bench_gemm, "ema": bench_ema,
+             "update": bench_update}
+    if a.kernel != "all":
+        table[a.kernel](a)
+        return
+    import copy
+    for rows, n, k in ((65536, 768, 8), (65536, 2048, 4), (262144, 2048, 1), (65536, 4096, 2), (65536, 8192, 1)):
+        b = copy.copy(a); b.rows, b.n, b.k = rows, n, k
+        bench_syrk(b)
+    for n, k in ((768, 8), (2048, 4), (4096, 2)):
+        for p, q in ((8, 4), (4, 1)):
+            b = copy.copy(a); b.n, b.k, b.p, b.q = n, k, p, q
+            bench_roots(b)
+    for d, batch in ((768, 8), (2048, 2), (4096, 1)):
+        b = copy.copy(a); b.m, b.n, b.batch = d, 4 * d, batch
+        bench_ns(b)
+    b = copy.copy(a); b.n, b.k = 2048, 16
+    bench_ema(b)
+    bench_update(a)
+
+
+if __name__ == "__main__":
+    main()
