@@ -81,9 +81,29 @@ typedef struct toner_gemm_desc {
   int32_t raster;           /* tile columns per rasterisation group for full schedules (0: default 8) */
   int32_t promote_all;      /* 0: chain only the first segment (later segments of a split product are 2^-11 of
                                it and form one chain each); 1: chain every segment */
+  /* Optional FP16 hi/lo operand planes of the result, written by the same kernel so that the next
+   * split-precision product needs no separate splitting pass:
+   *   split0: planes of split0_scale * d
+   *   split1: planes of split1_scale * (split1_aff_a * [r==c] + split1_aff_b * d)
+   * hi plane element (b, r, c) at split + b*split_bs + r*split_ld + c, lo plane split_plane elements further.
+   * The scales are the caller's (powers of two chosen from a bound on |d|; FP16 overflows above 65504). */
+  void* split0;
+  void* split1;
+  int64_t split_ld, split_bs, split_plane;
+  float split0_scale, split1_scale, split1_aff_a, split1_aff_b;
+  uint32_t* maxres;         /* optional per-batch accumulator: max |[r==c] - d| as FP32 bits */
 } toner_gemm_desc;
 
 int toner_gemm(const toner_gemm_desc* desc, void* stream);
+
+/* Diagnostics (the reference has none at this level; its engine reports phase times only,
+ * src/toner/fast/adapter.py:536-545).  While enabled, every toner_gemm launch adds cycle counts, summed over
+ * its CTAs, to eight counters: [0] MMA warp busy in its tile loop, [1] MMA warp waiting for a free accumulator,
+ * [2] MMA warp waiting for operands, [3] TMA warp waiting for a free stage, [4] first epilogue warp waiting for an
+ * accumulator, [5] that warp writing results, [6] that warp summing chains, [7] number of CTAs.
+ * The call synchronises `stream`, copies the counters to out8 (HOST, may be NULL), clears them, then switches
+ * the counting on or off.  Off by default; enabling allocates 64 bytes of device memory. */
+int toner_gemm_phase_cycles(int enable, void* stream, unsigned long long* out8);
 
 /* ------------------------------------------------------------------ input statistics
  * Upper-triangle SYRK  S_b = X_b^T X_b  over BF16 row buffers, FP32 accumulation.

@@ -42,6 +42,10 @@ class GemmDesc(C.Structure):
         ("sumsq", C.c_void_p), ("maxabs", C.c_void_p), ("maxaff", C.c_void_p),
         ("aff_a", C.c_float), ("aff_b", C.c_float),
         ("tile_n", C.c_int32), ("promote", C.c_int32), ("raster", C.c_int32), ("promote_all", C.c_int32),
+        ("split0", C.c_void_p), ("split1", C.c_void_p),
+        ("split_ld", C.c_int64), ("split_bs", C.c_int64), ("split_plane", C.c_int64),
+        ("split0_scale", C.c_float), ("split1_scale", C.c_float), ("split1_aff_a", C.c_float), ("split1_aff_b", C.c_float),
+        ("maxres", C.c_void_p),
     ]
 
 
@@ -54,6 +58,7 @@ SIGNATURES = {
     "toner_launch_count": (C.c_longlong, []),
     "toner_device_status": (C.c_int, [_vp, C.POINTER(C.c_int)]),
     "toner_gemm": (C.c_int, [C.POINTER(GemmDesc), _vp]),
+    "toner_gemm_phase_cycles": (C.c_int, [C.c_int, _vp, C.POINTER(C.c_uint64)]),
     "toner_syrk_upper": (C.c_int, [C.POINTER(_vp), _vp, _i64, _i32, _i32, _i32, _i64, _vp, _i32, _f32, _f32, _vp]),
     "toner_unpack_ema": (C.c_int, [_vp, _vp, _i32, _i32, _f32, _f32, _vp]),
     "toner_inv_roots_workspace_bytes": (C.c_size_t, [_i32, _i32]),

@@ -213,7 +213,7 @@ def _product(a_planes, a_inv, group: MatrixGroup, which: str, d, **kw) -> None:
     a = ops.operand(a_planes, seg_z=(0, 0, count))
     b = ops.operand(r_planes, seg_z=(group.first, f.k + group.first, group.first), z_step=group.step)
     ops.gemm(a, b, m=m, n=n, k=n, batch=count, fmt=0, segs=3, d=d, alpha_a=a_inv,
-             alpha_b=r_inv[group.first:], alpha_b_step=group.step, promote=ops.PROMOTE_ACCURATE, **kw)
+             alpha_b=r_inv[group.first:], alpha_b_step=group.step, promote=0, **kw)
 
 
 def muont_group_delta(group: MatrixGroup, grads: Sequence[torch.Tensor], delta: torch.Tensor, scratch: Scratch, *,

@@ -11,6 +11,7 @@
 // l_k is close to 1 they become the Newton values ((p+1)/p, 1/p).
 // The schedule depends only on (n, damping, p), so the iteration count is fixed and stated.
 #include <cmath>
+#include <cstdlib>
 #include <vector>
 
 #include "runtime.cuh"
@@ -57,6 +58,19 @@ static std::vector<NewtonStep> newton_schedule(double l0, int p, int iters, doub
   if (lower_out) *lower_out = l;
   return out;
 }
+
+// k-blocks (64 deep) per tensor-core accumulation chain for the products that update M, given the lower
+// bound of M's spectrum (0 = one chain over the whole product, the fastest kernel).  Truncation costs about
+// 1.2e-7 per k-block on same-sign sums, i.e. up to 1e-5 over a whole product of depth 5632; the damage to the
+// result is that divided by the smallest eigenvalue of M.
+static int chain_length(double lower) {
+  if (lower < 5e-3) return kPromoteAccurate;
+  if (lower < 5e-2) return kPromoteLinear;
+  return 0;
+}
+
+// Products applied to X (and the final squarings) pass their error on linearly: one chain, about 1e-5.
+constexpr int kPromoteX = 0;
 
 static int default_iterations(double l0, int p) {
   // steps until the spectrum is within 3e-4 of 1, plus one Newton step (which squares that distance)
@@ -121,87 +135,72 @@ __global__ void __launch_bounds__(256) damp_kernel(const float* __restrict__ c, 
   }
 }
 
-// x <- x * factor[b] (factor = 1/sqrt(sumsq) when rsqrt_of_sumsq), with max|x| and max|aff_a I + aff_b x|.
-__global__ void __launch_bounds__(256) scale_stats_kernel(float* __restrict__ x, int n, const float* __restrict__ sumsq,
-                                                          float aff_a, float aff_b, unsigned int* __restrict__ maxabs,
-                                                          unsigned int* __restrict__ maxaff) {
-  const int b = blockIdx.y;
-  float* X = x + (long long)b * n * n;
-  const float f = rsqrtf(fmaxf(sumsq[b], 1e-60f));
-  const long long total = (long long)n * n;
-  float m0 = 0.f, m1 = 0.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(i / n), c = (int)(i - (long long)r * n);
-    const float v = X[i] * f;
-    X[i] = v;
-    m0 = fmaxf(m0, fabsf(v));
-    m1 = fmaxf(m1, fabsf(aff_b * v + (r == c ? aff_a : 0.f)));
-  }
+// FP16 hi/lo planes of the two operands the iteration starts from, from A (FP32, damped and normalised):
+//   M_0 = A / ||A||_F  (scaled by s_m)      T_0 = a I - b M_0  (scaled by s_t)      X_1 = T_0
+// planes layout [2][batch][n][n], hi plane first.
+__global__ void __launch_bounds__(256) init_planes_kernel(const float* __restrict__ a32, int n, int batch,
+                                                          const float* __restrict__ sumsq, float a, float b, float s_m,
+                                                          float s_t, __half* __restrict__ m_planes,
+                                                          __half* __restrict__ t_planes, __half* __restrict__ x_planes) {
+  const int bi = blockIdx.y;
+  const long long nn = (long long)n * n;
+  const float4* A = reinterpret_cast<const float4*>(a32 + bi * nn);
+  const float f = rsqrtf(fmaxf(sumsq[bi], 1e-60f));
+  __half* mh = m_planes + bi * nn;
+  __half* ml = m_planes + ((long long)batch + bi) * nn;
+  __half* th = t_planes + bi * nn;
+  __half* tl = t_planes + ((long long)batch + bi) * nn;
+  __half* xh = x_planes + bi * nn;  // X_1 = T_0: a second copy, because T's buffer is rewritten by the first step
+  __half* xl = x_planes + ((long long)batch + bi) * nn;
+  const int n4 = n / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nn / 4; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / n4), c = (int)(i - (long long)r * n4) * 4;
+    const float4 v = A[i];
+    const float m[4] = {v.x * f, v.y * f, v.z * f, v.w * f};
+    __half h[4], l[4], g[4], k[4];
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
-    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, o));
-  }
-  if ((threadIdx.x & 31) == 0) {
-    atomicMax(maxabs + b, __float_as_uint(m0));
-    atomicMax(maxaff + b, __float_as_uint(m1));
-  }
-}
-
-// y = aff_a I + aff_b x (FP32 copy; used for X_1 = T_0)
-__global__ void __launch_bounds__(256) affine_copy_kernel(const float* __restrict__ x, float* __restrict__ y, int n,
-                                                          float aff_a, float aff_b) {
-  const int b = blockIdx.y;
-  const float* X = x + (long long)b * n * n;
-  float* Y = y + (long long)b * n * n;
-  const long long total = (long long)n * n;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(i / n), c = (int)(i - (long long)r * n);
-    Y[i] = aff_b * X[i] + (r == c ? aff_a : 0.f);
+    for (int e = 0; e < 4; ++e) {
+      const float x = m[e] * s_m;
+      h[e] = __float2half_rn(x);
+      l[e] = __float2half_rn(x - __half2float(h[e]));
+      const float t = (((c + e) == r ? a : 0.f) - b * m[e]) * s_t;
+      g[e] = __float2half_rn(t);
+      k[e] = __float2half_rn(t - __half2float(g[e]));
+    }
+    *reinterpret_cast<uint2*>(mh + i * 4) = *reinterpret_cast<uint2*>(h);
+    *reinterpret_cast<uint2*>(ml + i * 4) = *reinterpret_cast<uint2*>(l);
+    *reinterpret_cast<uint2*>(th + i * 4) = *reinterpret_cast<uint2*>(g);
+    *reinterpret_cast<uint2*>(tl + i * 4) = *reinterpret_cast<uint2*>(k);
+    *reinterpret_cast<uint2*>(xh + i * 4) = *reinterpret_cast<uint2*>(g);
+    *reinterpret_cast<uint2*>(xl + i * 4) = *reinterpret_cast<uint2*>(k);
   }
 }
 
-// status[b]: 0 converged, 1 residual max|I - M| above tol, 2 non-finite
-__global__ void __launch_bounds__(256) residual_kernel(const float* __restrict__ m, int n, unsigned int* __restrict__ resid) {
-  const int b = blockIdx.y;
-  const float* M = m + (long long)b * n * n;
-  const long long total = (long long)n * n;
-  float r0 = 0.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(i / n), c = (int)(i - (long long)r * n);
-    const float v = fabsf((r == c ? 1.f : 0.f) - M[i]);
-    r0 = (v == v) ? fmaxf(r0, v) : INFINITY;  // NaN counts as infinite residual
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, o));
-  if ((threadIdx.x & 31) == 0) atomicMax(resid + b, __float_as_uint(r0));
-}
-
-__global__ void finish_kernel(const unsigned int* __restrict__ resid, const float* __restrict__ sumsq_a, float* inv_x,
-                              float* root_scale_lo, float* root_scale_hi, int* status, int k, int p, int q, float tol) {
+// Per statistic: the scale that turns M_0^{-1/p} into A^{-1/p}, and the convergence status from the
+// distance max|I - M| gathered when the last M was produced (0 converged, 1 above tol, 2 non-finite).
+__global__ void finish_kernel(const unsigned int* __restrict__ resid, const float* __restrict__ sumsq_a,
+                              float* root_scale_lo, int* status, int k, int p, float tol) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= k) return;
   const float ub = sqrtf(fmaxf(sumsq_a[b], 1e-60f));
-  const float s_lo = powf(ub, -1.f / p);
-  root_scale_lo[b] = s_lo;
-  root_scale_hi[b] = powf(ub, -(float)q / p);
-  inv_x[b] *= s_lo;  // the last X product applies the inverse operand scales: fold the root's scale in
+  root_scale_lo[b] = powf(ub, -1.f / p);
   const float r = __uint_as_float(resid[b]);
   if (status) status[b] = !isfinite(r) ? 2 : (r > tol ? 1 : 0);
-}
-
-__global__ void mul_vec_kernel(float* a, const float* b, int k) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < k) a[i] *= b[i];
 }
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 static size_t per_statistic_bytes(int n) {
-  // M, X, F (FP32) + five FP16 hi/lo plane pairs (T, M, X, P0, P1) = 8 FP32-sized matrices
+  // A (FP32) + seven FP16 hi/lo plane pairs (T, M x2, X x2, two powers of T) = 8 FP32-sized matrices
   return align_up((size_t)n * n * 4, 256) * 8;
 }
-static size_t small_bytes(int chunk) { return align_up((size_t)chunk * 4, 256) * 16 + align_up(sumsq_scratch_bytes(chunk), 256); }
+static size_t small_bytes(int chunk) { return align_up((size_t)chunk * 4, 256) * 8 + align_up(sumsq_scratch_bytes(chunk), 256); }
+
+// Largest power of two s with s * bound <= 2^14: FP16 planes of s * x then stay a factor four below overflow
+// for |x| <= bound, and elements down to 2^-16 of the bound keep all 22 bits of the hi/lo pair.
+static float plane_scale(double bound) {
+  return (float)std::ldexp(1.0, (int)std::floor(std::log2(16384.0 / bound)));
+}
 
 }  // namespace toner
 
@@ -249,152 +248,184 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
   if (chunk_cap < 1) return fail(kErrWorkspace, "inv_roots: workspace holds less than one statistic");
   const long long nn = (long long)n * n;
   const size_t mat = align_up((size_t)nn * 4, 256);
-  const int ew_blocks = (int)std::min<long long>((nn + 1023) / 1024, 4LL * ctx->num_sms);
+  const int ew_blocks = (int)std::min<long long>((nn / 4 + 255) / 256, 8LL * ctx->num_sms / (k < 8 ? k : 8) + 1);
+
+  // Plane scales from norm bounds known in advance (no pass over the data is needed to find them):
+  // ||M_k|| <= 1, ||T_k|| <= a_k, ||T_k^(2^j)|| <= a_k^(2^j), ||X_k|| <= min(prod_{j<k} a_j, l0^(-1/p)),
+  // ||A^(-1/p)|| <= damping^(-1/p).
+  const float s_m = plane_scale(1.0);
+  const double x_cap = 1.01 * std::pow(l0, -1.0 / p);
+  const double root_bound = 1.01 * std::pow((double)damping, -1.0 / p);
 
   for (int k0 = 0; k0 < k; k0 += (int)chunk_cap) {
     const int kc = (int)std::min<long long>(chunk_cap, k - k0);
     char* w = static_cast<char*>(workspace);
-    float* M = reinterpret_cast<float*>(w); w += mat * kc;
-    float* X = reinterpret_cast<float*>(w); w += mat * kc;
-    float* F = reinterpret_cast<float*>(w); w += mat * kc;
-    __half* Tp = reinterpret_cast<__half*>(w); w += mat * kc;
-    __half* Mp = reinterpret_cast<__half*>(w); w += mat * kc;
-    __half* Xp = reinterpret_cast<__half*>(w); w += mat * kc;
-    __half* P0 = reinterpret_cast<__half*>(w); w += mat * kc;
-    __half* P1 = reinterpret_cast<__half*>(w); w += mat * kc;
+    float* A32 = reinterpret_cast<float*>(w); w += mat * kc;
+    __half* Tb[2];
+    __half* Mb[2];
+    __half* Xb[2];
+    __half* Pb[2];
+    Tb[0] = reinterpret_cast<__half*>(w); w += mat * kc;
+    Mb[0] = reinterpret_cast<__half*>(w); w += mat * kc;
+    Mb[1] = reinterpret_cast<__half*>(w); w += mat * kc;
+    Xb[0] = reinterpret_cast<__half*>(w); w += mat * kc;
+    Xb[1] = reinterpret_cast<__half*>(w); w += mat * kc;
+    Pb[0] = reinterpret_cast<__half*>(w); w += mat * kc;
+    Pb[1] = reinterpret_cast<__half*>(w); w += mat * kc;
+    Tb[1] = Pb[0];  // p == 1 has no powers of T to store: the next T is written beside the current one
     const size_t sm = align_up((size_t)kc * 4, 256);
     auto small = [&](int i) { return reinterpret_cast<float*>(w + sm * i); };
     float* trace = small(0);
     float* sumsq_a = small(1);
-    unsigned int* max_m = reinterpret_cast<unsigned int*>(small(2));
-    unsigned int* max_t = reinterpret_cast<unsigned int*>(small(3));
-    unsigned int* max_x = reinterpret_cast<unsigned int*>(small(4));
-    unsigned int* max_f = reinterpret_cast<unsigned int*>(small(5));
-    unsigned int* resid = reinterpret_cast<unsigned int*>(small(6));
-    float* inv_t = small(7);
-    float* inv_m = small(8);
-    float* inv_x = small(9);
-    float* inv_p0 = small(10);
-    float* inv_p1 = small(11);
-    float* scale_lo = small(12);
-    float* scale_hi = small(13);
-    float* fro_tmp = small(14);
-    float* partials = small(16);
-    TONER_CUDA(cudaMemsetAsync(w, 0, sm * 16, stream));
+    unsigned int* resid = reinterpret_cast<unsigned int*>(small(2));
+    float* scale_lo = small(3);
+    float* fro_tmp = small(4);
+    float* partials = small(8);
+    TONER_CUDA(cudaMemsetAsync(w, 0, sm * 8, stream));
 
     const float* C = ema + (long long)k0 * nn;
     const int t32 = (n + 31) / 32;
     trace_kernel<<<kc, 256, 0, stream>>>(C, n, trace);
     count_launch();
-    damp_kernel<<<dim3(t32, t32, kc), 256, 0, stream>>>(C, M, n, damping, trace);
+    damp_kernel<<<dim3(t32, t32, kc), 256, 0, stream>>>(C, A32, n, damping, trace);
     count_launch();
     {
-      int rc0 = sumsq_det(M, kc, n, n, n, nn, partials, sumsq_a, stream);
+      int rc0 = sumsq_det(A32, kc, n, n, n, nn, partials, sumsq_a, stream);
       if (rc0) return rc0;
     }
-    scale_stats_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(M, n, sumsq_a, (float)sched[0].a, (float)-sched[0].b, max_m, max_t);
+    float s_t = plane_scale(sched[0].a);
+    init_planes_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(A32, n, kc, sumsq_a, (float)sched[0].a, (float)sched[0].b, s_m,
+                                                                s_t, Mb[0], Tb[0], Xb[1]);
     count_launch();
     TONER_CUDA(cudaGetLastError());
 
-    auto planes_op = [&](const __half* planes, int hi_lo_first) {
-      toner_operand op = {};
-      op.base = planes;
-      op.rows = n; op.cols = n; op.ld = n; op.z_stride = nn; op.nz = 2 * kc; op.z_step = 1;
-      return op;
+    // D = (A planes) * (B planes)^T / (sa * sb): symmetric result, FP32-accurate; outputs as requested
+    struct Out {
+      float* d = nullptr;           // FP32 result
+      const float* alpha_a = nullptr;
+      __half* s0 = nullptr; float s0_scale = 0.f;
+      __half* s1 = nullptr; float s1_scale = 0.f, s1_a = 0.f, s1_b = 0.f;
+      unsigned int* maxres = nullptr;
     };
-    // D = (A planes) * (B planes)^T, symmetric result, FP32-accurate
-    auto sym_product = [&](const __half* ap, const float* ainv, const __half* bp, const float* binv, float* d,
-                           unsigned int* maxabs, unsigned int* maxaff, float aff_a, float aff_b, float* sumsq) -> int {
+    auto sym_product = [&](const __half* ap, float sa, const __half* bp, float sb, const Out& o, int promote) -> int {
       toner_gemm_desc g = {};
-      g.a = planes_op(ap, 0);
-      g.b = planes_op(bp, 0);
+      toner_operand op = {};
+      op.rows = n; op.cols = n; op.ld = n; op.z_stride = nn; op.nz = 2 * kc; op.z_step = 1;
+      g.a = op; g.a.base = ap;
+      g.b = op; g.b.base = bp;
       g.a.seg_z[0] = 0; g.a.seg_z[1] = 0; g.a.seg_z[2] = kc;   // Ah Ah Al
       g.b.seg_z[0] = 0; g.b.seg_z[1] = kc; g.b.seg_z[2] = 0;   // Bh Bl Bh
       g.m = n; g.n = n; g.k = n; g.batch = kc; g.segs = 3; g.fmt = 0;
       g.tri = 1; g.mirror = 1;
-      g.alpha = 1.f; g.alpha_a = ainv; g.alpha_b = binv;
-      g.d = d; g.ldd = n; g.d_bs = nn;
-      g.maxabs = maxabs; g.maxaff = maxaff; g.aff_a = aff_a; g.aff_b = aff_b; g.sumsq = sumsq;
-      g.promote = kPromoteAccurate;
+      g.alpha = (float)(1.0 / ((double)sa * (double)sb));
+      g.alpha_a = o.alpha_a;
+      g.d = o.d; g.ldd = n; g.d_bs = nn;
+      g.split0 = o.s0; g.split0_scale = o.s0_scale;
+      g.split1 = o.s1; g.split1_scale = o.s1_scale; g.split1_aff_a = o.s1_a; g.split1_aff_b = o.s1_b;
+      g.split_ld = n; g.split_bs = nn; g.split_plane = (long long)kc * nn;
+      g.maxres = o.maxres;
+      g.promote = promote;
       return launch_gemm(g, stream);
     };
-    auto zero = [&](void* ptr) { return cudaMemsetAsync(ptr, 0, sm, stream); };
     int rc = 0;
+    const __half* Xcur = Xb[1];  // X_1 = T_0
+    float s_x = s_t;
+    double x_bound = sched[0].a;
+    int xi = 0, mi = 0, ti = 0;
 
     for (int it = 0; it < iters; ++it) {
-      const float a = (float)sched[it].a, b = (float)sched[it].b;
       const bool last = (it == iters - 1);
-      // T_k planes from M_k (max|T_k| was gathered when M_k was produced)
-      rc = split16(M, nullptr, kc, n, n, n, nn, a, -b, max_t, nullptr, Tp, inv_t, stream);
-      if (rc) return rc;
-      if (it == 0) {
-        affine_copy_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(M, X, n, a, -b);  // X_1 = T_0
-        TONER_CUDA(cudaGetLastError());
-        count_launch();
-        TONER_CUDA(cudaMemcpyAsync(max_x, max_t, sm, cudaMemcpyDeviceToDevice, stream));
-      } else {
-        rc = split16(X, nullptr, kc, n, n, n, nn, 0.f, 1.f, max_x, nullptr, Xp, inv_x, stream);
-        if (rc) return rc;
+      const __half* Tcur = Tb[ti];
+      if (it > 0) {
+        x_bound = std::min(x_bound * sched[it].a, x_cap);
         if (last) {
-          // fold ||A||_F^{-1/p} into the product, take the residual of M before it stops being updated
-          TONER_CUDA(zero(resid));
-          residual_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(M, n, resid);
-          count_launch();
-          finish_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(resid, sumsq_a, inv_x, scale_lo, scale_hi,
-                                                            status ? status + k0 : nullptr, kc, p, q, 0.05f);
+          // fold ||A||_F^{-1/p} into the product; the distance of M from I was gathered when M was produced
+          finish_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(resid, sumsq_a, scale_lo, status ? status + k0 : nullptr, kc, p,
+                                                            0.05f);
           count_launch();
           TONER_CUDA(cudaGetLastError());
-          TONER_CUDA(zero(max_x));
-          rc = sym_product(Xp, inv_x, Tp, inv_t, root_lo + (long long)k0 * nn, max_x, nullptr, 0.f, 1.f, nullptr);
+          Out o;
+          o.d = root_lo + (long long)k0 * nn;
+          o.alpha_a = scale_lo;
+          if (q > 1) {
+            o.s0 = Xb[xi];
+            o.s0_scale = plane_scale(root_bound);
+          }
+          rc = sym_product(Xcur, s_x, Tcur, s_t, o, kPromoteX);
           if (rc) return rc;
           rc = sumsq_det(root_lo + (long long)k0 * nn, kc, n, n, n, nn, partials, fro_tmp, stream);
           if (rc) return rc;
+          Xcur = Xb[xi];
+          s_x = plane_scale(root_bound);
           break;
         }
-        TONER_CUDA(zero(max_x));
-        rc = sym_product(Xp, inv_x, Tp, inv_t, X, max_x, nullptr, 0.f, 1.f, nullptr);
+        Out o;
+        o.s0 = Xb[xi];
+        o.s0_scale = plane_scale(x_bound);
+        rc = sym_product(Xcur, s_x, Tcur, s_t, o, kPromoteX);
         if (rc) return rc;
+        Xcur = Xb[xi];
+        s_x = o.s0_scale;
+        xi ^= 1;
       }
-      // M_{k+1} = T^p M_k
-      rc = split16(M, nullptr, kc, n, n, n, nn, 0.f, 1.f, max_m, nullptr, Mp, inv_m, stream);
-      if (rc) return rc;
-      const __half* pw = Tp;
-      const float* pw_inv = inv_t;
+      // M_{k+1} = T^p M_k.  The tensor core adds into its accumulator by truncation, a one-sided error that
+      // grows with the length of the accumulation chain and, unlike rounding noise, does not average out over
+      // the sum; a relative error e of M matters as e / (smallest eigenvalue of M), so the chains are kept
+      // short while the spectrum's lower bound is small and lengthened as it approaches 1.
+      const int chain = chain_length(sched[it].lower);
+      const __half* pw = Tcur;
+      float s_pw = s_t;
+      double pw_bound = sched[it].a;
       for (int j = 0; j < log2p; ++j) {
-        TONER_CUDA(zero(max_f));
-        rc = sym_product(pw, pw_inv, pw, pw_inv, F, max_f, nullptr, 0.f, 1.f, nullptr);
+        pw_bound *= pw_bound;
+        Out o;
+        o.s0 = Pb[j & 1];
+        o.s0_scale = plane_scale(pw_bound);
+        rc = sym_product(pw, s_pw, pw, s_pw, o, chain);
         if (rc) return rc;
-        __half* dst = (j & 1) ? P1 : P0;
-        float* dst_inv = (j & 1) ? inv_p1 : inv_p0;
-        rc = split16(F, nullptr, kc, n, n, n, nn, 0.f, 1.f, max_f, nullptr, dst, dst_inv, stream);
-        if (rc) return rc;
-        pw = dst;
-        pw_inv = dst_inv;
+        pw = o.s0;
+        s_pw = o.s0_scale;
       }
-      TONER_CUDA(zero(max_m));
-      TONER_CUDA(zero(max_t));
-      const float na = (float)sched[it + 1].a, nb = (float)sched[it + 1].b;
-      rc = sym_product(pw, pw_inv, Mp, inv_m, M, max_m, max_t, na, -nb, nullptr);
-      if (rc) return rc;
+      {
+        const float na = (float)sched[it + 1].a, nb = (float)sched[it + 1].b;
+        const int tn = (log2p == 0) ? (ti ^ 1) : ti;  // with p == 1 the product reads T itself
+        Out o;
+        o.s0 = Mb[mi ^ 1];
+        o.s0_scale = s_m;
+        o.s1 = Tb[tn];
+        o.s1_scale = plane_scale(na);
+        o.s1_a = na;
+        o.s1_b = -nb;
+        if (it == iters - 2) o.maxres = resid;
+        rc = sym_product(pw, s_pw, Mb[mi], s_m, o, chain);
+        if (rc) return rc;
+        mi ^= 1;
+        ti = tn;
+        s_t = o.s1_scale;
+      }
     }
     if (fro2_lo) TONER_CUDA(cudaMemcpyAsync(fro2_lo + k0, fro_tmp, sizeof(float) * kc, cudaMemcpyDeviceToDevice, stream));
 
     if (q > 1) {
-      // A^{-q/p} by repeated squaring of A^{-1/p}
-      const float* src = root_lo + (long long)k0 * nn;
+      // A^{-q/p} by repeated squaring of A^{-1/p} (its planes came with the last product)
       int have = 1;
+      double bound = root_bound;
+      int pi = 0;
       while (have < q) {
-        __half* pl = (have == 1) ? Xp : P0;
-        float* pl_inv = (have == 1) ? inv_x : inv_p0;
-        const unsigned int* mx = (have == 1) ? max_x : max_f;
-        rc = split16(src, nullptr, kc, n, n, n, nn, 0.f, 1.f, mx, nullptr, pl, pl_inv, stream);
-        if (rc) return rc;
         have *= 2;
-        float* dst = (have == q) ? root_hi + (long long)k0 * nn : F;
-        TONER_CUDA(zero(max_f));
-        rc = sym_product(pl, pl_inv, pl, pl_inv, dst, max_f, nullptr, 0.f, 1.f, nullptr);
+        bound *= bound;
+        Out o;
+        if (have == q) {
+          o.d = root_hi + (long long)k0 * nn;
+        } else {
+          o.s0 = Pb[pi];
+          o.s0_scale = plane_scale(bound);
+        }
+        rc = sym_product(Xcur, s_x, Xcur, s_x, o, kPromoteX);
         if (rc) return rc;
-        src = dst;
+        Xcur = Pb[pi];
+        s_x = o.s0_scale;
+        pi ^= 1;
       }
     }
   }

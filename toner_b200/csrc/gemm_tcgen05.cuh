@@ -70,7 +70,16 @@ struct GemmParams {
   unsigned int* maxabs;   // per batch: max |d| as FP32 bits
   unsigned int* maxaff;   // per batch: max |aff_a * [r==c] + aff_b * d| as FP32 bits
   float aff_a, aff_b;
+  unsigned int* maxres;   // per batch: max |[r==c] - d| as FP32 bits (distance of the result from the identity)
+  // optional FP16 hi/lo operand planes of the result, ready to feed the next split-precision product:
+  //   S0: planes of s0_scale * d            S1: planes of s1_scale * (s1_aff_a * [r==c] + s1_aff_b * d)
+  // hi plane at S + b * s_bs + r * s_ld + c, lo plane s_plane elements further
+  __half* S0;
+  __half* S1;
+  long long s_ld, s_bs, s_plane;
+  float s0_scale, s1_scale, s1_aff_a, s1_aff_b;
   int* status;  // set non-zero if a bounded wait ran out
+  unsigned long long* prof;  // optional: eight cycle counters summed over CTAs (see toner_gemm_phase_cycles)
 };
 
 __host__ __device__ inline long long packed_off(long long r, long long c, long long n) {
@@ -140,6 +149,8 @@ struct EpilogueTile {
   const float* Cb;
   float* Db;
   uint16_t* Hb;  // 16-bit copy of the result (FP16 or BF16 bits)
+  __half* S0b;
+  __half* S1b;
   float alpha, beta;
   bool use_c;
 };
@@ -162,6 +173,23 @@ __device__ __forceinline__ uint2 pack4_16(float a, float b, float c, float d, in
   return u;
 }
 
+// FP16 hi/lo split of four consecutive values: hi = rn(x), lo = rn(x - hi).
+__device__ __forceinline__ void store_split4(__half* hi, long long plane, float x0, float x1, float x2, float x3) {
+  const __half2 h0 = __floats2half2_rn(x0, x1), h1 = __floats2half2_rn(x2, x3);
+  const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+  const __half2 l0 = __floats2half2_rn(x0 - f0.x, x1 - f0.y), l1 = __floats2half2_rn(x2 - f1.x, x3 - f1.y);
+  uint2 u, w;
+  u.x = *reinterpret_cast<const uint32_t*>(&h0); u.y = *reinterpret_cast<const uint32_t*>(&h1);
+  w.x = *reinterpret_cast<const uint32_t*>(&l0); w.y = *reinterpret_cast<const uint32_t*>(&l1);
+  *reinterpret_cast<uint2*>(hi) = u;
+  *reinterpret_cast<uint2*>(hi + plane) = w;
+}
+__device__ __forceinline__ void store_split1(__half* hi, long long plane, float x) {
+  const __half h = __float2half_rn(x);
+  hi[0] = h;
+  hi[plane] = __float2half_rn(x - __half2float(h));
+}
+
 // The epilogue writes the result in 32 x 32 blocks staged in shared memory (thread t's row of the
 // accumulator at stage[t * kEpiStride ...]), so that the loops below are rolled -- the code stays a few
 // KB and resident in the instruction cache -- and every global access of a warp is made of contiguous runs.
@@ -173,10 +201,11 @@ __device__ __forceinline__ uint2 pack4_16(float a, float b, float c, float d, in
 // exchanged.  The values read from C are fetched four row-groups at a time before any store, so that the
 // loads overlap (C and D may be the same matrix; every element is read before it is written).
 __device__ __forceinline__ void epilogue_block_vec(const GemmParams& p, const EpilogueTile& e, float* stage, int row_first,
-                                                   int c0, int lane, float& ssq, float& mabs) {
+                                                   int c0, int lane, float& ssq, float& mabs, float& maff, float& mres) {
   const int q = lane & 7, sub = lane >> 3;
   const int col = c0 + 4 * q;
   const bool mirror = p.tri && p.mirror;
+  const float s0 = p.s0_scale, s1 = p.s1_scale * p.s1_aff_b;  // no diagonal element in an interior block
   float s = 0.f, m = 0.f;
 #pragma unroll 1
   for (int half = 0; half < 2; ++half) {
@@ -200,6 +229,8 @@ __device__ __forceinline__ void epilogue_block_vec(const GemmParams& p, const Ep
       }
       if (e.Db) *reinterpret_cast<float4*>(e.Db + (long long)row * p.ldd + col) = make_float4(v0, v1, v2, v3);
       if (e.Hb) *reinterpret_cast<uint2*>(e.Hb + (long long)row * p.ld16 + col) = pack4_16(v0, v1, v2, v3, p.d16_fmt);
+      if (e.S0b) store_split4(e.S0b + (long long)row * p.s_ld + col, p.s_plane, s0 * v0, s0 * v1, s0 * v2, s0 * v3);
+      if (e.S1b) store_split4(e.S1b + (long long)row * p.s_ld + col, p.s_plane, s1 * v0, s1 * v1, s1 * v2, s1 * v3);
       if (mirror) {
         src[0] = v0; src[1] = v1; src[2] = v2; src[3] = v3;
       }
@@ -209,6 +240,8 @@ __device__ __forceinline__ void epilogue_block_vec(const GemmParams& p, const Ep
   }
   ssq += p.tri ? 2.f * s : s;
   mabs = fmaxf(mabs, m);
+  maff = fmaxf(maff, fabsf(p.aff_b) * m);  // off the diagonal the affine map is a plain scaling
+  mres = fmaxf(mres, m);                   // and the distance from the identity is |d|
   if (mirror) {
     __syncwarp();
     const int tcol = row_first + 4 * q;  // source rows 4q .. 4q+3 become four consecutive target columns
@@ -220,6 +253,8 @@ __device__ __forceinline__ void epilogue_block_vec(const GemmParams& p, const Ep
       const long long trow = c0 + j;
       if (e.Db) *reinterpret_cast<float4*>(e.Db + trow * p.ldd + tcol) = make_float4(v0, v1, v2, v3);
       if (e.Hb) *reinterpret_cast<uint2*>(e.Hb + trow * p.ld16 + tcol) = pack4_16(v0, v1, v2, v3, p.d16_fmt);
+      if (e.S0b) store_split4(e.S0b + trow * p.s_ld + tcol, p.s_plane, s0 * v0, s0 * v1, s0 * v2, s0 * v3);
+      if (e.S1b) store_split4(e.S1b + trow * p.s_ld + tcol, p.s_plane, s1 * v0, s1 * v1, s1 * v2, s1 * v3);
     }
   }
   __syncwarp();
@@ -229,7 +264,7 @@ __device__ __forceinline__ void epilogue_block_vec(const GemmParams& p, const Ep
 // element per lane with full masking, lane = column, so rows -- also rows of a packed triangle -- are
 // still written as contiguous runs; the mirrored half with lane = source row.
 __device__ __forceinline__ void epilogue_block_scalar(const GemmParams& p, const EpilogueTile& e, float* stage, int row_first,
-                                                      int c0, int lane, float& ssq, float& mabs, float& maff) {
+                                                      int c0, int lane, float& ssq, float& mabs, float& maff, float& mres) {
   const int col = c0 + lane;
   const bool col_ok = col < p.N;
   const bool mirror = p.tri && p.mirror;
@@ -245,6 +280,10 @@ __device__ __forceinline__ void epilogue_block_scalar(const GemmParams& p, const
       if (e.use_c) v = fmaf(e.beta, e.Cb[co], v);
       if (e.Db) e.Db[dof] = v;
       if (e.Hb) e.Hb[(long long)row * p.ld16 + col] = to_bits16(v, p.d16_fmt);
+      const float dg = (col == row) ? 1.f : 0.f;
+      if (e.S0b) store_split1(e.S0b + (long long)row * p.s_ld + col, p.s_plane, p.s0_scale * v);
+      if (e.S1b) store_split1(e.S1b + (long long)row * p.s_ld + col, p.s_plane, p.s1_scale * fmaf(p.s1_aff_b, v, p.s1_aff_a * dg));
+      mres = fmaxf(mres, fabsf(dg - v));
       const float w = (p.tri && col > row) ? 2.f : 1.f;
       ssq = fmaf(w * v, v, ssq);
       mabs = fmaxf(mabs, fabsf(v));
@@ -264,6 +303,8 @@ __device__ __forceinline__ void epilogue_block_scalar(const GemmParams& p, const
           const float v = stage[lane * kEpiStride + j];
           if (e.Db) e.Db[(long long)c * p.ldd + row] = v;
           if (e.Hb) e.Hb[(long long)c * p.ld16 + row] = to_bits16(v, p.d16_fmt);
+          if (e.S0b) store_split1(e.S0b + (long long)c * p.s_ld + row, p.s_plane, p.s0_scale * v);
+          if (e.S1b) store_split1(e.S1b + (long long)c * p.s_ld + row, p.s_plane, p.s1_scale * p.s1_aff_b * v);
         }
       }
     }
@@ -301,10 +342,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
   const int chunks_seg0 = p.promote > 0 ? (kb_per_seg + p.promote - 1) / p.promote : 1;
   const int chunks_rest = (p.promote > 0 && p.promote_all) ? chunks_seg0 : 1;
   const int chunks_per_tile = p.promote > 0 ? chunks_seg0 + (p.segs - 1) * chunks_rest : 1;
-  auto chunk_range = [&](int ch, int& kb_begin, int& kb_end) {
+  // Order of work inside a tile.  When only the first segment is chained, the later segments come FIRST, one
+  // long chain each: while the epilogue warps are still writing the previous tile they cannot sum chains, and
+  // two long chains give them that time; the short chains of the first segment follow.
+  const bool rest_first = p.promote > 0 && !p.promote_all && p.segs > 1;
+  auto chunk_range = [&](int ch, int& kb_begin, int& kb_end) {  // k-block indices in processing order
     if (p.promote <= 0) {
       kb_begin = 0;
       kb_end = num_kb;
+      return;
+    }
+    if (rest_first) {
+      const int rest = p.segs - 1;
+      if (ch < rest) {
+        kb_begin = ch * kb_per_seg;
+        kb_end = kb_begin + kb_per_seg;
+      } else {
+        kb_begin = rest * kb_per_seg + (ch - rest) * p.promote;
+        kb_end = min(kb_begin + p.promote, num_kb);
+      }
       return;
     }
     int seg = 0, c = ch;
@@ -345,6 +401,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long prof_wait = 0;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int b, tm, tn;
         tile_coord(p, BN, t, tiles_per_batch, tiles_n, b, tm, tn);
@@ -353,11 +410,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         ptx::fence_tensormap_acquire(amap);
         ptx::fence_tensormap_acquire(bmap);
         const int m0 = tm * kBM, n0 = tn * BN;
-        for (int seg = 0; seg < p.segs && ok; ++seg) {
+        for (int si = 0; si < p.segs && ok; ++si) {
+          const int seg = rest_first ? (si + 1 == p.segs ? 0 : si + 1) : si;
           const int za = b * p.a_z_stride + p.a_seg_z[seg];
           const int zb = b * p.b_z_stride + p.b_seg_z[seg];
           for (int k0 = 0; k0 < p.K; k0 += kBK) {
-            if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, kWaitCycles) || *abort_flag) {
+            const long long w0 = p.prof ? clock64() : 0;
+            const bool got = ptx::mbar_wait(empty_bar(stage), phase ^ 1u, kWaitCycles);
+            if (p.prof) prof_wait += clock64() - w0;
+            if (!got || *abort_flag) {
               report(p.status, kTimeoutProducer);
               *abort_flag = 1;
               ok = false;
@@ -385,6 +446,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
           }
         }
       }
+      if (p.prof) atomicAdd(p.prof + 3, (unsigned long long)prof_wait);
       if (!ok) {
         // give copies already in flight time to land before the CTA gives its shared memory back
         for (int s = 0; s < S::kStages; ++s) ptx::mbar_wait(full_bar(s), 0, 2000000LL);
@@ -403,12 +465,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
       uint32_t phase = 0;
       uint32_t gchunk = 0;  // accumulator hand-offs so far; buffer = gchunk & 1
       bool ok = true;
+      long long prof_acc = 0, prof_ops = 0;
+      const long long prof_t0 = p.prof ? clock64() : 0;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         for (int ch = 0; ch < chunks_per_tile && ok; ++ch, ++gchunk) {
           int kb_begin, kb_end;
           chunk_range(ch, kb_begin, kb_end);
           const int buf = gchunk & 1u;
-          if (!ptx::mbar_wait(tempty_bar(buf), ((gchunk >> 1) & 1u) ^ 1u, kWaitCycles) || *abort_flag) {
+          const long long w0 = p.prof ? clock64() : 0;
+          const bool got_acc = ptx::mbar_wait(tempty_bar(buf), ((gchunk >> 1) & 1u) ^ 1u, kWaitCycles);
+          if (p.prof) prof_acc += clock64() - w0;
+          if (!got_acc || *abort_flag) {
             report(p.status, kTimeoutMma);
             *abort_flag = 1;
             ok = false;
@@ -417,7 +484,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
           ptx::tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
           for (int kb = kb_begin; kb < kb_end; ++kb) {
-            if (!ptx::mbar_wait(full_bar(stage), phase, kWaitCycles) || *abort_flag) {
+            const long long w1 = p.prof ? clock64() : 0;
+            const bool got_ops = ptx::mbar_wait(full_bar(stage), phase, kWaitCycles);
+            if (p.prof) prof_ops += clock64() - w1;
+            if (!got_ops || *abort_flag) {
               report(p.status, kTimeoutMma);
               *abort_flag = 1;
               ok = false;
@@ -441,6 +511,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
           if (ok) ptx::mma_commit(tfull_bar(buf));  // this chain's partial sum is complete
         }
       }
+      if (p.prof) {
+        atomicAdd(p.prof + 0, (unsigned long long)(clock64() - prof_t0));
+        atomicAdd(p.prof + 1, (unsigned long long)prof_acc);
+        atomicAdd(p.prof + 2, (unsigned long long)prof_ops);
+        atomicAdd(p.prof + 7, 1ull);
+      }
     }
   }
   } else {
@@ -457,6 +533,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
     float racc[kChained ? NCH * 32 : 1];
     uint32_t gchunk = 0;
     bool alive = true;
+    long long prof_wait = 0, prof_out = 0, prof_sum = 0;
     for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
       int b, tm, tn;
       tile_coord(p, BN, t, tiles_per_batch, tiles_n, b, tm, tn);
@@ -466,6 +543,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
       // 32-column blocks this warp never needs: beyond N, or wholly below the diagonal (warp-uniform)
       auto needed = [&](int c0) { return (c0 < p.N) && !(p.tri && c0 + 31 < row_first); };
       auto wait_chain = [&](int buf) {
+        const long long w0 = p.prof ? clock64() : 0;
         // every lane observes the barrier itself, so each one is ordered after the MMAs' TMEM writes
         const int waited = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), (gchunk >> 1) & 1u, kWaitCycles) ? 1 : 0);
         if (!waited || *abort_flag) {
@@ -476,6 +554,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
           return false;
         }
         ptx::tc_fence_after();
+        if (p.prof) prof_wait += clock64() - w0;
         return true;
       };
       auto release = [&](int buf) {  // buffer drained: hand it back to the MMA warp
@@ -496,23 +575,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
             alive = false;
             break;
           }
+          const long long a0 = p.prof ? clock64() : 0;
           const uint32_t taddr = tmem_of(buf);
-          // Software pipeline over the warp's blocks: the load of block cc+1 is in flight while block cc is added.
-          uint32_t s0[32], s1[32];
-          if (needed(col_first)) ptx::tmem_ld32(taddr, s0);
+          // Software pipeline in steps of 16 columns: the next load is in flight while the current one is added.
+          // (Blocks wholly below the diagonal are loaded and added too: their sums are simply never written.)
+          uint32_t s0[16], s1[16];
+          ptx::tmem_ld16(taddr, s0);
           ptx::tmem_ld_wait();
 #pragma unroll
-          for (int cc = 0; cc < NCH; ++cc) {
-            uint32_t* cur = (cc & 1) ? s1 : s0;
-            uint32_t* nxt = (cc & 1) ? s0 : s1;
-            if (cc + 1 < NCH && needed(col_first + (cc + 1) * 32)) ptx::tmem_ld32(taddr + (uint32_t)((cc + 1) * 32), nxt);
-            if (needed(col_first + cc * 32)) {
+          for (int h = 0; h < NCH * 2; ++h) {
+            uint32_t* cur = (h & 1) ? s1 : s0;
+            uint32_t* nxt = (h & 1) ? s0 : s1;
+            if (h + 1 < NCH * 2) ptx::tmem_ld16(taddr + (uint32_t)((h + 1) * 16), nxt);
 #pragma unroll
-              for (int j = 0; j < 32; ++j) racc[cc * 32 + j] += __uint_as_float(cur[j]);
-            }
-            if (cc + 1 < NCH) ptx::tmem_ld_wait();
+            for (int j = 0; j < 16; ++j) racc[h * 16 + j] += __uint_as_float(cur[j]);
+            if (h + 1 < NCH * 2) ptx::tmem_ld_wait();
           }
           release(buf);
+          if (p.prof) prof_sum += clock64() - a0;
         }
         if (!alive) break;
       } else if (!wait_chain(gchunk & 1u)) {
@@ -521,6 +601,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
       }
 
       // ---- write the tile: one rolled loop over the warp's 32 x 32 blocks, staged through shared memory
+      const long long o0 = p.prof ? clock64() : 0;
       EpilogueTile e;
       e.alpha = p.alpha;
       e.beta = p.beta;
@@ -531,7 +612,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
       e.Cb = p.C ? p.C + (long long)b * p.c_bs : nullptr;
       e.Db = p.D ? p.D + (long long)b * p.d_bs : nullptr;
       e.Hb = p.D16 ? reinterpret_cast<uint16_t*>(p.D16) + (long long)b * p.d16_bs : nullptr;
-      float ssq = 0.f, mabs = 0.f, maff = 0.f;
+      e.S0b = p.S0 ? p.S0 + (long long)b * p.s_bs : nullptr;
+      e.S1b = p.S1 ? p.S1 + (long long)b * p.s_bs : nullptr;
+      float ssq = 0.f, mabs = 0.f, maff = 0.f, mres = 0.f;
       const bool rows_inside = row_first + 32 <= p.M;
       const uint32_t taddr = tmem_of(gchunk & 1u);
       float* const mine = stage + lane * kEpiStride;
@@ -572,31 +655,38 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         __syncwarp();
         // warp-uniform choice: interior blocks take the vector path
         const bool holds_diag = (c0 <= row_first + 31) && (c0 + 31 >= row_first);
-        if (rows_inside && (c0 + 32 <= p.N) && p.vec_ok && !(holds_diag && (p.tri || p.maxaff))) {
-          epilogue_block_vec(p, e, stage, row_first, c0, lane, ssq, mabs);
+        if (rows_inside && (c0 + 32 <= p.N) && p.vec_ok && !(holds_diag && (p.tri || p.maxaff || p.maxres || p.S1))) {
+          epilogue_block_vec(p, e, stage, row_first, c0, lane, ssq, mabs, maff, mres);
         } else {
-          epilogue_block_scalar(p, e, stage, row_first, c0, lane, ssq, mabs, maff);
+          epilogue_block_scalar(p, e, stage, row_first, c0, lane, ssq, mabs, maff, mres);
         }
       }
       if (!chained) {
         release(gchunk & 1u);
         ++gchunk;
       }
-      maff = fmaxf(maff, fabsf(p.aff_b) * mabs);  // off the diagonal the affine map is a plain scaling
+      if (p.prof) prof_out += clock64() - o0;
 
-      if (p.sumsq || p.maxabs || p.maxaff) {
+      if (p.sumsq || p.maxabs || p.maxaff || p.maxres) {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
           ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
           mabs = fmaxf(mabs, __shfl_xor_sync(0xffffffffu, mabs, o));
           maff = fmaxf(maff, __shfl_xor_sync(0xffffffffu, maff, o));
+          mres = fmaxf(mres, __shfl_xor_sync(0xffffffffu, mres, o));
         }
         if (lane == 0) {
           if (p.sumsq) atomicAdd(p.sumsq + b, ssq);  // order of these additions is not fixed
           if (p.maxabs) atomicMax(p.maxabs + b, __float_as_uint(mabs));
           if (p.maxaff) atomicMax(p.maxaff + b, __float_as_uint(maff));
+          if (p.maxres) atomicMax(p.maxres + b, __float_as_uint(mres));
         }
       }
+    }
+    if (p.prof && warp == 4 && lane == 0) {
+      atomicAdd(p.prof + 4, (unsigned long long)prof_wait);
+      atomicAdd(p.prof + 5, (unsigned long long)prof_out);
+      atomicAdd(p.prof + 6, (unsigned long long)prof_sum);
     }
   }
 

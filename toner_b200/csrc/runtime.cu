@@ -141,7 +141,8 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
   if (d.segs < 1 || d.segs > kMaxSegs) return fail(kErrArg, "gemm: segs must be 1..3");
   if (d.tri && d.m != d.n) return fail(kErrArg, "gemm: a symmetric result needs m == n");
   if (d.packed && (!d.tri || d.mirror || d.d16)) return fail(kErrArg, "gemm: packed output is upper-triangle FP32 only");
-  if (!d.d && !d.d16) return fail(kErrArg, "gemm: no output");
+  if (!d.d && !d.d16 && !d.split0 && !d.split1) return fail(kErrArg, "gemm: no output");
+  if (d.packed && (d.split0 || d.split1)) return fail(kErrArg, "gemm: operand planes cannot be packed");
   if (d.fmt != 0 && d.fmt != 1) return fail(kErrArg, "gemm: fmt must be 0 (FP16) or 1 (BF16)");
 
   int bn = d.tile_n;
@@ -186,9 +187,20 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
   p.vec_ok = !d.packed && (!d.c || (d.ldc % 4 == 0 && d.c_bs % 4 == 0 && al16(d.c))) &&
              (!d.d || (d.ldd % 4 == 0 && d.d_bs % 4 == 0 && al16(d.d))) &&
              (!d.d16 || (d.ld16 % 4 == 0 && d.d16_bs % 4 == 0 && (reinterpret_cast<uintptr_t>(d.d16) & 7u) == 0));
+  if (d.split0 || d.split1) {
+    const bool ok = d.split_ld % 4 == 0 && d.split_bs % 4 == 0 && d.split_plane % 4 == 0 &&
+                    (!d.split0 || (reinterpret_cast<uintptr_t>(d.split0) & 7u) == 0) &&
+                    (!d.split1 || (reinterpret_cast<uintptr_t>(d.split1) & 7u) == 0);
+    p.vec_ok = p.vec_ok && ok;
+  }
+  p.S0 = static_cast<__half*>(d.split0); p.S1 = static_cast<__half*>(d.split1);
+  p.s_ld = d.split_ld; p.s_bs = d.split_bs; p.s_plane = d.split_plane;
+  p.s0_scale = d.split0_scale; p.s1_scale = d.split1_scale; p.s1_aff_a = d.split1_aff_a; p.s1_aff_b = d.split1_aff_b;
+  p.maxres = d.maxres;
   p.sumsq = d.sumsq; p.maxabs = d.maxabs; p.maxaff = d.maxaff;
   p.aff_a = d.aff_a; p.aff_b = d.aff_b;
   p.status = ctx->status_dev;
+  p.prof = ctx->prof_dev;
 
   const long long total = (long long)gemm_tiles_per_batch(d.m, d.n, bn, d.tri) * d.batch;
   if (total > 0x7fffffffLL) return fail(kErrArg, "gemm: too many tiles");
@@ -237,6 +249,29 @@ int toner_device_status(void* stream, int* status_out) {
   TONER_CUDA(cudaStreamSynchronize(s));
   if (v != 0) TONER_CUDA(cudaMemsetAsync(c->status_dev, 0, sizeof(int), s));
   *status_out = v;
+  return 0;
+}
+
+int toner_gemm_phase_cycles(int enable, void* stream, unsigned long long* out8) {
+  toner::Context* c = toner::context();
+  if (!c) return toner::kErrCuda;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out8) {
+    for (int i = 0; i < 8; ++i) out8[i] = 0;
+    if (c->prof_dev) {
+      TONER_CUDA(cudaMemcpyAsync(out8, c->prof_dev, 8 * sizeof(unsigned long long), cudaMemcpyDeviceToHost, s));
+      TONER_CUDA(cudaStreamSynchronize(s));
+      TONER_CUDA(cudaMemsetAsync(c->prof_dev, 0, 8 * sizeof(unsigned long long), s));
+    }
+  }
+  if (enable && !c->prof_dev) {
+    TONER_CUDA(cudaMalloc(&c->prof_dev, 8 * sizeof(unsigned long long)));
+    TONER_CUDA(cudaMemset(c->prof_dev, 0, 8 * sizeof(unsigned long long)));
+  } else if (!enable && c->prof_dev) {
+    TONER_CUDA(cudaStreamSynchronize(s));
+    TONER_CUDA(cudaFree(c->prof_dev));
+    c->prof_dev = nullptr;
+  }
   return 0;
 }
 

@@ -38,6 +38,7 @@ struct Context {
   CUtensorMap* arena_host = nullptr;  // pinned mirror used as the copy source
   int arena_cap = 0, arena_used = 0;
   int* status_dev = nullptr;          // set by a kernel whose bounded wait ran out
+  unsigned long long* prof_dev = nullptr;  // eight cycle counters, allocated when phase profiling is switched on
   void* map_cache = nullptr;          // std::unordered_map<std::string, int>*
 };
 
@@ -66,5 +67,7 @@ int sumsq_det(const float* x, int batch, int rows, int cols, long long ld, long 
 
 // k-blocks per accumulation chain used for FP32-accurate (split-precision) products
 constexpr int kPromoteAccurate = 2;
+// chain length where a relative error of 1e-6 only propagates linearly (products applied to X, W, gradients)
+constexpr int kPromoteLinear = 8;
 
 }  // namespace toner

@@ -214,6 +214,10 @@ int toner_syrk_upper(const void* const* x_list, const void* x_base, int64_t x_ba
   d.segs = 1;
   d.fmt = 1;
   d.tri = 1;
+  // The tensor core adds into its accumulator by truncation; over tens of thousands of rows the all-positive
+  // sums of the diagonal would drift low by 1e-4.  Chains of 4096 rows, summed with rounding, bound it by 1.5e-5
+  // (two such chains also outlast the epilogue of the previous tile, so the tensor core never waits for it).
+  d.promote = rows > 4096 ? 64 : 0;
   const long long tri_elems = (long long)n * (n + 1) / 2;
   if (mode == 2) {
     d.mirror = 1;

@@ -16,6 +16,7 @@ from ._lib import GemmDesc, Operand, check
 
 PACKED, PACKED_ACC, EMA_FULL = 0, 1, 2
 PROMOTE_ACCURATE = 2  # k-blocks per tensor-core accumulation chain in FP32-accurate products
+PROMOTE_LINEAR = 8    # chain length for products whose error only propagates linearly (about 1e-6 relative)
 _FMT = {torch.float16: 0, torch.bfloat16: 1}
 
 
@@ -53,6 +54,19 @@ def assert_healthy() -> None:
     code = device_status()
     if code:
         raise _lib.TonerError(f"a CUDA kernel gave up a bounded wait (status {code})")
+
+
+def gemm_phase_cycles(enable: bool):
+    """Read and clear the GEMM kernels' phase cycle counters, then switch the counting on or off
+    (toner_gemm_phase_cycles).  Returns a dict of per-CTA averages, or None if nothing was counted."""
+    out = (C.c_uint64 * 8)()
+    check(_lib.load().toner_gemm_phase_cycles(int(enable), _stream(), out), "toner_gemm_phase_cycles")
+    ctas = int(out[7])
+    if not ctas:
+        return None
+    names = ("mma_total", "mma_wait_accumulator", "mma_wait_operands", "tma_wait_stage", "epilogue_wait",
+             "epilogue_write", "epilogue_sum")
+    return {"ctas": ctas, **{n: int(out[i]) // ctas for i, n in enumerate(names)}}
 
 
 def operand(t: torch.Tensor, *, mn_major: bool = False, seg_z: Sequence[int] = (0, 0, 0),

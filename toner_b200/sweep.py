@@ -53,10 +53,17 @@ def flush_l2():
     _flush.zero_()
 
 
+PHASES = False
+
+
 def timed(fn, warmup: int, reps: int, flush: bool):
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
+    if PHASES:  # one extra, untimed call with the kernels' own cycle counters on
+        ops.gemm_phase_cycles(True)
+        fn()
+        print(json.dumps({"phase_cycles_per_cta": ops.gemm_phase_cycles(False)}), flush=True)
     total = 0.0
     best = float("inf")
     for _ in range(reps):
@@ -168,7 +175,7 @@ def bench_gemm(a):
         A = ops.operand(pl, seg_z=(0, 0, batch))
         B = ops.operand(pl, seg_z=(0, batch, 0))
         fn = lambda: ops.gemm(A, B, m=n, n=n, k=n, batch=batch, fmt=0, segs=3, d=d, alpha_a=inv, alpha_b=inv,
-                              tri=a.tri, mirror=a.tri, promote=ops.PROMOTE_ACCURATE)
+                              tri=a.tri, mirror=a.tri, promote=a.promote)
         name = "gemm_split3" + ("_sym" if a.tri else "")
     else:
         x = torch.randn(batch, n, n, device="cuda", generator=g).to(torch.bfloat16)
@@ -177,6 +184,8 @@ def bench_gemm(a):
         fn = lambda: ops.gemm(A, B, m=n, n=n, k=n, batch=batch, fmt=1, d=d, tri=a.tri, mirror=a.tri)
         name = "gemm_bf16" + ("_sym" if a.tri else "")
     ms, best = timed(fn, a.warmup, a.reps, n * n * batch * 2 < (80 << 20))
+    if a.split:
+        name += f"_chain{a.promote}"
     return report(name, {"n": n, "batch": batch}, ms, best, flops=batch * 2 * n ** 3,
                   extra={"note": "single-pass dense count 2 n^3 per product"})
 
@@ -223,9 +232,13 @@ def main():
     ap.add_argument("--mode", default="ema", choices=["ema", "packed"])
     ap.add_argument("--split", action="store_true")
     ap.add_argument("--tri", action="store_true")
+    ap.add_argument("--promote", type=int, default=ops.PROMOTE_ACCURATE, help="k-blocks per accumulation chain of a split product")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--reps", type=int, default=10)
+    ap.add_argument("--phases", action="store_true", help="also print the GEMM kernels' phase cycle counters")
     a = ap.parse_args()
+    global PHASES
+    PHASES = a.phases
     if not torch.cuda.is_available():
         raise SystemExit("the kernel sweep needs a CUDA device (there is no CPU path)")
     torch.cuda.set_device(0)
