@@ -178,6 +178,22 @@ size_t toner_sumsq_scratch_bytes(int32_t batch);
 int toner_sumsq(const float* x, int32_t batch, int32_t rows, int32_t cols, int64_t ld, int64_t bs, float* scratch,
                 float* out, void* stream);
 
+/* toner_sumsq without caller scratch (no counterpart in the reference: it exists for hosts that cannot hand
+ * this library device memory to work in -- for instance an embedding whose every device byte is budgeted and
+ * owned by its own pool, so that neither a scratch tensor for the caller nor a cudaMalloc inside a library is
+ * acceptable).  The partial sums go to an array that is part of the library image: 296 KB on every device that
+ * loads the library, held until the process exits.  Limit: batch <= toner_sumsq_static_max_batch() (256);
+ * larger batches are refused with an error, not truncated.  The result has the same bits as toner_sumsq.
+ * The call allocates and frees nothing (no cudaMalloc / cudaFree, no allocating library routine) and does not
+ * create the library's per-device context.  The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress, with that device current); make that first call before any stream capture begins.
+ * All calls on a device share the one array: two calls whose kernels may overlap on the GPU (different
+ * streams without an ordering between them) race on it -- keep them on one stream or order them with events.
+ * Nothing needs clearing between calls: each call overwrites every partial sum before reading it. */
+int toner_sumsq_static_max_batch(void);
+int toner_sumsq_static(const float* x, int32_t batch, int32_t rows, int32_t cols, int64_t ld, int64_t bs, float* out,
+                       void* stream);
+
 /* m <- mu*m + g ; u = nesterov ? g + mu*m : m ; maxabs[b] = max|u| (FP32 bits, optional).
  * Replaces src/toner/reference.py:197-202 and _muont_in's momentum (src/toner/fast/engine.py:35-39). */
 int toner_muont_momentum(const float* const* grad_ptrs, float* m, float* u, int32_t count, int64_t per, float mu,

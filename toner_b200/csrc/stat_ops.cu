@@ -1,6 +1,8 @@
 // Statistic path: upper-triangle SYRK (on the tcgen05 GEMM), packed-triangle EMA, FP16 hi/lo splitting.
 #include <cuda_fp16.h>
 
+#include <mutex>
+
 #include "runtime.cuh"
 
 namespace toner {
@@ -154,6 +156,35 @@ int sumsq_det(const float* x, int batch, int rows, int cols, long long ld, long 
   return 0;
 }
 
+// ------------------------------------------------------------------ sum of squares without caller scratch
+// Partial sums of toner_sumsq_static live here instead of in a caller-provided buffer.  The array belongs to
+// the library image: every device that loads the library holds these 296 KB until the process exits.
+constexpr int kStaticSumsqMaxBatch = 256;
+static __device__ __align__(256) float g_sumsq_static_scratch[kStaticSumsqMaxBatch * kSumsqBlocks];
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel can use: the
+// device address is looked up once per device (with that device current) and remembered.
+static float* g_sumsq_static_ptr[64] = {};
+static std::mutex g_sumsq_static_mutex;
+
+static int sumsq_static_scratch(float** out) {
+  int dev = -1;
+  TONER_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(kErrCuda, "sumsq_static: unexpected device ordinal");
+  std::lock_guard<std::mutex> lock(g_sumsq_static_mutex);
+  if (!g_sumsq_static_ptr[dev]) {
+    int major = 0;
+    TONER_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10) return fail(kErrUnsupported, "sumsq_static: the kernels are built for sm_100a only");
+    void* ptr = nullptr;
+    TONER_CUDA(cudaGetSymbolAddress(&ptr, g_sumsq_static_scratch));
+    if (!ptr) return fail(kErrCuda, "sumsq_static: the scratch array has no device address");
+    g_sumsq_static_ptr[dev] = static_cast<float*>(ptr);
+  }
+  *out = g_sumsq_static_ptr[dev];
+  return 0;
+}
+
 static int blocks_for(long long work, int per_block, int cap) {
   long long b = (work + per_block - 1) / per_block;
   if (b < 1) b = 1;
@@ -234,6 +265,22 @@ int toner_syrk_upper(const void* const* x_list, const void* x_base, int64_t x_ba
     }
   }
   return launch_gemm(d, static_cast<cudaStream_t>(stream));
+}
+
+int toner_sumsq_static_max_batch(void) { return toner::kStaticSumsqMaxBatch; }
+
+int toner_sumsq_static(const float* x, int32_t batch, int32_t rows, int32_t cols, int64_t ld, int64_t bs, float* out,
+                       void* stream) {
+  using namespace toner;
+  if (!x || !out || batch <= 0 || rows <= 0 || cols <= 0) return fail(kErrArg, "sumsq_static: bad arguments");
+  if (batch > kStaticSumsqMaxBatch)
+    return fail(kErrArg, "sumsq_static: batch " + std::to_string(batch) + " exceeds the built-in scratch (" +
+                             std::to_string(kStaticSumsqMaxBatch) + " matrices); use toner_sumsq with caller scratch");
+  float* scratch = nullptr;
+  if (int rc = sumsq_static_scratch(&scratch)) return rc;
+  // Every partial sum the second kernel reads is written by the first one in this call, so nothing left in
+  // the array by an earlier call needs clearing.
+  return sumsq_det(x, batch, rows, cols, ld, bs, scratch, out, static_cast<cudaStream_t>(stream));
 }
 
 int toner_unpack_ema(const float* packed, float* ema, int32_t k, int32_t n, float beta, float gamma, void* stream) {

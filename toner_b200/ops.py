@@ -313,6 +313,20 @@ def sumsq(x: torch.Tensor, out: Optional[torch.Tensor] = None, scratch: Optional
     return out
 
 
+def sumsq_static(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Per-matrix sum of squares with the library's built-in scratch (toner_sumsq_static): for hosts that may
+    not give the library device memory to work in.  ``out`` is the caller's (batch,) FP32 result buffer; the
+    call itself allocates nothing.  At most ``toner_sumsq_static_max_batch()`` matrices; calls that may overlap
+    on the GPU share the scratch and race."""
+    _need_cuda(x, out)
+    if x.ndim == 2:
+        x = x.unsqueeze(0)
+    batch, rows, cols = x.shape
+    check(_lib.load().toner_sumsq_static(x.data_ptr(), batch, rows, cols, x.stride(1), x.stride(0), out.data_ptr(),
+                                         _stream()), "toner_sumsq_static")
+    return out
+
+
 def pointer_table(tensors: Sequence[torch.Tensor]) -> torch.Tensor:
     """Device array of the tensors' addresses (int64), for kernels over separately allocated matrices."""
     return torch.tensor([t.data_ptr() for t in tensors], dtype=torch.int64).to(tensors[0].device, non_blocking=False)
