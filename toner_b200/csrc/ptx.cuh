@@ -71,7 +71,7 @@ __device__ __forceinline__ void prefetch_tensormap(const void* map) {
 }
 
 // ---------------------------------------------------------------- TMA
-// 3-D tiled load global -> shared; completion is signalled on `bar` in bytes.  No multicast.
+// 3-D tiled load global -> shared; completion is signalled on `bar` in bytes; one destination CTA.
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, uint32_t bar, int x, int y, int z) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
