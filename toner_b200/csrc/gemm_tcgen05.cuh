@@ -86,23 +86,27 @@ __host__ __device__ inline long long packed_off(long long r, long long c, long l
   return r * n - r * (r + 1) / 2 + c;
 }
 
-__host__ __device__ inline int gemm_tiles_per_batch(int M, int N, int BN, int tri) {
-  const int tm = (M + kBM - 1) / kBM, tn = (N + BN - 1) / BN;
+// Tiles are TM x BN (TM = 128, or 256 for CTA pairs).
+__host__ __device__ inline int gemm_tiles_per_batch(int M, int N, int BN, int tri, int TM = kBM) {
+  const int tm = (M + TM - 1) / TM, tn = (N + BN - 1) / BN;
   if (!tri) return tm * tn;
   int total = 0;
   for (int i = 0; i < tm; ++i) {
-    const int first = (i * kBM) / BN;
+    const int first = (i * TM) / BN;
     if (first < tn) total += tn - first;
   }
   return total;
 }
 
-template <int BN>
+// kPair: two CTAs of a cluster work on one 256 x BN tile (cta_group::2); each holds 128 rows of A and BN/2
+// rows of B per stage, so a stage is two thirds the size and the ring two stages deeper.
+template <int BN, bool kPair = false>
 struct GemmSmem {
   static constexpr int kABytes = kBM * kBK * 2;
-  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kBRows = kPair ? BN / 2 : BN;   // rows of B this CTA loads per stage
+  static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStages = (192 * 1024) / kStageBytes;
   static constexpr int kTileBytes = kStages * kStageBytes;
   static constexpr int kBarBytes = 256;
   static constexpr int kEpiBytes = 8 * 32 * 33 * 4;  // one padded 32 x 32 FP32 staging block per epilogue warp
@@ -110,7 +114,7 @@ struct GemmSmem {
   static constexpr int kTmemCols = 2 * BN;
 };
 
-__device__ __forceinline__ void tile_coord(const GemmParams& p, int BN, int t, int tiles_per_batch, int tiles_n,
+__device__ __forceinline__ void tile_coord(const GemmParams& p, int BN, int TM, int t, int tiles_per_batch, int tiles_n,
                                            int& b, int& tm, int& tn) {
   b = t / tiles_per_batch;
   int r = t - b * tiles_per_batch;
@@ -129,7 +133,7 @@ __device__ __forceinline__ void tile_coord(const GemmParams& p, int BN, int t, i
   }
   tm = 0;
   for (;;) {
-    const int first = (tm * kBM) / BN;
+    const int first = (tm * TM) / BN;
     const int cnt = tiles_n - first;
     if (r < cnt) {
       tn = first + r;
@@ -313,9 +317,17 @@ __device__ __forceinline__ void epilogue_block_scalar(const GemmParams& p, const
 }
 
 // kChained: the kernel sums several accumulation chains per tile in registers (p.promote > 0).
-template <int BN, bool kChained>
+// kPair: launched as clusters of two CTAs that share each 256 x BN tile (BN = 256): both load their halves of
+// the operands, the leader CTA's MMA thread issues cta_group::2 MMAs, each CTA's epilogue warps write the
+// 128 rows that sit in its own tensor memory.  The pair halves the operand traffic per flop of B.
+template <int BN, bool kChained, bool kPair = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
-  using S = GemmSmem<BN>;
+  using S = GemmSmem<BN, kPair>;
+  constexpr int TM = kPair ? 2 * kBM : kBM;            // rows of one scheduled tile
+  const uint32_t cta_rank = kPair ? ptx::cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int unit = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;     // which persistent worker this CTA (pair) is
+  const int units = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -331,7 +343,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = (p.N + BN - 1) / BN;
-  const int tiles_per_batch = gemm_tiles_per_batch(p.M, p.N, BN, p.tri);
+  const int tiles_per_batch = gemm_tiles_per_batch(p.M, p.N, BN, p.tri, TM);
   const int total_tiles = tiles_per_batch * p.batch;
   const int kb_per_seg = (p.K + kBK - 1) / kBK;
   const int num_kb = kb_per_seg * p.segs;
@@ -379,17 +391,23 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
     }
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(tfull_bar(s), 1);
-      ptx::mbar_init(tempty_bar(s), 8);  // one arrival per epilogue warp
+      ptx::mbar_init(tempty_bar(s), kPair ? 16 : 8);  // one arrival per epilogue warp (of both CTAs of a pair)
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
   }
   if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), S::kTmemCols);
-    ptx::tmem_relinquish();
+    if constexpr (kPair) {
+      ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), S::kTmemCols);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), S::kTmemCols);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before();
-  __syncthreads();
+  if constexpr (kPair) ptx::cluster_sync();  // the peer's barriers exist before anything signals them
+  else __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -402,14 +420,15 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
       uint32_t phase = 0;
       bool ok = true;
       long long prof_wait = 0;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < total_tiles && ok; t += units) {
         int b, tm, tn;
-        tile_coord(p, BN, t, tiles_per_batch, tiles_n, b, tm, tn);
+        tile_coord(p, BN, TM, t, tiles_per_batch, tiles_n, b, tm, tn);
         const CUtensorMap* amap = p.a_maps + (long long)b * p.a_map_stride;
         const CUtensorMap* bmap = p.b_maps + (long long)b * p.b_map_stride;
         ptx::fence_tensormap_acquire(amap);
         ptx::fence_tensormap_acquire(bmap);
-        const int m0 = tm * kBM, n0 = tn * BN;
+        // a pair splits the tile's rows (A) and its columns (B) between its two CTAs
+        const int m0 = tm * TM + (int)cta_rank * kBM, n0 = tn * BN + (int)cta_rank * S::kBRows;
         for (int si = 0; si < p.segs && ok; ++si) {
           const int seg = rest_first ? (si + 1 == p.segs ? 0 : si + 1) : si;
           const int za = b * p.a_z_stride + p.a_seg_z[seg];
@@ -426,18 +445,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
             }
             const uint32_t sa = base + stage * S::kStageBytes;
             const uint32_t sb = sa + S::kABytes;
-            ptx::mbar_expect_tx(full_bar(stage), S::kStageBytes);
-            if (p.a_mn) {
+            if constexpr (kPair) {
+              // Both CTAs' copies report to the leader's barrier, which expects the bytes of the whole pair.
+              const uint32_t lbar = ptx::mapa(full_bar(stage), 0);
+              if (leader) ptx::mbar_expect_tx(full_bar(stage), 2 * S::kStageBytes);
+              if (p.a_mn) {
 #pragma unroll
-              for (int s = 0; s < kBM / 64; ++s) ptx::tma_load_3d(sa + s * 8192, amap, full_bar(stage), m0 + s * 64, k0, za);
-            } else {
-              ptx::tma_load_3d(sa, amap, full_bar(stage), k0, m0, za);
-            }
-            if (p.b_mn) {
+                for (int s = 0; s < kBM / 64; ++s) ptx::tma_load_3d_pair(sa + s * 8192, amap, lbar, m0 + s * 64, k0, za);
+              } else {
+                ptx::tma_load_3d_pair(sa, amap, lbar, k0, m0, za);
+              }
+              if (p.b_mn) {
 #pragma unroll
-              for (int s = 0; s < BN / 64; ++s) ptx::tma_load_3d(sb + s * 8192, bmap, full_bar(stage), n0 + s * 64, k0, zb);
+                for (int s = 0; s < S::kBRows / 64; ++s) ptx::tma_load_3d_pair(sb + s * 8192, bmap, lbar, n0 + s * 64, k0, zb);
+              } else {
+                ptx::tma_load_3d_pair(sb, bmap, lbar, k0, n0, zb);
+              }
             } else {
-              ptx::tma_load_3d(sb, bmap, full_bar(stage), k0, n0, zb);
+              ptx::mbar_expect_tx(full_bar(stage), S::kStageBytes);
+              if (p.a_mn) {
+#pragma unroll
+                for (int s = 0; s < kBM / 64; ++s) ptx::tma_load_3d(sa + s * 8192, amap, full_bar(stage), m0 + s * 64, k0, za);
+              } else {
+                ptx::tma_load_3d(sa, amap, full_bar(stage), k0, m0, za);
+              }
+              if (p.b_mn) {
+#pragma unroll
+                for (int s = 0; s < BN / 64; ++s) ptx::tma_load_3d(sb + s * 8192, bmap, full_bar(stage), n0 + s * 64, k0, zb);
+              } else {
+                ptx::tma_load_3d(sb, bmap, full_bar(stage), k0, n0, zb);
+              }
             }
             if (++stage == S::kStages) {
               stage = 0;
@@ -447,16 +484,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         }
       }
       if (p.prof) atomicAdd(p.prof + 3, (unsigned long long)prof_wait);
-      if (!ok) {
+      if (!ok && !kPair) {
         // give copies already in flight time to land before the CTA gives its shared memory back
         for (int s = 0; s < S::kStages; ++s) ptx::mbar_wait(full_bar(s), 0, 2000000LL);
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (of a pair: the leader CTA only)
+    if (lane == 0 && leader) {
       const uint32_t idesc = (1u << 4) | ((uint32_t)p.fmt << 7) | ((uint32_t)p.fmt << 10) | ((uint32_t)p.a_mn << 15) |
-                             ((uint32_t)p.b_mn << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+                             ((uint32_t)p.b_mn << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
       // K-major: 8-row groups 1024 B apart, k advances 32 B inside the swizzled row.
       // MN-major: 64-element slabs 8192 B apart (LBO), 8-k-row groups 1024 B apart (SBO), k advances 16 rows = 2048 B.
       const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
@@ -467,7 +504,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
       bool ok = true;
       long long prof_acc = 0, prof_ops = 0;
       const long long prof_t0 = p.prof ? clock64() : 0;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = unit; t < total_tiles && ok; t += units) {
         for (int ch = 0; ch < chunks_per_tile && ok; ++ch, ++gchunk) {
           int kb_begin, kb_end;
           chunk_range(ch, kb_begin, kb_end);
@@ -500,15 +537,29 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
             for (int k = 0; k < kBK / kUmmaK; ++k) {
               const uint64_t da = ptx::smem_desc(sa + k * a_step, a_lbo, 1024u);
               const uint64_t db = ptx::smem_desc(sb + k * b_step, b_lbo, 1024u);
-              ptx::mma_f16(d_tmem, da, db, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
+              if constexpr (kPair) ptx::mma_f16_pair(d_tmem, da, db, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
+              else ptx::mma_f16(d_tmem, da, db, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
             }
-            ptx::mma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+            // frees the stage (in both CTAs of a pair) once these MMAs have read it
+            if constexpr (kPair) {
+              ptx::mma_commit_pair(empty_bar(stage));
+              ptx::mma_commit_pair(ptx::mapa(empty_bar(stage), 1));
+            } else {
+              ptx::mma_commit(empty_bar(stage));
+            }
             if (++stage == S::kStages) {
               stage = 0;
               phase ^= 1u;
             }
           }
-          if (ok) ptx::mma_commit(tfull_bar(buf));  // this chain's partial sum is complete
+          if (ok) {  // this chain's partial sum is complete
+            if constexpr (kPair) {
+              ptx::mma_commit_pair(tfull_bar(buf));
+              ptx::mma_commit_pair(ptx::mapa(tfull_bar(buf), 1));
+            } else {
+              ptx::mma_commit(tfull_bar(buf));
+            }
+          }
         }
       }
       if (p.prof) {
@@ -534,10 +585,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
     uint32_t gchunk = 0;
     bool alive = true;
     long long prof_wait = 0, prof_out = 0, prof_sum = 0;
-    for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
+    for (int t = unit; t < total_tiles && alive; t += units) {
       int b, tm, tn;
-      tile_coord(p, BN, t, tiles_per_batch, tiles_n, b, tm, tn);
-      const int m0 = tm * kBM, n0 = tn * BN;
+      tile_coord(p, BN, TM, t, tiles_per_batch, tiles_n, b, tm, tn);
+      const int m0 = tm * TM + (int)cta_rank * kBM, n0 = tn * BN;  // this CTA's 128 rows of the tile
       const int row_first = m0 + lane_group * 32;
       const int col_first = n0 + half * (BN / 2);
       // 32-column blocks this warp never needs: beyond N, or wholly below the diagonal (warp-uniform)
@@ -560,7 +611,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
       auto release = [&](int buf) {  // buffer drained: hand it back to the MMA warp
         ptx::tc_fence_before();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+        if (lane == 0) {
+          if constexpr (kPair) ptx::mbar_arrive_cluster(ptx::mapa(tempty_bar(buf), 0));  // the leader's MMA thread waits
+          else ptx::mbar_arrive(tempty_bar(buf));
+        }
       };
       auto tmem_of = [&](int buf) {
         return tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN + half * (BN / 2));
@@ -692,10 +746,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
 
   // ---------------------------------------------------------------- teardown
   ptx::tc_fence_before();
-  __syncthreads();
+  if constexpr (kPair) ptx::cluster_sync();  // neither CTA leaves while the other may still signal or read it
+  else __syncthreads();
   if (warp == 1) {
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, S::kTmemCols);
+    if constexpr (kPair) ptx::tmem_dealloc_pair(tmem_base, S::kTmemCols);
+    else ptx::tmem_dealloc(tmem_base, S::kTmemCols);
   }
 }
 

@@ -72,6 +72,8 @@ Context* context() {
   cudaFuncSetAttribute(gemm_tcgen05_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256>::kTotal);
   cudaFuncSetAttribute(gemm_tcgen05_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<128>::kTotal);
   cudaFuncSetAttribute(gemm_tcgen05_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<128>::kTotal);
+  cudaFuncSetAttribute(gemm_tcgen05_kernel<256, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256, true>::kTotal);
+  cudaFuncSetAttribute(gemm_tcgen05_kernel<256, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256, true>::kTotal);
   c.device = dev;
   return &c;
 }
@@ -145,18 +147,30 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
   if (d.packed && (d.split0 || d.split1)) return fail(kErrArg, "gemm: operand planes cannot be packed");
   if (d.fmt != 0 && d.fmt != 1) return fail(kErrArg, "gemm: fmt must be 0 (FP16) or 1 (BF16)");
 
+  // Tile choice: 256 x 256 tiles on CTA pairs when they fill the machine (fewest operand bytes per flop), else
+  // 128 x 256, else 128 x 128 (most tiles for small problems).  tile_n forces one: 128, 256, or 512 for the pair.
   int bn = d.tile_n;
+  bool pair = false;
   if (bn == 0) {
+    const long long tpair = (long long)gemm_tiles_per_batch(d.m, d.n, 256, d.tri, 256) * d.batch;
     const long long t256 = (long long)gemm_tiles_per_batch(d.m, d.n, 256, d.tri) * d.batch;
-    bn = (t256 >= ctx->num_sms) ? 256 : 128;
+    if (tpair >= ctx->num_sms / 2) {
+      bn = 256;
+      pair = true;
+    } else {
+      bn = (t256 >= ctx->num_sms) ? 256 : 128;
+    }
+  } else if (bn == 512) {
+    bn = 256;
+    pair = true;
   }
-  if (bn != 128 && bn != 256) return fail(kErrArg, "gemm: tile_n must be 0, 128 or 256");
+  if (bn != 128 && bn != 256) return fail(kErrArg, "gemm: tile_n must be 0, 128, 256 or 512 (256 x 256 on a CTA pair)");
 
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
   int rc = get_maps(ctx, d.a, d.batch, kBM, stream, &p.a_maps);
   if (rc) return rc;
-  rc = get_maps(ctx, d.b, d.batch, bn, stream, &p.b_maps);
+  rc = get_maps(ctx, d.b, d.batch, pair ? bn / 2 : bn, stream, &p.b_maps);
   if (rc) return rc;
   p.a_map_stride = d.a.list ? 1 : 0;
   p.b_map_stride = d.b.list ? 1 : 0;
@@ -202,10 +216,29 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
   p.status = ctx->status_dev;
   p.prof = ctx->prof_dev;
 
-  const long long total = (long long)gemm_tiles_per_batch(d.m, d.n, bn, d.tri) * d.batch;
+  const long long total = (long long)gemm_tiles_per_batch(d.m, d.n, bn, d.tri, pair ? 256 : kBM) * d.batch;
   if (total > 0x7fffffffLL) return fail(kErrArg, "gemm: too many tiles");
-  const int grid = (int)(total < ctx->num_sms ? total : ctx->num_sms);
   const bool chained = p.promote > 0;
+  if (pair) {
+    const int pairs = (int)(total < ctx->num_sms / 2 ? total : ctx->num_sms / 2);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = GemmSmem<256, true>::kTotal;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (chained) TONER_CUDA(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<256, true, true>, p));
+    else TONER_CUDA(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<256, false, true>, p));
+    count_launch();
+    return 0;
+  }
+  const int grid = (int)(total < ctx->num_sms ? total : ctx->num_sms);
   if (bn == 256) {
     if (chained) gemm_tcgen05_kernel<256, true><<<grid, kGemmThreads, GemmSmem<256>::kTotal, stream>>>(p);
     else gemm_tcgen05_kernel<256, false><<<grid, kGemmThreads, GemmSmem<256>::kTotal, stream>>>(p);

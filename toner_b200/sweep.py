@@ -175,13 +175,13 @@ def bench_gemm(a):
         A = ops.operand(pl, seg_z=(0, 0, batch))
         B = ops.operand(pl, seg_z=(0, batch, 0))
         fn = lambda: ops.gemm(A, B, m=n, n=n, k=n, batch=batch, fmt=0, segs=3, d=d, alpha_a=inv, alpha_b=inv,
-                              tri=a.tri, mirror=a.tri, promote=a.promote)
+                              tri=a.tri, mirror=a.tri, promote=a.promote, tile_n=a.tile)
         name = "gemm_split3" + ("_sym" if a.tri else "")
     else:
         x = torch.randn(batch, n, n, device="cuda", generator=g).to(torch.bfloat16)
         y = torch.randn(batch, n, n, device="cuda", generator=g).to(torch.bfloat16)
         A, B = ops.operand(x), ops.operand(y)
-        fn = lambda: ops.gemm(A, B, m=n, n=n, k=n, batch=batch, fmt=1, d=d, tri=a.tri, mirror=a.tri)
+        fn = lambda: ops.gemm(A, B, m=n, n=n, k=n, batch=batch, fmt=1, d=d, tri=a.tri, mirror=a.tri, tile_n=a.tile)
         name = "gemm_bf16" + ("_sym" if a.tri else "")
     ms, best = timed(fn, a.warmup, a.reps, n * n * batch * 2 < (80 << 20))
     if a.split:
@@ -232,6 +232,7 @@ def main():
     ap.add_argument("--mode", default="ema", choices=["ema", "packed"])
     ap.add_argument("--split", action="store_true")
     ap.add_argument("--tri", action="store_true")
+    ap.add_argument("--tile", type=int, default=0, help="force a tile: 128, 256, or 512 for 256x256 on CTA pairs (0: the library chooses)")
     ap.add_argument("--promote", type=int, default=ops.PROMOTE_ACCURATE, help="k-blocks per accumulation chain of a split product")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--reps", type=int, default=10)
