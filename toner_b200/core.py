@@ -99,7 +99,10 @@ class FactorSet:
             self.hi_planes, self.hi_inv = self.lo_planes, self.lo_inv
         per = ops.inv_roots_workspace_bytes(1, n)
         if chunk is None:
-            chunk = max(1, min(k, (6 << 30) // per))
+            # One launch over all statistics keeps the persistent kernel's last wave full (24 statistics of width
+            # 5632 are 83 waves of pair tiles; five at a time would be 18 waves per launch with a ragged tail each).
+            budget = min(32 << 30, torch.cuda.get_device_properties(device).total_memory // 5)
+            chunk = max(1, min(k, budget // per))
         self.workspace = self.scratch.bytes_like("inv_roots", ops.inv_roots_workspace_bytes(chunk, n), device)
         self.iterations = ops.inv_roots_iterations(n, self.damping, self.p)
         self.fallbacks = 0
@@ -216,28 +219,46 @@ def _product(a_planes, a_inv, group: MatrixGroup, which: str, d, **kw) -> None:
              alpha_b=r_inv[group.first:], alpha_b_step=group.step, promote=0, **kw)
 
 
-def muont_group_delta(group: MatrixGroup, grads: Sequence[torch.Tensor], delta: torch.Tensor, scratch: Scratch, *,
-                      lr: float, weight_decay: float, momentum: float, nesterov: bool, ns_steps: int,
-                      ns_eps: float) -> None:
-    """Write the MuonT parameter change of every matrix of the group into ``delta`` (count, out, in)."""
-    f, dev = group.factors, group.device
+def _muont_buffers(group: MatrixGroup, scratch: Scratch):
+    dev = group.device
     count, m, n = group.count, group.out_features, group.in_features
     shape = (count, m, n)
-    work = scratch.get("work", shape, torch.float32, dev)
-    planes = scratch.get("planes", (2,) + shape, torch.float16, dev)
-    inv = scratch.get("inv", (count,), torch.float32, dev)
-    maxabs = scratch.get("maxabs", (count,), torch.int32, dev)
-    c1 = scratch.get("c1", (count,), torch.float32, dev)
-    c2 = scratch.get("c2", (count,), torch.float32, dev)
+    return dict(work=scratch.get("work", shape, torch.float32, dev),
+                planes=scratch.get("planes", (2,) + shape, torch.float16, dev),
+                inv=scratch.get("inv", (count,), torch.float32, dev),
+                maxabs=scratch.get("maxabs", (count,), torch.int32, dev),
+                c1=scratch.get("c1", (count,), torch.float32, dev),
+                c2=scratch.get("c2", (count,), torch.float32, dev))
+
+
+def muont_ns_input(group: MatrixGroup, grads: Sequence[torch.Tensor], scratch: Scratch, *, momentum: float,
+                   nesterov: bool) -> torch.Tensor:
+    """Stage 1 of the MuonT update: momentum, Nesterov direction and the inner preconditioning d R_in
+    (src/toner/reference.py:197-204).  Returns the (count, out, in) stack the polar iteration starts from."""
+    f = group.factors
+    buf = _muont_buffers(group, scratch)
+    work, planes, inv, maxabs = buf["work"], buf["planes"], buf["inv"], buf["maxabs"]
     ops.muont_momentum(group.grad_ptrs(grads), group.m, work, momentum, nesterov, maxabs)
     if f.inner_strength != 0:
         ops.split16(work, planes=planes, inv_scale=inv, maxabs=maxabs)
         _product(planes, inv, group, "inner", work)
-    ns_ws = scratch.bytes_like("ns", ops.ns_polar_workspace_bytes(count, m, n), dev)
-    ops.ns_polar(work, ns_steps, ns_eps, out=work, maxabs=maxabs, workspace=ns_ws)
+    return work
+
+
+def muont_delta_from_polar(group: MatrixGroup, polar: torch.Tensor, delta: torch.Tensor, scratch: Scratch, *, lr: float,
+                           weight_decay: float, polar_maxabs: Optional[torch.Tensor] = None) -> None:
+    """Stage 3: outer map, shape scale and shaped weight decay (src/toner/reference.py:206-215), fused as the
+    reference's engine fuses them (src/toner/fast/engine.py:42-51):
+    delta = -((lr wd n / ||R||^2) W R + (lr s sqrt(n) / ||R||) P) R.  `polar` may be the work stack itself."""
+    f = group.factors
+    count, m, n = group.count, group.out_features, group.in_features
+    buf = _muont_buffers(group, scratch)
+    work, planes, inv, maxabs, c1, c2 = (buf[k] for k in ("work", "planes", "inv", "maxabs", "c1", "c2"))
+    if polar.data_ptr() != work.data_ptr():
+        work.copy_(polar)
+        polar_maxabs = None
     scale = max(1.0, m / n) ** 0.5
     if f.outer_strength == 0:
-        # identity outer factor: delta = -(lr wd W + lr scale P)
         raise ValueError("outer_strength 0 is not supported by the CUDA path")
     ops.muont_coeffs(f.fro2_outer, group.first, group.step, count, n, lr, weight_decay, scale, c1, c2)
     if weight_decay != 0:
@@ -247,9 +268,25 @@ def muont_group_delta(group: MatrixGroup, grads: Sequence[torch.Tensor], delta: 
         _product(planes, inv, group, "outer", work, c=work, beta=1.0, beta_v=c2, maxabs=maxabs)  # V = c1 W R + c2 P
         ops.split16(work, planes=planes, inv_scale=inv, maxabs=maxabs)
     else:
-        ops.split16(work, planes=planes, inv_scale=inv, maxabs=maxabs)
+        if polar_maxabs is None:
+            ops.split16(work, planes=planes, inv_scale=inv, scratch=maxabs)
+        else:
+            ops.split16(work, planes=planes, inv_scale=inv, maxabs=polar_maxabs)
         ops.scale_vec(inv, c2)  # V = c2 P
     _product(planes, inv, group, "outer", delta, alpha=-1.0)
+
+
+def muont_group_delta(group: MatrixGroup, grads: Sequence[torch.Tensor], delta: torch.Tensor, scratch: Scratch, *,
+                      lr: float, weight_decay: float, momentum: float, nesterov: bool, ns_steps: int,
+                      ns_eps: float) -> None:
+    """Write the MuonT parameter change of every matrix of the group into ``delta`` (count, out, in)."""
+    dev = group.device
+    count, m, n = group.count, group.out_features, group.in_features
+    work = muont_ns_input(group, grads, scratch, momentum=momentum, nesterov=nesterov)
+    maxabs = _muont_buffers(group, scratch)["maxabs"]
+    ns_ws = scratch.bytes_like("ns", ops.ns_polar_workspace_bytes(count, m, n), dev)
+    ops.ns_polar(work, ns_steps, ns_eps, out=work, maxabs=maxabs, workspace=ns_ws)
+    muont_delta_from_polar(group, work, delta, scratch, lr=lr, weight_decay=weight_decay, polar_maxabs=maxabs)
 
 
 def adamt_group_delta(group: MatrixGroup, grads: Sequence[torch.Tensor], delta: torch.Tensor, scratch: Scratch, *,
