@@ -202,9 +202,12 @@ def run_ours(args) -> None:
 
     if rank == 0:
         pk = peaks()
-        p_iters = ops.inv_roots_iterations(mlp, 1e-3, 8)
-        gemms = (p_iters - 1) + (p_iters - 1) * 4 + 2   # X T, T^2 T^4 T^8 T^8 M per iteration, two squarings
-        fl = step_flops(layers, hidden, mlp, local_rows * world, gemms, gemms)
+        # products per statistic: X T and T^2 T^4 T^8 T^8 M per Newton step (no X product in the first, no M update
+        # in the last), two squarings for A^-1/2; the step count follows each group's spectrum bound
+        it_d, it_f = core.groups["d"].factors.iterations, core.groups["f"].factors.iterations
+        gemms_d, gemms_f = (it_d - 1) * 5 + 2, (it_f - 1) * 5 + 2
+        gemms = gemms_f
+        fl = step_flops(layers, hidden, mlp, local_rows * world, gemms_d, gemms_f)
         ph = phases[-1] if phases and phases[-1] else {}
         per_phase = {}
         for name, work in (("stats", fl["syrk"]), ("roots", fl["roots"]), ("update", fl["ns"] + fl["precond"])):
@@ -223,8 +226,9 @@ def run_ours(args) -> None:
             if top == "roots":
                 # what the tensor cores execute: three FP16 plane products per accumulator, on the 128x256 tiles
                 # that meet the upper triangle (fractions 0.5625 at n=2048, 0.523 at n=5632)
-                ex = (3 * layers * gemms * 2 * hidden ** 3 * 3 * tri_fraction(hidden) +
-                      layers * gemms * 2 * mlp ** 3 * 3 * tri_fraction(mlp)) / world / ph[top] / 1e9
+                ex = (3 * layers * gemms_d * 2 * hidden ** 3 * 3 * tri_fraction(hidden, 256) +
+                      layers * gemms_f * 2 * mlp ** 3 * 3 * tri_fraction(mlp, 256)) / world / ph[top] / 1e9
+                roof["newton_steps"] = {"hidden": it_d, "mlp": it_f}
                 roof["executed"] = round(ex, 1)
                 roof["frac_executed"] = round(ex / pk["tflops"], 4)
         line = {

@@ -151,9 +151,24 @@ int toner_split16(const float* x, const float* const* x_list, int32_t batch, int
  * smaller workspace makes the call loop over chunks (it must hold at least one statistic). */
 size_t toner_inv_roots_workspace_bytes(int32_t chunk, int32_t n);
 int toner_inv_roots_iterations(int32_t n, float damping, int32_t p);
+int toner_inv_roots_iterations_for(float lower, int32_t p);   /* the count for a given spectrum lower bound */
 int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
                     float* root_lo, float* root_hi, float* fro2_lo, int32_t* status, void* workspace,
                     size_t workspace_bytes, void* stream);
+/* The same with what a caller that factors slowly changing statistics every step can add:
+ *   lower     lower bound of the spectrum of A' / ||A'||_F valid for every statistic of the call (0: use the bound
+ *             damping / (n (1 + damping)) that always holds).  A larger bound means fewer Newton steps
+ *             (toner_inv_roots_iterations_for).  The bound is checked on the device: status[b] = 3 where
+ *             damping / ||A'_b||_F lies below it, and the caller recomputes that statistic.
+ *   norm_out  (DEVICE, optional, k floats) ||A'_b||_F, from which the caller derives next step's bound.
+ * A' is A with its dominant eigen-direction deflated: six power-iteration steps find (lambda_1, v); where they
+ * converged (residual below 1e-5) and lambda_1 stands above 8x the mean of the rest, the engine factors
+ * A' = A - (lambda_1 - c) v v^T and adds (lambda_1^(-1/p) - c^(-1/p)) v v^T back to the root.  This is what the
+ * reference's eigendecomposition does implicitly for the mean-activation direction of an input statistic
+ * (src/toner/linalg.py:72-86); toner_inv_roots deflates too. */
+int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
+                       float lower, float* root_lo, float* root_hi, float* fro2_lo, int32_t* status, float* norm_out,
+                       void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------ Newton-Schulz polar iteration
  * x = u / (||u||_F + eps); `steps` times  A = x x^T (on the short side),  x <- a x + (b A + c A A) x  with

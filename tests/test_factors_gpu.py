@@ -114,3 +114,42 @@ def test_iteration_counts_are_stated(ops):
     assert ops.inv_roots_iterations(5632, 1e-3, 4) == 11
     assert ops.inv_roots_iterations(5632, 1e-3, 2) == 12
     assert ops.inv_roots_iterations(768, 1e-3, 8) <= 10
+
+
+def test_callers_spectrum_bound_saves_steps_and_is_checked(ops):
+    """toner_inv_roots_ex: with the bound a caller derives from the reported ||A'||_F the engine takes fewer Newton
+    steps and returns the same roots; a bound the statistics do not satisfy is flagged (status 3), not trusted."""
+    stats = torch.stack([spd(512, 1e3, s) for s in range(3)]).cuda()
+    norms = torch.zeros(3, device="cuda")
+    lo0, hi0, _, st0 = ops.inv_roots(stats, DAMPING, 8, 4, norms=norms)
+    assert st0.tolist() == [0, 0, 0]
+    lower = 0.6 * DAMPING / norms.max().item()
+    assert ops.inv_roots_iterations_for(lower, 8) < ops.inv_roots_iterations(512, DAMPING, 8)
+    lo1, hi1, _, st1 = ops.inv_roots(stats, DAMPING, 8, 4, lower=lower)
+    ops.assert_healthy()
+    assert st1.tolist() == [0, 0, 0]
+    for b in range(3):
+        assert orc.rel_fro(lo1[b].cpu(), lo0[b].cpu()) < 2e-5 and orc.rel_fro(hi1[b].cpu(), hi0[b].cpu()) < 1e-4
+    too_high = 5.0 * DAMPING / norms.min().item()
+    _, _, _, st2 = ops.inv_roots(stats, DAMPING, 8, 4, lower=too_high)
+    assert all(s in (1, 3) for s in st2.tolist()) and 3 in st2.tolist()
+
+
+def test_dominant_direction_is_deflated(ops):
+    """One eigenvalue 400 times the rest: the reported norm is that of the deflated statistic (about
+    0.8 sqrt(n), not 0.8 (1 + n/4)), and the roots are as accurate as for a flat spectrum."""
+    from toner_b200.synthetic import fill_rows
+    n, rows = 2048, 16384
+    buf = torch.empty(1, rows, n, device="cuda", dtype=torch.bfloat16)
+    fill_rows(buf, seed=5)
+    ema = torch.zeros(1, n, n, device="cuda")
+    ops.syrk_upper(buf, ema, ops.EMA_FULL, 0.0, 1.0 / rows)
+    norms = torch.zeros(1, device="cuda")
+    lo, hi, _, status = ops.inv_roots(ema, DAMPING, 8, 4, norms=norms)
+    ops.assert_healthy()
+    assert status.tolist() == [0]
+    assert norms.item() < 3.0 * n ** 0.5
+    c = ema[0].cpu()
+    assert orc.rel_fro(lo[0].cpu(), orc.inverse_root_truth(c, 0.125, DAMPING)) < 1e-4
+    assert orc.rel_fro(hi[0].cpu(), orc.inverse_root_truth(c, 0.5, DAMPING)) < 5e-4
+    assert torch.equal(lo[0], lo[0].T)

@@ -89,6 +89,11 @@ class FactorSet:
         self.fro2_hi = torch.empty(k, device=device, dtype=torch.float32) if self.q > 1 else None
         self.status = torch.zeros(k, device=device, dtype=torch.int32)
         self.status_host = torch.zeros(k, dtype=torch.int32).pin_memory()
+        # ||A'||_F of every statistic as the last factorisation saw it: next step's spectrum bound comes from it
+        # (the statistics are EMAs and move by a few percent per step)
+        self.norms = torch.zeros(k, device=device, dtype=torch.float32)
+        self.norms_host = torch.zeros(k, dtype=torch.float32).pin_memory()
+        self.lower = 0.0
         self.status_event: Optional[torch.cuda.Event] = None
         self.lo_planes = torch.empty(2, k, n, n, device=device, dtype=torch.float16)
         self.lo_inv = torch.empty(k, device=device, dtype=torch.float32)
@@ -134,9 +139,13 @@ class FactorSet:
         if self.inner_strength == 0 and self.outer_strength == 0:
             return
         ops.inv_roots(self.ema, self.damping, self.p, self.q, root_lo=self.root_lo, root_hi=self.root_hi,
-                      fro2_lo=self.fro2_lo, status=self.status, workspace=self.workspace)
+                      fro2_lo=self.fro2_lo, status=self.status, workspace=self.workspace, lower=self.lower,
+                      norms=self.norms)
+        self.iterations = (ops.inv_roots_iterations_for(self.lower, self.p) if self.lower > 0
+                           else ops.inv_roots_iterations(self.n, self.damping, self.p))
         self._split()
         self.status_host.copy_(self.status, non_blocking=True)
+        self.norms_host.copy_(self.norms, non_blocking=True)
         self.status_event = torch.cuda.Event()
         self.status_event.record(torch.cuda.current_stream())
 
@@ -156,6 +165,16 @@ class FactorSet:
         self.status_event.synchronize()
         self.status_event = None
         bad = [i for i, s in enumerate(self.status_host.tolist()) if s != 0]
+        # Next step's bound: damping / ||A'||_F of the widest statistic, with room for one step of EMA drift.
+        # A flagged statistic (not converged, or below the bound used) sends the next step back to the bound
+        # that always holds.
+        top = float(self.norms_host.max())
+        worst = self.damping / (self.n * (1.0 + self.damping))
+        self.lower = 0.0
+        if not bad and math.isfinite(top) and top > 0:
+            hint = 0.6 * self.damping / top
+            if worst < hint < 1.0:
+                self.lower = hint
         if not bad:
             return 0
         self.fallbacks += len(bad)

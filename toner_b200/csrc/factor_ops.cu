@@ -72,6 +72,9 @@ static int chain_length(double lower) {
 // Products applied to X (and the final squarings) pass their error on linearly: one chain, about 1e-5.
 constexpr int kPromoteX = 0;
 
+// power-iteration steps spent on the dominant direction (each one pass over the statistic)
+constexpr int kPowerSteps = 6;
+
 static int default_iterations(double l0, int p) {
   // steps until the spectrum is within 3e-4 of 1, plus one Newton step (which squares that distance)
   for (int k = 1; k < 64; ++k) {
@@ -176,16 +179,147 @@ __global__ void __launch_bounds__(256) init_planes_kernel(const float* __restric
   }
 }
 
+// ------------------------------------------------------------------ deflation of a dominant direction
+// Activation statistics usually have one eigenvalue far above the rest (the mean activation).  It sets ||A||
+// and with it the spectrum's lower bound after normalisation, i.e. the number of Newton steps and the
+// attainable accuracy.  A few power-iteration steps find that eigenpair (lambda_1, v) to working accuracy when
+// the gap is large; then  A' = A - (lambda_1 - c) v v^T  (c = mean of the remaining eigenvalues) has the same
+// eigenvectors, and  A^{-s} = A'^{-s} + (lambda_1^{-s} - c^{-s}) v v^T.  When the iteration has not converged
+// (no dominant direction) nothing is deflated.
+
+// v_0: a fixed pattern of +-1 / sqrt(n)
+__global__ void power_start_kernel(float* __restrict__ v, int n) {
+  const int b = blockIdx.y;
+  const float s = rsqrtf((float)n);
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    v[(long long)b * n + i] = (((unsigned)i * 2654435761u) >> 15) & 1u ? s : -s;
+}
+
+// y = A v, one warp per row, FP64 accumulation
+__global__ void __launch_bounds__(256) gemv_kernel(const float* __restrict__ a, const float* __restrict__ v,
+                                                   float* __restrict__ y, int n) {
+  const int b = blockIdx.y;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= n) return;
+  const float* A = a + ((long long)b * n + row) * n;
+  const float* X = v + (long long)b * n;
+  double acc = 0.0;
+  for (int c = lane * 4; c < n; c += 128) {
+    const float4 av = *reinterpret_cast<const float4*>(A + c);
+    const float4 xv = *reinterpret_cast<const float4*>(X + c);
+    acc += (double)av.x * xv.x + (double)av.y * xv.y + (double)av.z * xv.z + (double)av.w * xv.w;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) y[(long long)b * n + row] = (float)acc;
+}
+
+// lambda = v.y / v.v (Rayleigh quotient), res = ||y - lambda v|| / ||lambda v||, then v <- y / ||y||.
+// The residual is summed term by term: the shortcut ||y||^2 - lambda^2 cancels catastrophically.
+__global__ void __launch_bounds__(256) power_norm_kernel(float* __restrict__ v, const float* __restrict__ y, int n,
+                                                         float* __restrict__ lam, float* __restrict__ res) {
+  const int b = blockIdx.x;
+  float* V = v + (long long)b * n;
+  const float* Y = y + (long long)b * n;
+  __shared__ double red[3][8];
+  __shared__ double tot[3];
+  auto block_sum3 = [&](double a0, double a1, double a2) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      a0 += __shfl_xor_sync(0xffffffffu, a0, o);
+      a1 += __shfl_xor_sync(0xffffffffu, a1, o);
+      a2 += __shfl_xor_sync(0xffffffffu, a2, o);
+    }
+    __syncthreads();  // the previous round's totals have been read
+    if ((threadIdx.x & 31) == 0) {
+      red[0][threadIdx.x >> 5] = a0;
+      red[1][threadIdx.x >> 5] = a1;
+      red[2][threadIdx.x >> 5] = a2;
+    }
+    __syncthreads();
+    if (threadIdx.x < 3) {
+      double t = 0.0;
+      for (int w = 0; w < 8; ++w) t += red[threadIdx.x][w];
+      tot[threadIdx.x] = t;
+    }
+    __syncthreads();
+  };
+  double yy = 0.0, vy = 0.0, vv = 0.0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const double t = Y[i], u = V[i];
+    yy += t * t;
+    vy += t * u;
+    vv += u * u;
+  }
+  block_sum3(yy, vy, vv);
+  yy = tot[0];
+  vy = tot[1];
+  vv = tot[2];
+  const double l = vv > 0.0 ? vy / vv : 0.0;
+  double rr = 0.0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const double d = (double)Y[i] - l * (double)V[i];
+    rr += d * d;
+  }
+  block_sum3(rr, 0.0, 0.0);
+  rr = tot[0];
+  const double inv = yy > 0.0 ? 1.0 / sqrt(yy) : 0.0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) V[i] = (float)(Y[i] * inv);
+  if (threadIdx.x == 0) {
+    lam[b] = (float)l;
+    res[b] = (l > 0.0 && vv > 0.0) ? (float)(sqrt(rr) / (l * sqrt(vv))) : INFINITY;
+  }
+}
+
+// sigma = lambda_1 - c if the pair converged and stands well above the rest, else 0;  corr = lambda_1^{-1/p} - c^{-1/p}
+__global__ void deflate_decide_kernel(const float* __restrict__ lam, const float* __restrict__ res, int k, int n,
+                                      float damping, int p, float* __restrict__ neg_sigma, float* __restrict__ corr) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= k) return;
+  const float l1 = lam[b];
+  const float tr = (float)n * (1.f + damping);  // A has unit mean diagonal plus the damping
+  const float c = (tr - l1) / (float)(n - 1);
+  const bool ok = n > 1 && isfinite(l1) && isfinite(res[b]) && res[b] < 1e-5f && c > 0.f && l1 > 8.f * c;
+  neg_sigma[b] = ok ? -(l1 - c) : 0.f;
+  corr[b] = ok ? powf(l1, -1.f / p) - powf(c, -1.f / p) : 0.f;
+}
+
+// A_b += coef[b] v_b v_b^T  (skipped where coef is zero)
+__global__ void __launch_bounds__(256) rank1_update_kernel(float* __restrict__ a, const float* __restrict__ v,
+                                                           const float* __restrict__ coef, int n) {
+  const int b = blockIdx.y;
+  const float cf = coef[b];
+  if (cf == 0.f) return;
+  float* A = a + (long long)b * n * n;
+  const float* V = v + (long long)b * n;
+  const int n4 = n / 4;
+  const long long total = (long long)n * n4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / n4), c = (int)(i - (long long)r * n4) * 4;
+    const float vr = V[r];
+    const float4 vc = *reinterpret_cast<const float4*>(V + c);
+    float4 x = *reinterpret_cast<float4*>(A + (long long)r * n + c);
+    // cf * (v_r v_c): the product v_r v_c is the same bits at (r, c) and (c, r), so symmetry is kept exactly
+    x.x = fmaf(cf, vr * vc.x, x.x); x.y = fmaf(cf, vr * vc.y, x.y); x.z = fmaf(cf, vr * vc.z, x.z); x.w = fmaf(cf, vr * vc.w, x.w);
+    *reinterpret_cast<float4*>(A + (long long)r * n + c) = x;
+  }
+}
+
 // Per statistic: the scale that turns M_0^{-1/p} into A^{-1/p}, and the convergence status from the
 // distance max|I - M| gathered when the last M was produced (0 converged, 1 above tol, 2 non-finite).
+// 3: the statistic's spectrum reaches below the lower bound the schedule was built for (caller's bound too high).
 __global__ void finish_kernel(const unsigned int* __restrict__ resid, const float* __restrict__ sumsq_a,
-                              float* root_scale_lo, int* status, int k, int p, float tol) {
+                              float* root_scale_lo, int* status, float* norm_out, int k, int p, float tol, float damping,
+                              float lower_used) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= k) return;
   const float ub = sqrtf(fmaxf(sumsq_a[b], 1e-60f));
   root_scale_lo[b] = powf(ub, -1.f / p);
+  if (norm_out) norm_out[b] = ub;
   const float r = __uint_as_float(resid[b]);
-  if (status) status[b] = !isfinite(r) ? 2 : (r > tol ? 1 : 0);
+  int st = !isfinite(r) ? 2 : (r > tol ? 1 : 0);
+  if (st == 0 && damping / ub < lower_used * 0.999f) st = 3;
+  if (status) status[b] = st;
 }
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -194,7 +328,10 @@ static size_t per_statistic_bytes(int n) {
   // A (FP32) + seven FP16 hi/lo plane pairs (T, M x2, X x2, two powers of T) = 8 FP32-sized matrices
   return align_up((size_t)n * n * 4, 256) * 8;
 }
-static size_t small_bytes(int chunk) { return align_up((size_t)chunk * 4, 256) * 8 + align_up(sumsq_scratch_bytes(chunk), 256); }
+static size_t small_bytes(int chunk, int n) {
+  // sixteen per-statistic scalars, the reduction scratch, and two n-vectors per statistic (power iteration)
+  return align_up((size_t)chunk * 4, 256) * 16 + align_up(sumsq_scratch_bytes(chunk), 256) + 2 * align_up((size_t)chunk * n * 4, 256);
+}
 
 // Largest power of two s with s * bound <= 2^14: FP16 planes of s * x then stay a factor four below overflow
 // for |x| <= bound, and elements down to 2^-16 of the bound keep all 22 bits of the hi/lo pair.
@@ -208,7 +345,7 @@ extern "C" {
 
 size_t toner_inv_roots_workspace_bytes(int32_t chunk, int32_t n) {
   if (chunk <= 0 || n <= 0) return 0;
-  return toner::per_statistic_bytes(n) * (size_t)chunk + toner::small_bytes(chunk);
+  return toner::per_statistic_bytes(n) * (size_t)chunk + toner::small_bytes(chunk, n);
 }
 
 int toner_inv_roots_iterations(int32_t n, float damping, int32_t p) {
@@ -216,9 +353,21 @@ int toner_inv_roots_iterations(int32_t n, float damping, int32_t p) {
   return toner::default_iterations((double)damping / ((double)n * (1.0 + damping)), p);
 }
 
+int toner_inv_roots_iterations_for(float lower, int32_t p) {
+  if (!(lower > 0.f) || !(lower < 1.f) || p < 1) return 0;
+  return toner::default_iterations((double)lower, p);
+}
+
 int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
                     float* root_lo, float* root_hi, float* fro2_lo, int32_t* status, void* workspace,
                     size_t workspace_bytes, void* stream_) {
+  return toner_inv_roots_ex(ema, k, n, damping, p, q, iters, 0.f, root_lo, root_hi, fro2_lo, status, nullptr, workspace,
+                            workspace_bytes, stream_);
+}
+
+int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
+                       float lower, float* root_lo, float* root_hi, float* fro2_lo, int32_t* status, float* norm_out,
+                       void* workspace, size_t workspace_bytes, void* stream_) {
   using namespace toner;
   Context* ctx = context();
   if (!ctx) return kErrCuda;
@@ -230,7 +379,12 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
   if (p < 1 || p > 32 || (p & (p - 1))) return fail(kErrUnsupported, "inv_roots: root order p must be a power of two <= 32");
   if (q < 1 || q > p || (q & (q - 1))) return fail(kErrUnsupported, "inv_roots: q must be a power of two <= p");
   if (q > 1 && !root_hi) return fail(kErrArg, "inv_roots: root_hi is required when q > 1");
-  const double l0 = (double)damping / ((double)n * (1.0 + damping));
+  // Lower bound of the normalised spectrum the schedule is built for: the caller's (checked per statistic, status 3
+  // where it does not hold), else the bound that holds for every statistic, damping / (n (1 + damping)).
+  const double l_worst = (double)damping / ((double)n * (1.0 + damping));
+  if (lower != 0.f && !(lower > 0.f && lower < 1.f)) return fail(kErrArg, "inv_roots: lower must be 0 or inside (0, 1)");
+  const double l0 = (lower > 0.f && (double)lower > l_worst) ? (double)lower : l_worst;
+  const float lower_used = l0 > l_worst ? (float)l0 : 0.f;
   if (iters <= 0) iters = default_iterations(l0, p);
   if (iters < 2) return fail(kErrArg, "inv_roots: at least two iterations are required");
   const std::vector<NewtonStep> sched = newton_schedule(l0, p, iters, nullptr);
@@ -240,7 +394,7 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
   const size_t per = per_statistic_bytes(n);
   long long chunk_cap = 0;
   for (long long c = k; c >= 1; --c) {
-    if (per * (size_t)c + small_bytes((int)c) <= workspace_bytes) {
+    if (per * (size_t)c + small_bytes((int)c, n) <= workspace_bytes) {
       chunk_cap = c;
       break;
     }
@@ -280,8 +434,17 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
     unsigned int* resid = reinterpret_cast<unsigned int*>(small(2));
     float* scale_lo = small(3);
     float* fro_tmp = small(4);
-    float* partials = small(8);
-    TONER_CUDA(cudaMemsetAsync(w, 0, sm * 8, stream));
+    float* lam = small(5);
+    float* pres = small(6);
+    float* neg_sigma = small(7);
+    float* corr = small(8);
+    float* inv_r = small(9);
+    unsigned int* max_r = reinterpret_cast<unsigned int*>(small(10));
+    float* partials = small(16);
+    const size_t vec = align_up((size_t)kc * n * 4, 256);
+    float* pv = reinterpret_cast<float*>(w + sm * 16 + align_up(sumsq_scratch_bytes(kc), 256));
+    float* py = reinterpret_cast<float*>(reinterpret_cast<char*>(pv) + vec);
+    TONER_CUDA(cudaMemsetAsync(w, 0, sm * 16, stream));
 
     const float* C = ema + (long long)k0 * nn;
     const int t32 = (n + 31) / 32;
@@ -289,6 +452,20 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
     count_launch();
     damp_kernel<<<dim3(t32, t32, kc), 256, 0, stream>>>(C, A32, n, damping, trace);
     count_launch();
+    // dominant direction: six power-iteration steps, then deflate where they converged
+    power_start_kernel<<<dim3(8, kc), 256, 0, stream>>>(pv, n);
+    count_launch();
+    for (int pi = 0; pi < kPowerSteps; ++pi) {
+      gemv_kernel<<<dim3((n + 7) / 8, kc), 256, 0, stream>>>(A32, pv, py, n);
+      count_launch();
+      power_norm_kernel<<<kc, 256, 0, stream>>>(pv, py, n, lam, pres);
+      count_launch();
+    }
+    deflate_decide_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(lam, pres, kc, n, damping, p, neg_sigma, corr);
+    count_launch();
+    rank1_update_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(A32, pv, neg_sigma, n);
+    count_launch();
+    TONER_CUDA(cudaGetLastError());
     {
       int rc0 = sumsq_det(A32, kc, n, n, n, nn, partials, sumsq_a, stream);
       if (rc0) return rc0;
@@ -302,7 +479,8 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
     // D = (A planes) * (B planes)^T / (sa * sb): symmetric result, FP32-accurate; outputs as requested
     struct Out {
       float* d = nullptr;           // FP32 result
-      const float* alpha_a = nullptr;
+      const float* alpha_a = nullptr;  // optional per-statistic factors of the result
+      const float* alpha_b = nullptr;
       __half* s0 = nullptr; float s0_scale = 0.f;
       __half* s1 = nullptr; float s1_scale = 0.f, s1_a = 0.f, s1_b = 0.f;
       unsigned int* maxres = nullptr;
@@ -319,6 +497,7 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
       g.tri = 1; g.mirror = 1;
       g.alpha = (float)(1.0 / ((double)sa * (double)sb));
       g.alpha_a = o.alpha_a;
+      g.alpha_b = o.alpha_b;
       g.d = o.d; g.ldd = n; g.d_bs = nn;
       g.split0 = o.s0; g.split0_scale = o.s0_scale;
       g.split1 = o.s1; g.split1_scale = o.s1_scale; g.split1_aff_a = o.s1_a; g.split1_aff_b = o.s1_b;
@@ -340,23 +519,28 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
         x_bound = std::min(x_bound * sched[it].a, x_cap);
         if (last) {
           // fold ||A||_F^{-1/p} into the product; the distance of M from I was gathered when M was produced
-          finish_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(resid, sumsq_a, scale_lo, status ? status + k0 : nullptr, kc, p,
-                                                            0.05f);
+          finish_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(resid, sumsq_a, scale_lo, status ? status + k0 : nullptr,
+                                                            norm_out ? norm_out + k0 : nullptr, kc, p, 0.05f, damping,
+                                                            lower_used);
           count_launch();
           TONER_CUDA(cudaGetLastError());
+          float* R = root_lo + (long long)k0 * nn;
           Out o;
-          o.d = root_lo + (long long)k0 * nn;
+          o.d = R;
           o.alpha_a = scale_lo;
-          if (q > 1) {
-            o.s0 = Xb[xi];
-            o.s0_scale = plane_scale(root_bound);
-          }
           rc = sym_product(Xcur, s_x, Tcur, s_t, o, kPromoteX);
           if (rc) return rc;
-          rc = sumsq_det(root_lo + (long long)k0 * nn, kc, n, n, n, nn, partials, fro_tmp, stream);
+          // put the deflated direction back: A^{-1/p} = A'^{-1/p} + (lambda_1^{-1/p} - c^{-1/p}) v v^T
+          rank1_update_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(R, pv, corr, n);
+          count_launch();
+          TONER_CUDA(cudaGetLastError());
+          rc = sumsq_det(R, kc, n, n, n, nn, partials, fro_tmp, stream);
           if (rc) return rc;
+          if (q > 1) {  // operand planes of the finished root for the squarings below
+            rc = split16(R, nullptr, kc, n, n, n, nn, 0.f, 1.f, nullptr, max_r, Xb[xi], inv_r, stream);
+            if (rc) return rc;
+          }
           Xcur = Xb[xi];
-          s_x = plane_scale(root_bound);
           break;
         }
         Out o;
@@ -411,10 +595,16 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
       int have = 1;
       double bound = root_bound;
       int pi = 0;
+      s_x = 1.f;  // the root's planes carry per-statistic scales (inv_r), applied below
       while (have < q) {
+        const bool first = (have == 1);
         have *= 2;
         bound *= bound;
         Out o;
+        if (first) {
+          o.alpha_a = inv_r;
+          o.alpha_b = inv_r;
+        }
         if (have == q) {
           o.d = root_hi + (long long)k0 * nn;
         } else {

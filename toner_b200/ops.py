@@ -238,12 +238,20 @@ def inv_roots_workspace_bytes(chunk: int, n: int) -> int:
     return _lib.load().toner_inv_roots_workspace_bytes(chunk, n)
 
 
+def inv_roots_iterations_for(lower: float, p: int) -> int:
+    """Newton steps needed when the normalised spectrum is known to lie in [lower, 1]."""
+    return _lib.load().toner_inv_roots_iterations_for(lower, p)
+
+
 def inv_roots(ema: torch.Tensor, damping: float, p: int, q: int = 1, *, iters: int = 0,
               root_lo: Optional[torch.Tensor] = None, root_hi: Optional[torch.Tensor] = None,
               fro2_lo: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
-              workspace: Optional[torch.Tensor] = None, chunk: Optional[int] = None):
+              workspace: Optional[torch.Tensor] = None, chunk: Optional[int] = None, lower: float = 0.0,
+              norms: Optional[torch.Tensor] = None):
     """A^(-1/p) and A^(-q/p) of the damped, trace-normalised statistics (toner_inv_roots).
 
+    ``lower``: a lower bound of the normalised spectrum valid for every statistic (0: the bound that always
+    holds); ``norms`` (k,) receives ||A'_b||_F, from which the next call's bound can be derived.
     Returns (root_lo, root_hi or None, fro2_lo, status); nothing is synchronised."""
     _need_cuda(ema)
     if ema.ndim == 2:
@@ -265,9 +273,9 @@ def inv_roots(ema: torch.Tensor, damping: float, p: int, q: int = 1, *, iters: i
             per = inv_roots_workspace_bytes(1, n)
             chunk = max(1, min(k, (4 << 30) // per))
         workspace = torch.empty(inv_roots_workspace_bytes(chunk, n), device=dev, dtype=torch.uint8)
-    check(_lib.load().toner_inv_roots(ema.data_ptr(), k, n, damping, p, q, iters, root_lo.data_ptr(), _ptr(root_hi),
-                                      fro2_lo.data_ptr(), status.data_ptr(), workspace.data_ptr(), workspace.numel(),
-                                      _stream()), "toner_inv_roots")
+    check(_lib.load().toner_inv_roots_ex(ema.data_ptr(), k, n, damping, p, q, iters, lower, root_lo.data_ptr(),
+                                         _ptr(root_hi), fro2_lo.data_ptr(), status.data_ptr(), _ptr(norms),
+                                         workspace.data_ptr(), workspace.numel(), _stream()), "toner_inv_roots_ex")
     return root_lo, root_hi, fro2_lo, status
 
 
