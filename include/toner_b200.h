@@ -117,6 +117,15 @@ int toner_syrk_upper(const void* const* x_list, const void* x_base, int64_t x_ba
                      int32_t rows, int32_t n, int64_t ld, float* out, int32_t mode, float beta, float gamma,
                      void* stream);
 
+/* Sampled-row capture: dst[(b*count + j), :] = BF16(x[b, positions[j], :]) for a (batch, seq, n) activation tensor
+ * (BF16, or FP32 when x_is_fp32: rounded to BF16 as autocast would), `positions` a DEVICE array of `count` token
+ * indices (toner's head-then-stride sample).  dst is (batch*count, n) BF16, typically a slice of the statistic's
+ * row buffer.  Strides in elements; rows 16-byte aligned; n a multiple of 8; positions are not range-checked.
+ * Replaces x.index_select(1, positions) + copy in the capture hooks (src/toner/fast/adapter.py:398-402,
+ * src/toner/statistics.py:68-80) and the row-gather capture kernel (reproduce/marin/ops.py:10-27). */
+int toner_gather_rows(const void* x, int32_t x_is_fp32, int32_t batch, int32_t seq, int32_t n, int64_t batch_stride,
+                      int64_t row_stride, const int32_t* positions, int32_t count, void* dst, void* stream);
+
 /* C_b <- beta*C_b + gamma*S_b with S_b read from its packed upper triangle and mirrored.
  * Replaces unpack_ema_ (src/toner/fast/syrk.py:220-247); general-path EMA src/toner/reference.py:79. */
 int toner_unpack_ema(const float* packed, float* ema, int32_t k, int32_t n, float beta, float gamma, void* stream);

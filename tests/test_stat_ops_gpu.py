@@ -105,3 +105,21 @@ def test_split16_affine_source(ops):
     rec = (planes[0].double() + planes[1].double()) * inv.double()[:, None, None]
     assert ((rec - want.double()).abs().amax() / want.abs().amax()).item() < 2 ** -21
     assert planes[0].float().abs().amax().item() < 2 ** 14
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_gather_rows_matches_index_select(ops, dtype):
+    """Sampled-row capture: bit-exact against index_select + BF16 rounding, also from a strided view."""
+    from toner_b200.statistics import sample_positions
+    g = torch.Generator(device="cuda").manual_seed(2)
+    batch, seq, n = 3, 200, 264
+    wide = torch.randn(batch, seq, n + 24, device="cuda", generator=g).to(dtype)
+    x = wide[:, :, 8:8 + n]                              # rows 16-byte aligned, not contiguous
+    pos = sample_positions(seq, 32, 16)
+    positions = torch.tensor(pos, device="cuda", dtype=torch.int32)
+    dst = torch.full((batch * len(pos), n), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.gather_rows(x, positions, dst)
+    ops.assert_healthy()
+    want = x.index_select(1, positions.long()).to(torch.bfloat16).reshape(batch * len(pos), n)
+    assert torch.equal(dst, want)
+    assert orc.sample_positions(seq, 32, 16) == pos

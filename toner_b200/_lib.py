@@ -70,6 +70,7 @@ SIGNATURES = {
     "toner_ns_polar": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _sz, _vp]),
     "toner_sumsq_scratch_bytes": (C.c_size_t, [_i32]),
     "toner_sumsq": (C.c_int, [_vp, _i32, _i32, _i32, _i64, _i64, _vp, _vp, _vp]),
+    "toner_gather_rows": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _i64, _i64, _vp, _i32, _vp, _vp]),
     "toner_sumsq_static_max_batch": (C.c_int, []),
     "toner_sumsq_static": (C.c_int, [_vp, _i32, _i32, _i32, _i64, _i64, _vp, _vp]),
     "toner_muont_momentum": (C.c_int, [_vp, _vp, _vp, _i32, _i64, _f32, _i32, _vp, _vp]),

@@ -65,6 +65,24 @@ size_t sumsq_scratch_bytes(int batch);
 int sumsq_det(const float* x, int batch, int rows, int cols, long long ld, long long bs, float* scratch, float* out,
               cudaStream_t stream);
 
+// Block-wide max of non-negative values into one FP32-bits accumulator: one atomic per block, and none when the
+// accumulator already holds as much (thousands of blocks share a few addresses; per-warp atomics serialise in L2).
+// Every thread of a 256-thread block calls this.
+__device__ __forceinline__ void block_atomic_max(float v, unsigned int* acc) {
+  __shared__ float warp_max[8];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float m = warp_max[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, warp_max[w]);
+    const unsigned int bits = __float_as_uint(m);
+    if (bits > *reinterpret_cast<volatile unsigned int*>(acc)) atomicMax(acc, bits);
+  }
+}
+
 // k-blocks per accumulation chain used for FP32-accurate (split-precision) products
 constexpr int kPromoteAccurate = 2;
 // chain length where a relative error of 1e-6 only propagates linearly (products applied to X, W, gradients)

@@ -1,4 +1,5 @@
 // Statistic path: upper-triangle SYRK (on the tcgen05 GEMM), packed-triangle EMA, FP16 hi/lo splitting.
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <mutex>
@@ -40,6 +41,33 @@ __global__ void __launch_bounds__(256) unpack_ema_kernel(const float* __restrict
   }
 }
 
+// ------------------------------------------------------------------ sampled-row capture
+// dst[(b * count + j), :] = bf16(x[b, positions[j], :]): the rows of the sampled token positions of one microbatch,
+// written straight into the statistic's row buffer.  One warp per row, 16-byte accesses.
+template <typename T>
+__global__ void __launch_bounds__(256) gather_rows_kernel(const T* __restrict__ x, long long batch_stride, long long row_stride,
+                                                          const int* __restrict__ positions, int count, int n, int rows_total,
+                                                          __nv_bfloat16* __restrict__ dst) {
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows_total) return;
+  const int b = row / count, j = row - b * count;
+  const T* src = x + (long long)b * batch_stride + (long long)positions[j] * row_stride;
+  __nv_bfloat16* out = dst + (long long)row * n;
+  for (int c = lane * 8; c < n; c += 256) {
+    if constexpr (sizeof(T) == 2) {
+      *reinterpret_cast<uint4*>(out + c) = *reinterpret_cast<const uint4*>(src + c);
+    } else {
+      const float4 lo = *reinterpret_cast<const float4*>(src + c), hi = *reinterpret_cast<const float4*>(src + c + 4);
+      __nv_bfloat162 p0 = __floats2bfloat162_rn(lo.x, lo.y), p1 = __floats2bfloat162_rn(lo.z, lo.w);
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(hi.x, hi.y), p3 = __floats2bfloat162_rn(hi.z, hi.w);
+      uint4 u;
+      u.x = *reinterpret_cast<uint32_t*>(&p0); u.y = *reinterpret_cast<uint32_t*>(&p1);
+      u.z = *reinterpret_cast<uint32_t*>(&p2); u.w = *reinterpret_cast<uint32_t*>(&p3);
+      *reinterpret_cast<uint4*>(out + c) = u;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ max |aff_a*I + aff_b*x| per matrix
 __global__ void __launch_bounds__(256) maxabs_kernel(const float* __restrict__ x, const float* const* __restrict__ x_list,
                                                      int rows, int cols, long long ld, long long bs, float aff_a,
@@ -53,9 +81,7 @@ __global__ void __launch_bounds__(256) maxabs_kernel(const float* __restrict__ x
     const float v = aff_b * X[(long long)r * ld + c] + (r == c ? aff_a : 0.f);
     m = fmaxf(m, fabsf(v));
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if ((threadIdx.x & 31) == 0) atomicMax(out + b, __float_as_uint(m));
+  block_atomic_max(m, out + b);
 }
 
 // scale = 2^(13 - floor(log2 maxabs)); 1 when the matrix is all zero or its maximum is not finite
@@ -265,6 +291,30 @@ int toner_syrk_upper(const void* const* x_list, const void* x_base, int64_t x_ba
     }
   }
   return launch_gemm(d, static_cast<cudaStream_t>(stream));
+}
+
+int toner_gather_rows(const void* x, int32_t x_is_fp32, int32_t batch, int32_t seq, int32_t n, int64_t batch_stride,
+                      int64_t row_stride, const int32_t* positions, int32_t count, void* dst, void* stream) {
+  using namespace toner;
+  if (!context()) return kErrCuda;
+  if (!x || !positions || !dst || batch <= 0 || seq <= 0 || n <= 0 || count <= 0) return fail(kErrArg, "gather_rows: bad arguments");
+  const int elt = x_is_fp32 ? 4 : 2;
+  if (n % 8 != 0 || (row_stride * elt) % 16 != 0 || (batch_stride * elt) % 16 != 0 ||
+      (reinterpret_cast<uintptr_t>(x) & 15u) != 0 || (reinterpret_cast<uintptr_t>(dst) & 15u) != 0)
+    return fail(kErrArg, "gather_rows: rows must be 16-byte aligned and n a multiple of 8");
+  const long long rows = (long long)batch * count;
+  if (rows > 0x7fffffffLL) return fail(kErrArg, "gather_rows: too many rows");
+  const int blocks = (int)((rows + 7) / 8);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (x_is_fp32)
+    gather_rows_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const float*>(x), batch_stride, row_stride, positions, count, n,
+                                                     (int)rows, static_cast<__nv_bfloat16*>(dst));
+  else
+    gather_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), batch_stride, row_stride,
+                                                             positions, count, n, (int)rows, static_cast<__nv_bfloat16*>(dst));
+  count_launch();
+  TONER_CUDA(cudaGetLastError());
+  return 0;
 }
 
 int toner_sumsq_static_max_batch(void) { return toner::kStaticSumsqMaxBatch; }

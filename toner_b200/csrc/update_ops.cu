@@ -47,9 +47,7 @@ __global__ void __launch_bounds__(256) muont_momentum_kernel(const float* const*
   float4* U = reinterpret_cast<float4*>(u + (long long)b * per);
   const long long n4 = per / 4;
   float mx = 0.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
-    const float4 g = G[i];
-    float4 mm = M[i];
+  auto update = [&](const float4 g, float4 mm, long long i) {
     mm.x = fmaf(mu, mm.x, g.x); mm.y = fmaf(mu, mm.y, g.y); mm.z = fmaf(mu, mm.z, g.z); mm.w = fmaf(mu, mm.w, g.w);
     M[i] = mm;
     float4 d = mm;
@@ -58,10 +56,18 @@ __global__ void __launch_bounds__(256) muont_momentum_kernel(const float* const*
     }
     U[i] = d;
     mx = fmaxf(fmaxf(fmaxf(mx, fabsf(d.x)), fabsf(d.y)), fmaxf(fabsf(d.z), fabsf(d.w)));
+  };
+  // four independent 16-byte loads in flight per thread before the first store
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + stride < n4; i += 2 * stride) {
+    const float4 g0 = G[i], g1 = G[i + stride];
+    const float4 m0 = M[i], m1 = M[i + stride];
+    update(g0, m0, i);
+    update(g1, m1, i + stride);
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  if ((threadIdx.x & 31) == 0 && maxabs) atomicMax(maxabs + b, __float_as_uint(mx));
+  if (i < n4) update(G[i], M[i], i);
+  if (maxabs) block_atomic_max(mx, maxabs + b);
 }
 
 // c1[b] = lr wd n / ||R||_F^2 ,  c2[b] = lr scale sqrt(n) / ||R||_F   with ||R||_F^2 = fro2[first + b*step]
@@ -119,9 +125,7 @@ __global__ void __launch_bounds__(256) adamt_ratio_kernel(const float* __restric
     N[i] = nn;
     mx = fmaxf(fmaxf(fmaxf(mx, fabsf(nn.x)), fabsf(nn.y)), fmaxf(fabsf(nn.z), fabsf(nn.w)));
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  if ((threadIdx.x & 31) == 0 && maxabs) atomicMax(maxabs + b, __float_as_uint(mx));
+  if (maxabs) block_atomic_max(mx, maxabs + b);
 }
 
 // c1[b] = lr wd n / ||R||_F^2 ;  c2[b] = -lr ||U||_F / max(||U R||_F, 1e-30)

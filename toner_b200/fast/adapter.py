@@ -21,6 +21,7 @@ import torch
 import torch.distributed as dist
 from torch import nn
 
+from .. import ops
 from ..statistics import sample_positions
 
 
@@ -199,7 +200,7 @@ class _FastToner(torch.optim.Optimizer):
         self._input_signatures = {}
         self._hooks = []
         self._device = device
-        self._positions = torch.tensor(positions, device=device, dtype=torch.long)
+        self._positions = torch.tensor(positions, device=device, dtype=torch.int32)
         self._rows_per_microbatch = micro_batch_size * len(positions)
         local_rows = self._rows_per_microbatch * accumulation_steps
         args = SimpleNamespace(
@@ -268,7 +269,10 @@ class _FastToner(torch.optim.Optimizer):
                 self._input_signatures[(layer, stat)] = signature
                 lo = self._microbatches * self._rows_per_microbatch
                 dst = getattr(self._buffers[layer], f"input_rows_{stat}")[lo: lo + self._rows_per_microbatch]
-                dst.view(self.micro_batch_size, -1, module.in_features).copy_(x.index_select(1, self._positions))
+                if x.stride(2) != 1 or (x.stride(1) * x.element_size()) % 16 or (x.stride(0) * x.element_size()) % 16 \
+                        or x.data_ptr() % 16:
+                    x = x.contiguous()
+                ops.gather_rows(x, self._positions, dst)   # sampled rows straight into the statistic's row buffer
 
         return hook
 

@@ -184,6 +184,22 @@ def syrk_upper(x, out: torch.Tensor, mode: int = PACKED, beta: float = 0.0, gamm
                                out.data_ptr(), mode, beta, gamma, _stream()), "toner_syrk_upper")
 
 
+def gather_rows(x: torch.Tensor, positions: torch.Tensor, dst: torch.Tensor) -> None:
+    """dst[(b*P + j), :] = bf16(x[b, positions[j], :]) for a (batch, seq, n) BF16 or FP32 tensor (toner_gather_rows).
+    ``positions`` is an int32 device tensor; ``dst`` a contiguous (batch*P, n) BF16 buffer (slice)."""
+    _need_cuda(x, positions, dst)
+    if x.ndim != 3 or x.stride(2) != 1 or x.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("gather_rows takes a (batch, seq, n) BF16 or FP32 tensor with contiguous features")
+    if positions.dtype != torch.int32 or dst.dtype != torch.bfloat16 or not dst.is_contiguous():
+        raise ValueError("gather_rows needs int32 positions and a contiguous BF16 destination")
+    batch, seq, n = x.shape
+    count = positions.numel()
+    if dst.numel() != batch * count * n:
+        raise ValueError("destination does not hold batch * positions rows")
+    check(_lib.load().toner_gather_rows(x.data_ptr(), int(x.dtype == torch.float32), batch, seq, n, x.stride(0), x.stride(1),
+                                        positions.data_ptr(), count, dst.data_ptr(), _stream()), "toner_gather_rows")
+
+
 def unpack_ema(packed: torch.Tensor, ema: torch.Tensor, beta: float, gamma: float) -> None:
     """ema <- beta*ema + gamma*S, S given as packed upper triangles (toner_unpack_ema)."""
     _need_cuda(packed, ema)
