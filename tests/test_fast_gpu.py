@@ -8,6 +8,12 @@ from oracle import toner_oracle as orc
 
 pytestmark = pytest.mark.gpu
 HID, MLP, SEQ, MB, ACC, LAYERS = 256, 512, 64, 2, 2, 2
+# Adam's eps for the parity run.  With the adapter's default (1e-15) the early updates are num / sqrt(v) on entries
+# whose v is nearly zero: the first step is sign(g R), later ones have unbounded outliers where g R_old vanishes but
+# g R_new does not, and one such entry rescales a whole matrix through ||U|| / ||U R||.  Both sides then amplify
+# last-bit differences to 1e-2..1e-1 on the weights.  A comparable eps (gradients here are ~1e-3) keeps the same
+# arithmetic on every path and makes the comparison meaningful.
+ADAM_EPS = 1e-4
 
 
 @pytest.fixture()
@@ -44,7 +50,7 @@ def role_modules(block, layout):
 
 @pytest.mark.parametrize("layout,kind", [("llama", "muont"), ("nanogpt", "muont"), ("llama", "adamt")])
 def test_two_steps_match_oracle(fast, layout, kind):
-    extra = dict(ns_steps=2) if kind == "muont" else dict(betas=(0.9, 0.95))
+    extra = dict(ns_steps=2) if kind == "muont" else dict(betas=(0.9, 0.95), eps=ADAM_EPS)
     stack, opt = make(fast, layout, kind, **extra)
     try:
         positions = orc.sample_positions(SEQ, 8, 4)
@@ -79,12 +85,10 @@ def test_two_steps_match_oracle(fast, layout, kind):
                 if kind == "muont":
                     after = orc.muont_step(before, g, st, lr=0.02, weight_decay=0.1, momentum=0.95, ns_steps=2, ns_mode="tpu")
                 else:
-                    after = orc.adamt_step(before, g, st, lr=2e-3, weight_decay=0.1, betas=(0.9, 0.95), eps=1e-15)
+                    after = orc.adamt_step(before, g, st, lr=2e-3, weight_decay=0.1, betas=(0.9, 0.95), eps=ADAM_EPS)
                 ref_w[id(m)] = after
                 worst = max(worst, orc.rel_fro(m.weight.detach().cpu(), after))
-            # AdamT's first updates are close to sign(g R): entries of g R near zero flip under any factor
-            # difference, and each flip moves a weight by 2 lr.  With lr/|w| ~ 0.1 here that is ~1e-2 on the weights.
-            assert worst < (2e-3 if kind == "muont" else 3e-2), (layout, kind, step, worst)
+            assert worst < 2e-3, (layout, kind, step, worst)
             if kind == "adamt":  # the moments themselves are smooth functions of the factors
                 for li, k, m in params[:3]:
                     role = [r for r, info in opt._core.roles.items() if any(w is m.weight for w in info["all"])][0]

@@ -74,12 +74,24 @@ __global__ void __launch_bounds__(256) maxabs_kernel(const float* __restrict__ x
                                                      float aff_b, unsigned int* __restrict__ out) {
   const int b = blockIdx.y;
   const float* X = x_list ? x_list[b] : x + (long long)b * bs;
-  const long long total = (long long)rows * cols;
   float m = 0.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
-    const float v = aff_b * X[(long long)r * ld + c] + (r == c ? aff_a : 0.f);
-    m = fmaxf(m, fabsf(v));
+  const bool vec = (cols % 4 == 0) && (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(X) & 15u) == 0);
+  if (vec) {
+    const int c4 = cols / 4;
+    const long long total4 = (long long)rows * c4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+      const int r = (int)(i / c4), c = (int)(i - (long long)r * c4) * 4;
+      const float4 q = *reinterpret_cast<const float4*>(X + (long long)r * ld + c);
+      const float v[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) m = fmaxf(m, fabsf(fmaf(aff_b, v[e], (c + e) == r ? aff_a : 0.f)));
+    }
+  } else {
+    const long long total = (long long)rows * cols;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+      const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
+      m = fmaxf(m, fabsf(fmaf(aff_b, X[(long long)r * ld + c], r == c ? aff_a : 0.f)));
+    }
   }
   block_atomic_max(m, out + b);
 }
@@ -142,13 +154,27 @@ __global__ void __launch_bounds__(256) sumsq_partial_kernel(const float* __restr
   const int b = blockIdx.y;
   const float* X = x + (long long)b * bs;
   const long long total = (long long)rows * cols;
-  const long long per = (total + gridDim.x - 1) / gridDim.x;
-  const long long lo = per * blockIdx.x, hi = (lo + per < total) ? lo + per : total;
   float s = 0.f;
-  for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-    const long long r = i / cols, c = i - r * cols;
-    const float v = X[r * ld + c];
-    s = fmaf(v, v, s);
+  if (ld == cols && total % 4 == 0 && (reinterpret_cast<uintptr_t>(X) & 15u) == 0) {
+    // contiguous matrix: 16-byte loads, four running sums per thread, combined in a fixed order
+    const long long total4 = total / 4;
+    const long long per = (total4 + gridDim.x - 1) / gridDim.x;
+    const long long lo = per * blockIdx.x, hi = (lo + per < total4) ? lo + per : total4;
+    const float4* X4 = reinterpret_cast<const float4*>(X);
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const float4 v = X4[i];
+      s0 = fmaf(v.x, v.x, s0); s1 = fmaf(v.y, v.y, s1); s2 = fmaf(v.z, v.z, s2); s3 = fmaf(v.w, v.w, s3);
+    }
+    s = (s0 + s1) + (s2 + s3);
+  } else {
+    const long long per = (total + gridDim.x - 1) / gridDim.x;
+    const long long lo = per * blockIdx.x, hi = (lo + per < total) ? lo + per : total;
+    for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      const long long r = i / cols, c = i - r * cols;
+      const float v = X[r * ld + c];
+      s = fmaf(v, v, s);
+    }
   }
   __shared__ float red[8];
 #pragma unroll

@@ -212,7 +212,21 @@ def bench_update(a):
     ms, best = timed(lambda: ops.muont_momentum(gp, m, u, 0.95, True, mx), a.warmup, a.reps, small)
     report("muont_momentum", {"count": a.count, "per": a.per}, ms, best, bytes_=16 * a.count * a.per)
     ms, best = timed(lambda: ops.apply_delta(wp, u), a.warmup, a.reps, small)
-    return report("apply_delta", {"count": a.count, "per": a.per}, ms, best, bytes_=12 * a.count * a.per)
+    report("apply_delta", {"count": a.count, "per": a.per}, ms, best, bytes_=12 * a.count * a.per)
+    side = int(math.isqrt(a.per))
+    if side * side == a.per and side % 8 == 0:
+        x = u.view(a.count, side, side)
+        planes = torch.empty(2, a.count, side, side, device="cuda", dtype=torch.float16)
+        inv = torch.empty(a.count, device="cuda")
+        ms, best = timed(lambda: ops.split16(x, planes=planes, inv_scale=inv, maxabs=mx), a.warmup, a.reps, small)
+        report("split16", {"count": a.count, "per": a.per}, ms, best, bytes_=8 * a.count * a.per)
+        ms, best = timed(lambda: ops.split16(x, planes=planes, inv_scale=inv, scratch=mx), a.warmup, a.reps, small)
+        report("maxabs+split16", {"count": a.count, "per": a.per}, ms, best, bytes_=12 * a.count * a.per)
+        out = torch.empty(a.count, device="cuda")
+        ws = torch.empty(ops.sumsq_scratch_bytes(a.count), device="cuda", dtype=torch.uint8)
+        ms, best = timed(lambda: ops.sumsq(x, out=out, scratch=ws), a.warmup, a.reps, small)
+        report("sumsq", {"count": a.count, "per": a.per}, ms, best, bytes_=4 * a.count * a.per)
+    return None
 
 
 def main():
