@@ -82,8 +82,12 @@ class ClockSampler:
         return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
 
 
-# DRAM bytes per launch of the dominant kernel, from the ncu capture summarised under profiles/ (null: not captured)
-TRAFFIC = {"roots": None, "update": None, "stats": None}
+# DRAM bytes per launch of the dominant kernel from the ncu capture summarised in profiles/gemm_tcgen05_kernel_ncu.md:
+# the factor engine's M-update product moved 564 MB (dram__bytes_read + write) for 8 statistics of 2048^2; traffic is
+# proportional to the operand size (every operand byte is read from DRAM once), so a launch over k statistics of
+# width n moves 564e6 * k n^2 / (8 * 2048^2).
+def roots_traffic(k: int, n: int) -> int:
+    return int(564e6 * k * n * n / (8 * 2048 * 2048))
 
 
 def tri_fraction(n: int, bm: int = 128, bn: int = 256) -> float:
@@ -219,7 +223,7 @@ def run_ours(args) -> None:
         if top:
             a = per_phase[top]["tflops_per_gpu"]
             roof = {"bound": "tensor", "kernel": "gemm_tcgen05_kernel", "phase": top, "achieved": a, "peak": pk["tflops"],
-                    "unit": "TFLOP/s", "frac": round(a / pk["tflops"], 4), "traffic": TRAFFIC.get(top),
+                    "unit": "TFLOP/s", "frac": round(a / pk["tflops"], 4), "traffic": (roots_traffic(layers // world, mlp) if top == "roots" else None),
                     "peak_source": pk["source"] + " (sustained cuBLAS BF16: the kernel runs inside a long step)",
                     "note": "achieved = algorithmic single-pass flops of the phase / its CUDA-event time on the launching "
                             "stream; the phase is >97% this kernel by ncu share"}
