@@ -96,6 +96,12 @@ def tri_fraction(n: int, bm: int = 128, bn: int = 256) -> float:
     return sum(max(0, tn - (i * bm) // bn) for i in range(tm)) / (tm * tn)
 
 
+def workload_config(layers: int, hidden: int, mlp: int, sequences: int) -> dict:
+    rows = sequences * len(list(range(HEAD)) + list(range(HEAD + 1, SEQ_LEN, STRIDE)))
+    return {"workload": f"MuonT step, {layers}-layer Llama-style stack d={hidden} mlp={mlp}, "
+                        f"{sequences}x{SEQ_LEN} tokens per update ({rows} sampled rows)"}
+
+
 def sampled_positions() -> int:
     return len(list(range(HEAD)) + list(range(HEAD + 1, SEQ_LEN, STRIDE)))
 
@@ -240,10 +246,9 @@ def run_ours(args) -> None:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3), "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16 operands / fp16 hi-lo splits, fp32 accumulate",
             "data": "synthetic",
-            "config": {"workload": f"FastMuonT step, {layers}-layer Llama-style stack d={hidden} mlp={mlp}, "
-                                   f"{sequences}x{SEQ_LEN} tokens per update ({local_rows * world} sampled rows)",
-                       "parallelism": f"layer-sharded x{world}", "l2": "inputs larger than L2",
-                       "entry": "engine seam: rows resident in the row buffers, begin()+step()"},
+            "config": dict(workload_config(layers, hidden, mlp, sequences), parallelism=f"layer-sharded x{world}",
+                           l2="inputs larger than L2",
+                           entry="engine seam: rows resident in the row buffers, begin()+step()"),
             "e2e": ({"value": round(e2e_ms, 3), "unit": "ms", "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4}
                     if e2e_ms is not None else None),
             "gpu_launches": int(launches),
@@ -313,8 +318,8 @@ def run_reference(args) -> None:
             "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": f"MuonT general path (CPU restatement of the reference), {args.layers}-layer "
-                                   f"Llama-style stack d={args.hidden} mlp={args.mlp}, {args.sequences}x{SEQ_LEN} tokens"},
+            "config": dict(workload_config(args.layers, args.hidden, args.mlp, args.sequences),
+                           entry="reference general path (eigh factors, FP32 Newton-Schulz) restated on CPU, host cores"),
             "cpu_baseline": base,
             "e2e": {"value": ms, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
