@@ -153,3 +153,26 @@ def test_dominant_direction_is_deflated(ops):
     assert orc.rel_fro(lo[0].cpu(), orc.inverse_root_truth(c, 0.125, DAMPING)) < 1e-4
     assert orc.rel_fro(hi[0].cpu(), orc.inverse_root_truth(c, 0.5, DAMPING)) < 5e-4
     assert torch.equal(lo[0], lo[0].T)
+
+
+def test_repair_round_when_the_bound_no_longer_holds(ops):
+    """FactorSet: a statistic that grows a dominant direction between two steps breaks the bound derived from the
+    previous step; the device flags it, the repair round refactors it with the bound that always holds, and no
+    eigendecomposition fallback is needed."""
+    from toner_b200 import core
+    n = 512
+    f = core.FactorSet(2, n, torch.device("cuda"), (0.5, 0.125), DAMPING)
+    f.ema.copy_(torch.stack([spd(n, 10.0, 1), spd(n, 10.0, 2)]))
+    f.compute()
+    assert f.finish() == 0 and f.lower > 0
+    # two strong directions: only one can be deflated, so ||A'||_F jumps far above what the bound allows for
+    g = torch.Generator().manual_seed(3)
+    u, v = torch.randn(n, 1, generator=g), torch.randn(n, 1, generator=g)
+    f.ema[1] += ((u @ u.T) + (v @ v.T)).cuda() * 50.0
+    f.compute()
+    assert f.finish() == 0
+    assert f.repairs == 1 and f.fallbacks == 0
+    for b in range(2):
+        c = f.ema[b].cpu()
+        assert orc.rel_fro(f.root_lo[b].cpu(), orc.inverse_root_truth(c, 0.125, DAMPING)) < 5e-4
+        assert orc.rel_fro(f.root_hi[b].cpu(), orc.inverse_root_truth(c, 0.5, DAMPING)) < 2e-3

@@ -111,6 +111,7 @@ class FactorSet:
         self.workspace = self.scratch.bytes_like("inv_roots", ops.inv_roots_workspace_bytes(chunk, n), device)
         self.iterations = ops.inv_roots_iterations(n, self.damping, self.p)
         self.fallbacks = 0
+        self.repairs = 0
 
     # -- which stored root serves a given strength
     def _is_hi(self, strength: float) -> bool:
@@ -177,6 +178,17 @@ class FactorSet:
                 self.lower = hint
         if not bad:
             return 0
+        # Repair round (the reference's engine repairs flagged roots before it falls back,
+        # src/toner/fast/engine.py:646-713): the flagged statistics once more with the bound that always holds.
+        self.repairs += len(bad)
+        idx = torch.tensor(bad, device=self.device)
+        sub = self.ema.index_select(0, idx).contiguous()
+        lo, hi, fro2, st = ops.inv_roots(sub, self.damping, self.p, self.q)
+        self.root_lo.index_copy_(0, idx, lo)
+        if self.q > 1:
+            self.root_hi.index_copy_(0, idx, hi)
+        still = [b for b, s in zip(bad, st.tolist()) if s != 0]   # host sync: this path is the exception
+        bad = still
         self.fallbacks += len(bad)
         for i in bad:
             c = self.ema[i]
@@ -189,7 +201,7 @@ class FactorSet:
                 self.root_hi[i] = ((vec * (unit + self.damping).pow(-float(self.q) / self.p)) @ vec.T).float()
         ops.sumsq(self.root_lo, out=self.fro2_lo, scratch=self.scratch.bytes_like("sumsq", ops.sumsq_scratch_bytes(self.k), self.device))
         self._split()
-        return len(bad)
+        return len(bad) if bad else 0
 
 
 class MatrixGroup:

@@ -154,7 +154,6 @@ class FastTonerCore:
                                     gathered=gathered, all_ptrs=ops.pointer_table(all_w))
         self.t = 0
         self.steps = 0
-        self.extra = 0
         self.timing: Dict[str, float] = {}
         self.gpu_ms: Dict[str, float] = {}
         self.main_stream = torch.cuda.current_stream(device)
@@ -171,6 +170,11 @@ class FastTonerCore:
     @property
     def fallbacks(self) -> int:
         return sum(g.factors.fallbacks for g in self.groups.values())
+
+    @property
+    def extra(self) -> int:
+        """Statistics that needed a repair round (factored again with the bound that always holds)."""
+        return sum(g.factors.repairs for g in self.groups.values())
 
     # ------------------------------------------------------------------ statistics (side stream)
     def _stats(self) -> None:
