@@ -8,8 +8,8 @@ Work split on one multi-GPU box (one process per GPU):
   reduce-scatter of packed FP32 triangles, issued chunk by chunk so that it overlaps the SYRK of the
   next chunk), keep the statistic EMAs, compute the inverse-root factors and the parameter changes of
   their layers;
-* the changes are all-gathered per projection role (NCCL, asynchronous, overlapping the next role's
-  products) and every rank adds all of them to its replica of the weights.
+* the changes of all roles sit in one flat buffer per rank; one NCCL all-gather after the last role moves
+  them, and every rank adds all of them to its replica of the weights.
 
 ``begin()`` runs statistics and factors on a high-priority side stream so that they overlap the
 last backward pass; ``step()`` joins it.  The only host synchronisation in ``step()`` is the wait
@@ -135,10 +135,19 @@ class FastTonerCore:
             roles.setdefault(role, []).append((layer, name, p))
         self.roles = {}
         lo_layer = sum(self.layer_counts[:rank])
+        plan = []
         for role, items in roles.items():
             items.sort(key=lambda it: it[0])
             if [it[0] for it in items] != list(range(layers)):
                 raise ValueError(f"role {role} must have exactly one matrix per layer")
+            plan.append((role, items))
+        # One flat buffer holds this rank's changes of every role, so that a single all-gather moves them all
+        # (one large NCCL transfer after the last role instead of seven that fight the GEMMs for SMs).
+        sizes = [self.per_layers * items[0][2].numel() for _, items in plan]
+        self.delta_flat = torch.empty(sum(sizes), device=device, dtype=torch.float32)
+        self.gathered_flat = (torch.empty(world, sum(sizes), device=device, dtype=torch.float32) if world > 1 else None)
+        offset = 0
+        for (role, items), size in zip(plan, sizes):
             all_w = [it[2] for it in items]
             own_w = all_w[lo_layer: lo_layer + self.per_layers]
             stat_kind = ROLE_KIND[role]
@@ -148,10 +157,10 @@ class FastTonerCore:
                 g, first, step = self.groups["d"], KINDS_D.index(stat_kind), len(KINDS_D)
             group = core.MatrixGroup(own_w, g.factors, first, step, kind)
             shape = (self.per_layers,) + tuple(all_w[0].shape)
-            delta = torch.empty(shape, device=device, dtype=torch.float32)
-            gathered = torch.empty((world,) + shape, device=device, dtype=torch.float32) if world > 1 else None
-            self.roles[role] = dict(group=group, all=all_w, names=[it[1] for it in items], delta=delta,
-                                    gathered=gathered, all_ptrs=ops.pointer_table(all_w))
+            delta = self.delta_flat[offset: offset + size].view(shape)
+            self.roles[role] = dict(group=group, all=all_w, names=[it[1] for it in items], delta=delta, offset=offset,
+                                    size=size, all_ptrs=ops.pointer_table(all_w))
+            offset += size
         self.t = 0
         self.steps = 0
         self.timing: Dict[str, float] = {}
@@ -204,7 +213,7 @@ class FastTonerCore:
         t0 = time.perf_counter()
         ev_fwd = torch.cuda.Event()
         ev_fwd.record(self.main_stream)
-        self._ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        self._ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
         with torch.cuda.stream(self.side):
             self.side.wait_event(ev_fwd)
             self._ev[0].record(self.side)
@@ -227,6 +236,8 @@ class FastTonerCore:
             e = self._ev_last
             self.gpu_ms = {"stats": e[0].elapsed_time(e[1]), "roots": e[1].elapsed_time(e[2]),
                            "update": e[2].elapsed_time(e[3])}
+            if self.world > 1:   # the part of "update" spent gathering and applying the other ranks' changes
+                self.gpu_ms["exchange"] = e[4].elapsed_time(e[3])
         t0 = time.perf_counter()
         if not self.begun:
             self.begin()
@@ -238,7 +249,6 @@ class FastTonerCore:
         self.main_stream.wait_stream(self.side)
         t1 = time.perf_counter()
         self.t += 1
-        works = []
         for role, info in self.roles.items():
             group: core.MatrixGroup = info["group"]
             if group.count:
@@ -250,14 +260,17 @@ class FastTonerCore:
                 else:
                     core.adamt_group_delta(group, grads, info["delta"], self.scratch, lr=lr, weight_decay=wd,
                                            betas=(float(a.beta1), float(a.beta2)), eps=float(a.eps), t=self.t)
-            if self.world > 1:
-                works.append((info, dist.all_gather_into_tensor(info["gathered"], info["delta"], group=self.pg,
-                                                                async_op=True)))
-            else:
+            if self.world == 1:
                 ops.apply_delta(info["all_ptrs"], info["delta"])
-        for info, work in works:
-            work.wait()
-            ops.apply_delta(info["all_ptrs"], info["gathered"].view((-1,) + tuple(info["delta"].shape[1:])))
+        self._ev[4].record(self.main_stream)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.gathered_flat, self.delta_flat, group=self.pg)
+            per = self.per_layers
+            for info in self.roles.values():
+                shape = tuple(info["delta"].shape)
+                for r in range(self.world):   # rank r's block holds layers r*per .. (r+1)*per - 1 of this role
+                    block = self.gathered_flat[r, info["offset"]: info["offset"] + info["size"]].view(shape)
+                    ops.apply_delta(info["all_ptrs"][r * per:(r + 1) * per], block)
         self._ev[3].record(self.main_stream)
         self._ev_last = self._ev
         self.steps += 1
