@@ -168,8 +168,11 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
  *   lower     lower bound of the spectrum of A' / ||A'||_F valid for every statistic of the call (0: use the bound
  *             damping / (n (1 + damping)) that always holds).  A larger bound means fewer Newton steps
  *             (toner_inv_roots_iterations_for).  The bound is checked on the device: status[b] = 3 where
- *             damping / ||A'_b||_F lies below it, and the caller recomputes that statistic.
- *   norm_out  (DEVICE, optional, k floats) ||A'_b||_F, from which the caller derives next step's bound.
+ *             damping / norm_out[b] lies below it, and the caller recomputes that statistic.
+ *   norm_out  (DEVICE, optional, k floats) the bound of lambda_max(A'_b) the engine normalised by: the smaller of ||A'||_F
+ *             and 1.04 ||A'||_F ||P^2||_F^(1/2) with P = A' / ||A'||_F (one extra single-pass product; (sum lambda^4)^(1/4)
+ *             bounds lambda_max far more tightly than the Frobenius norm when the spectrum is flat).  The caller derives
+ *             next step's bound from it: lower = margin * damping / max_b norm_out[b].
  * A' is A with its dominant eigen-direction deflated: six power-iteration steps find (lambda_1, v); where they
  * converged (residual below 1e-5) and lambda_1 stands above 8x the mean of the rest, the engine factors
  * A' = A - (lambda_1 - c) v v^T and adds (lambda_1^(-1/p) - c^(-1/p)) v v^T back to the root.  This is what the

@@ -305,6 +305,15 @@ __global__ void __launch_bounds__(256) rank1_update_kernel(float* __restrict__ a
   }
 }
 
+// bound^2 <- bound^2 * min(1, 1.04 * sqrt(||P^2||_F^2)): the normalisation moves from ||A'||_F to the tighter
+// ||A'||_F ||P^2||_F^(1/2) (2 % above it, for the single-pass product's rounding).
+__global__ void tighten_bound_kernel(float* __restrict__ bound2, const float* __restrict__ ss2, int k) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= k) return;
+  const float t = 1.04f * sqrtf(fmaxf(ss2[b], 0.f));
+  if (isfinite(t) && t > 0.f && t < 1.f) bound2[b] *= t;
+}
+
 // Per statistic: the scale that turns M_0^{-1/p} into A^{-1/p}, and the convergence status from the
 // distance max|I - M| gathered when the last M was produced (0 converged, 1 above tol, 2 non-finite).
 // 3: the statistic's spectrum reaches below the lower bound the schedule was built for (caller's bound too high).
@@ -440,6 +449,7 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
     float* corr = small(8);
     float* inv_r = small(9);
     unsigned int* max_r = reinterpret_cast<unsigned int*>(small(10));
+    float* ss2 = small(11);
     float* partials = small(16);
     const size_t vec = align_up((size_t)kc * n * 4, 256);
     float* pv = reinterpret_cast<float*>(w + sm * 16 + align_up(sumsq_scratch_bytes(kc), 256));
@@ -475,6 +485,32 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
                                                                 s_t, Mb[0], Tb[0], Xb[1]);
     count_launch();
     TONER_CUDA(cudaGetLastError());
+    {
+      // A tighter bound of the largest eigenvalue than ||A'||_F: with P = A' / ||A'||_F, lambda_max(P) <= ||P^2||_F^(1/2)
+      // = (sum lambda^4)^(1/4).  For a flat spectrum that is n^(-1/4) instead of 1, which raises the spectrum's lower
+      // bound after normalisation by the same factor and saves a Newton step.  One single-pass product of the hi
+      // planes is accurate enough for a bound (2 % is added); its FP32 result goes to a buffer that is free here.
+      float* P2 = reinterpret_cast<float*>(Pb[0]);
+      toner_gemm_desc g = {};
+      toner_operand op = {};
+      op.base = Mb[0];
+      op.rows = n; op.cols = n; op.ld = n; op.z_stride = nn; op.nz = 2 * kc; op.z_step = 1;
+      g.a = op; g.b = op;
+      g.m = n; g.n = n; g.k = n; g.batch = kc; g.segs = 1; g.fmt = 0;
+      g.tri = 1; g.mirror = 1;
+      g.alpha = (float)(1.0 / ((double)s_m * (double)s_m));
+      g.d = P2; g.ldd = n; g.d_bs = nn;
+      int rc1 = launch_gemm(g, stream);
+      if (rc1) return rc1;
+      rc1 = sumsq_det(P2, kc, n, n, n, nn, partials, ss2, stream);
+      if (rc1) return rc1;
+      tighten_bound_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(sumsq_a, ss2, kc);
+      count_launch();
+      init_planes_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(A32, n, kc, sumsq_a, (float)sched[0].a, (float)sched[0].b,
+                                                                  s_m, s_t, Mb[0], Tb[0], Xb[1]);
+      count_launch();
+      TONER_CUDA(cudaGetLastError());
+    }
 
     // D = (A planes) * (B planes)^T / (sa * sb): symmetric result, FP32-accurate; outputs as requested
     struct Out {
