@@ -152,7 +152,7 @@ int toner_split16(const float* x, const float* const* x_list, int32_t batch, int
  * Method: coupled Newton iteration T = a I - b M, X <- X T, M <- T^p M with minimax-scaled (a, b), batched
  * over the k statistics, all products FP32-accurate on tensor cores (FP16 hi/lo planes, three plane products
  * per accumulator).  `iters` <= 0 selects toner_inv_roots_iterations(n, damping, p), which depends only on
- * its arguments (10 for p = 8, 11 for p = 4, 12 for p = 2 at n = 5632, damping 1e-3).
+ * its arguments (9 for p = 8, 10 for p = 4, 12 for p = 2 at n = 5632, damping 1e-3).
  * status[b] (DEVICE, optional): 0 converged, 1 residual max|I - M| above 0.05 before the last step,
  * 2 non-finite.  The caller decides what to do with a non-zero status (the Python host recomputes that
  * statistic with an eigendecomposition, as the reference's fallback does, src/toner/fast/engine.py:714-731).

@@ -110,8 +110,8 @@ def test_chunked_workspace_gives_identical_roots(ops):
 
 
 def test_iteration_counts_are_stated(ops):
-    assert ops.inv_roots_iterations(5632, 1e-3, 8) == 10
-    assert ops.inv_roots_iterations(5632, 1e-3, 4) == 11
+    assert ops.inv_roots_iterations(5632, 1e-3, 8) == 9
+    assert ops.inv_roots_iterations(5632, 1e-3, 4) == 10
     assert ops.inv_roots_iterations(5632, 1e-3, 2) == 12
     assert ops.inv_roots_iterations(768, 1e-3, 8) <= 10
 
