@@ -107,7 +107,7 @@ def sampled_positions() -> int:
 
 
 def step_flops(layers: int, hidden: int, mlp: int, rows_total: int, root_gemms_d: int, root_gemms_f: int, ns_steps: int = 10):
-    """Algorithmic work of one whole-job step (single-pass dense counts)."""
+    """Algorithmic work of one whole-job step (single-pass dense counts: 2 n^3 per product, rows n (n+1) for the triangle of a Gram)."""
     syrk = rows_total * (3 * layers * hidden * (hidden + 1) + layers * mlp * (mlp + 1))
     shapes = [(hidden, hidden)] * 4 + [(mlp, hidden)] * 2 + [(hidden, mlp)]
     ns = precond = 0

@@ -19,7 +19,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, os.environ.get("REFERENCE_SRC", "/root/reference/src"))
+if "REFERENCE_SRC" not in os.environ:
+    raise SystemExit("set REFERENCE_SRC to the src/ directory of a Toner checkout")
+sys.path.insert(0, os.environ["REFERENCE_SRC"])
 
 import toner  # noqa: E402
 from toner.linalg import input_factors, newton_schulz  # noqa: E402
