@@ -239,14 +239,22 @@ class MatrixGroup:
         return self._grad_ptrs
 
 
-def _product(a_planes, a_inv, group: MatrixGroup, which: str, d, **kw) -> None:
-    """d[b] = A[b] @ R[first + b*step] in split precision, R the inner or outer factor (symmetric)."""
+def _product(a_planes, a_inv, group: MatrixGroup, which: str, d, coarse: bool = False, **kw) -> None:
+    """d[b] = A[b] @ R[first + b*step], R the inner or outer factor (symmetric).  FP32-accurate from the FP16 hi/lo
+    planes (three plane products in one accumulator); ``coarse`` multiplies the hi planes only (relative error
+    about 5e-4), for terms that enter the result with a small coefficient."""
     f = group.factors
     r_planes, r_inv = f.planes(which)
     count, m, n = group.count, group.out_features, group.in_features
-    a = ops.operand(a_planes, seg_z=(0, 0, count))
-    b = ops.operand(r_planes, seg_z=(group.first, f.k + group.first, group.first), z_step=group.step)
-    ops.gemm(a, b, m=m, n=n, k=n, batch=count, fmt=0, segs=3, d=d, alpha_a=a_inv,
+    if coarse:
+        a = ops.operand(a_planes, seg_z=(0, 0, 0))
+        b = ops.operand(r_planes, seg_z=(group.first, group.first, group.first), z_step=group.step)
+        segs = 1
+    else:
+        a = ops.operand(a_planes, seg_z=(0, 0, count))
+        b = ops.operand(r_planes, seg_z=(group.first, f.k + group.first, group.first), z_step=group.step)
+        segs = 3
+    ops.gemm(a, b, m=m, n=n, k=n, batch=count, fmt=0, segs=segs, d=d, alpha_a=a_inv,
              alpha_b=r_inv[group.first:], alpha_b_step=group.step, promote=0, **kw)
 
 
@@ -296,7 +304,8 @@ def muont_delta_from_polar(group: MatrixGroup, polar: torch.Tensor, delta: torch
         ops.split16_list(group.weight_ptrs, count, m, n, planes, inv, maxabs)
         ops.scale_vec(inv, c1)
         maxabs.zero_()
-        _product(planes, inv, group, "outer", work, c=work, beta=1.0, beta_v=c2, maxabs=maxabs)  # V = c1 W R + c2 P
+        # V = c1 W R + c2 P.  The decay term is lr wd ||W|| against lr ||P||, about 1 % of V: the hi planes suffice
+        _product(planes, inv, group, "outer", work, coarse=True, c=work, beta=1.0, beta_v=c2, maxabs=maxabs)
         ops.split16(work, planes=planes, inv_scale=inv, maxabs=maxabs)
     else:
         if polar_maxabs is None:
@@ -354,7 +363,7 @@ def adamt_group_delta(group: MatrixGroup, grads: Sequence[torch.Tensor], delta: 
         ops.split16_list(group.weight_ptrs, count, m, n, planes, inv, maxabs)
         ops.scale_vec(inv, c1)
         maxabs.zero_()
-        _product(planes, inv, group, "outer", work2, maxabs=maxabs)   # c1 W R
+        _product(planes, inv, group, "outer", work2, coarse=True, maxabs=maxabs)   # c1 W R (small term: hi planes)
         ops.split16(work2, planes=planes, inv_scale=inv, maxabs=maxabs)
         _product(planes, inv, group, "outer", delta, alpha=-1.0, c=work, beta=1.0, beta_v=c2)
     else:
