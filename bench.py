@@ -106,7 +106,8 @@ def sampled_positions() -> int:
     return len(list(range(HEAD)) + list(range(HEAD + 1, SEQ_LEN, STRIDE)))
 
 
-def step_flops(layers: int, hidden: int, mlp: int, rows_total: int, root_gemms_d: int, root_gemms_f: int, ns_steps: int = 10):
+def step_flops(layers: int, hidden: int, mlp: int, rows_total: int, root_gemms_d: int, root_gemms_f: int, ns_steps: int = 10,
+               products: int = 3):
     """Algorithmic work of one whole-job step (single-pass dense counts: 2 n^3 per product, rows n (n+1) for the triangle of a Gram)."""
     syrk = rows_total * (3 * layers * hidden * (hidden + 1) + layers * mlp * (mlp + 1))
     shapes = [(hidden, hidden)] * 4 + [(mlp, hidden)] * 2 + [(hidden, mlp)]
@@ -114,7 +115,7 @@ def step_flops(layers: int, hidden: int, mlp: int, rows_total: int, root_gemms_d
     for m, n in shapes:
         a, b = min(m, n), max(m, n)
         ns += layers * ns_steps * (4 * a * a * b + 2 * a ** 3)
-        precond += layers * 3 * 2 * m * n * n
+        precond += layers * products * 2 * m * n * n
     roots = 3 * layers * root_gemms_d * 2 * hidden ** 3 + layers * root_gemms_f * 2 * mlp ** 3
     return {"syrk": syrk, "ns": ns, "precond": precond, "roots": roots}
 
@@ -123,7 +124,7 @@ def run_ours(args) -> None:
     import torch.distributed as dist
 
     from toner_b200 import ops
-    from toner_b200.fast import FastMuonT, ProjectionBlock
+    from toner_b200.fast import FastAdamT, FastMuonT, ProjectionBlock
     from toner_b200.synthetic import fill_rows, make_stack
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -140,8 +141,13 @@ def run_ours(args) -> None:
     micro = 1
     acc = sequences // world
     stack = make_stack("llama", layers, hidden, mlp, dev, seed=0)
-    opt = FastMuonT([ProjectionBlock.from_module(b) for b in stack], LR, weight_decay=WD, momentum=MOMENTUM,
-                    micro_batch_size=micro, sequence_length=SEQ_LEN, accumulation_steps=acc)
+    blocks = [ProjectionBlock.from_module(b) for b in stack]
+    if args.optimizer == "adamt":   # AdamT: factors A^-1/4 only, five right-products per matrix, no Newton-Schulz
+        opt = FastAdamT(blocks, 2e-3, weight_decay=WD, betas=(0.9, 0.95), micro_batch_size=micro,
+                        sequence_length=SEQ_LEN, accumulation_steps=acc)
+    else:
+        opt = FastMuonT(blocks, LR, weight_decay=WD, momentum=MOMENTUM, micro_batch_size=micro,
+                        sequence_length=SEQ_LEN, accumulation_steps=acc)
     core = opt._core
     # Engine-level seam (what the reference's second trainer uses): the sampled rows of this rank's tokens
     # are written straight into the row buffers, gradients into .grad, then begin() and step().
@@ -215,9 +221,13 @@ def run_ours(args) -> None:
         # products per statistic: X T and T^2 T^4 T^8 T^8 M per Newton step (no X product in the first, no M update
         # in the last), two squarings for A^-1/2; the step count follows each group's spectrum bound
         it_d, it_f = core.groups["d"].factors.iterations, core.groups["f"].factors.iterations
-        gemms_d, gemms_f = (it_d - 1) * 5 + 2, (it_f - 1) * 5 + 2
+        if args.optimizer == "adamt":   # p = 4: X T, T^2, T^4, T^4 M per step, no squarings afterwards
+            gemms_d, gemms_f = (it_d - 1) * 4, (it_f - 1) * 4
+            fl = step_flops(layers, hidden, mlp, local_rows * world, gemms_d, gemms_f, ns_steps=0, products=5)
+        else:
+            gemms_d, gemms_f = (it_d - 1) * 5 + 2, (it_f - 1) * 5 + 2
+            fl = step_flops(layers, hidden, mlp, local_rows * world, gemms_d, gemms_f)
         gemms = gemms_f
-        fl = step_flops(layers, hidden, mlp, local_rows * world, gemms_d, gemms_f)
         ph = phases[-1] if phases and phases[-1] else {}
         per_phase = {}
         for name, work in (("stats", fl["syrk"]), ("roots", fl["roots"]), ("update", fl["ns"] + fl["precond"])):
@@ -244,7 +254,7 @@ def run_ours(args) -> None:
                 roof["executed"] = round(ex, 1)
                 roof["frac_executed"] = round(ex / pk["tflops"], 4)
         line = {
-            "metric": "muont_optimizer_step_ms", "value": round(ms, 3), "unit": "ms", "n_gpus": world,
+            "metric": f"{args.optimizer}_optimizer_step_ms", "value": round(ms, 3), "unit": "ms", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3), "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16 operands / fp16 hi-lo splits, fp32 accumulate",
             "data": "synthetic",
@@ -294,10 +304,14 @@ def cpu_baseline(args, sample_rows: int = 2048):
     for role, (m, n, kind) in shapes.items():
         w = torch.randn(m, n, generator=g) * 0.02
         grad = torch.randn(m, n, generator=g) * 1e-3
-        st = orc.MuonTState()
+        adam = getattr(args, "optimizer", "muont") == "adamt"
+        st = orc.AdamTState() if adam else orc.MuonTState()
         st.ema, st.weight = orc.ema_update(None, 0.0, stats[kind], MOMENTUM)
         t0 = time.perf_counter()
-        orc.muont_step(w, grad, st, lr=LR, weight_decay=WD, momentum=MOMENTUM, ns_mode="f32")
+        if adam:
+            orc.adamt_step(w, grad, st, lr=2e-3, weight_decay=WD, betas=(0.9, 0.95), eps=1e-15)
+        else:
+            orc.muont_step(w, grad, st, lr=LR, weight_decay=WD, momentum=MOMENTUM, ns_mode="f32")
         t_step += time.perf_counter() - t0
     per_layer_ms = (t_gram + t_step) * 1e3
     return {"value": round(per_layer_ms * layers, 1), "unit": "ms", "cores": cores, "kind": "port",
@@ -316,7 +330,7 @@ def run_reference(args) -> None:
         times.append(base["value"])
     ms = min(times)
     base["value"] = ms
-    line = {"impl": "reference", "metric": "muont_optimizer_step_ms", "value": ms, "unit": "ms",
+    line = {"impl": "reference", "metric": f"{args.optimizer}_optimizer_step_ms", "value": ms, "unit": "ms",
             "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
@@ -337,6 +351,7 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=HIDDEN)
     ap.add_argument("--mlp", type=int, default=MLP)
     ap.add_argument("--sequences", type=int, default=SEQUENCES)
+    ap.add_argument("--optimizer", default="muont", choices=["muont", "adamt"], help="FastMuonT (headline) or FastAdamT")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (for profiler runs)")
     args = ap.parse_args()
