@@ -34,7 +34,7 @@ def close(got, want, k, tol=4e-7):
     assert err <= tol * (k ** 0.5) * scale + 1e-30, (err, scale)
 
 
-@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("tile_n", [128, 256, 512])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_k_major_square(ops, tile_n, dtype):
     m = n = k = 256
@@ -46,7 +46,7 @@ def test_k_major_square(ops, tile_n, dtype):
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, False), (False, True), (True, True)])
-@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("tile_n", [128, 256, 512])   # 512: 256 x 256 tiles on CTA pairs
 def test_layouts_ragged_batched(ops, a_mn, b_mn, tile_n):
     """Sizes that are not multiples of the tile or of the k-block; three matrices per call."""
     batch, m, n, k = 3, 200, 328, 136
@@ -165,3 +165,32 @@ def test_split_product_is_fp32_accurate(ops, scale):
     # planes reconstruct the source to ~2^-22 of its largest entry
     rec = (ap[0].double() + ap[1].double()) * ai.double()[:, None, None]
     assert ((rec - a.double()).abs().amax() / a.abs().amax()).item() < 2 ** -21
+
+
+@pytest.mark.parametrize("promote", [0, 2])
+def test_cta_pair_symmetric_split_product_matches_single_cta_tiles(ops, promote):
+    """256 x 256 tiles on CTA pairs against 128 x 256 single-CTA tiles: FP16 hi/lo split product with a symmetric,
+    mirrored result, all epilogue outputs (FP32, operand planes, statistics), sizes that leave ragged edge tiles."""
+    batch, n = 3, 600
+    x = rnd((batch, n, n), torch.float32, 9)
+    x = x + x.transpose(1, 2)
+    planes, inv = ops.split16(x)
+    a = ops.operand(planes, seg_z=(0, 0, batch))
+    b = ops.operand(planes, seg_z=(0, batch, 0))
+    out = {}
+    for tile in (256, 512):
+        d = torch.full((batch, n, n), float("nan"), device="cuda")
+        sp = torch.zeros(2, batch, n, n, device="cuda", dtype=torch.float16)
+        mx = torch.zeros(batch, device="cuda", dtype=torch.int32)
+        desc_extra = dict(tri=True, mirror=True, promote=promote, maxabs=mx, tile_n=tile)
+        ops.gemm(a, b, m=n, n=n, k=n, batch=batch, fmt=0, segs=3, d=d, alpha_a=inv, alpha_b=inv, **desc_extra)
+        ops.assert_healthy()
+        out[tile] = (d, mx.clone())
+    want = x.double() @ x.double()
+    for tile in (256, 512):
+        # one chain over the whole depth adds by truncation (about 1.2e-7 per k-block on the all-positive diagonal)
+        tol = 2e-6 if promote else 1e-5
+        assert (out[tile][0].double() - want).abs().max().item() <= tol * want.abs().max().item()
+        assert torch.equal(out[tile][0], out[tile][0].transpose(1, 2))
+    assert torch.equal(out[256][0], out[512][0])        # same accumulation order, same bits
+    assert torch.equal(out[256][1], out[512][1])
