@@ -213,7 +213,7 @@ class FastTonerCore:
         t0 = time.perf_counter()
         ev_fwd = torch.cuda.Event()
         ev_fwd.record(self.main_stream)
-        self._ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        self._ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
         with torch.cuda.stream(self.side):
             self.side.wait_event(ev_fwd)
             self._ev[0].record(self.side)
@@ -238,6 +238,7 @@ class FastTonerCore:
                            "update": e[2].elapsed_time(e[3])}
             if self.world > 1:   # the part of "update" spent gathering and applying the other ranks' changes
                 self.gpu_ms["exchange"] = e[4].elapsed_time(e[3])
+                self.gpu_ms["gather"] = e[4].elapsed_time(e[5])   # includes waiting for the slowest rank
         t0 = time.perf_counter()
         if not self.begun:
             self.begin()
@@ -265,6 +266,7 @@ class FastTonerCore:
         self._ev[4].record(self.main_stream)
         if self.world > 1:
             dist.all_gather_into_tensor(self.gathered_flat, self.delta_flat, group=self.pg)
+            self._ev[5].record(self.main_stream)
             per = self.per_layers
             for info in self.roles.values():
                 shape = tuple(info["delta"].shape)
