@@ -61,3 +61,40 @@ def test_two_ranks_reduce_to_owners_and_gather_in_layer_order(tmp_path):
         # layer l is owned by rank l // 2 at position l % 2: gathered row l must carry that signature
         want = torch.tensor([0.0, 0.1, 1.0, 1.1]).view(-1, 1, 1).expand(-1, 2, 2)
         assert torch.allclose(got["gathered"], want)
+
+
+def _flat_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from toner_b200.fast.engine import flat_layout, gathered_block, layer_counts
+        layers = 4
+        per = layer_counts(layers, world)[rank]
+        shapes = {"q": (per, 2, 3), "up": (per, 4, 3), "down": (per, 3, 4)}     # roles of different sizes
+        sizes = [int(torch.tensor(s).prod()) for s in shapes.values()]
+        offsets = flat_layout(sizes)
+        flat = torch.empty(sum(sizes))
+        for (role, shape), off, size in zip(shapes.items(), offsets, sizes):
+            # value encodes (role, global layer): what every rank must find after the exchange
+            stack = torch.stack([torch.full(shape[1:], 100.0 * list(shapes).index(role) + rank * per + j) for j in range(per)])
+            flat[off: off + size] = stack.reshape(-1)
+        gathered = torch.empty(world, sum(sizes))
+        dist.all_gather_into_tensor(gathered.view(-1), flat)   # gloo wants the concatenated form
+        found = {}
+        for (role, shape), off, size in zip(shapes.items(), offsets, sizes):
+            for r in range(world):
+                block = gathered_block(gathered, r, off, size, shape)
+                for j in range(per):
+                    found[(role, r * per + j)] = block[j].unique().tolist()
+        torch.save(found, os.path.join(out_dir, f"f{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_flat_exchange_buffer_maps_back_to_role_and_layer(tmp_path):
+    world = 2
+    mp.spawn(_flat_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        found = torch.load(os.path.join(tmp_path, f"f{r}.pt"))
+        for (role, layer), vals in found.items():
+            assert vals == [100.0 * ["q", "up", "down"].index(role) + layer]

@@ -68,6 +68,20 @@ def chunk_members(world: int, per_rank: int, chunks: int, c: int) -> List[int]:
     return [r * per_rank + c * cs + j for r in range(world) for j in range(cs)]
 
 
+def flat_layout(sizes: Sequence[int]) -> List[int]:
+    """Offsets of the roles' change stacks inside one rank's flat exchange buffer (roles in registration order)."""
+    offsets, total = [], 0
+    for size in sizes:
+        offsets.append(total)
+        total += int(size)
+    return offsets
+
+
+def gathered_block(gathered: torch.Tensor, rank: int, offset: int, size: int, shape) -> torch.Tensor:
+    """Rank `rank`'s stack of one role inside the all-gathered (world, total) buffer: layers rank*per .. of that role."""
+    return gathered[rank, offset: offset + size].view(tuple(shape))
+
+
 class StatGroup:
     """All statistics of one width: row buffers for every layer, EMAs and factors for the owned ones."""
 
@@ -146,8 +160,7 @@ class FastTonerCore:
         sizes = [self.per_layers * items[0][2].numel() for _, items in plan]
         self.delta_flat = torch.empty(sum(sizes), device=device, dtype=torch.float32)
         self.gathered_flat = (torch.empty(world, sum(sizes), device=device, dtype=torch.float32) if world > 1 else None)
-        offset = 0
-        for (role, items), size in zip(plan, sizes):
+        for (role, items), size, offset in zip(plan, sizes, flat_layout(sizes)):
             all_w = [it[2] for it in items]
             own_w = all_w[lo_layer: lo_layer + self.per_layers]
             stat_kind = ROLE_KIND[role]
@@ -160,7 +173,6 @@ class FastTonerCore:
             delta = self.delta_flat[offset: offset + size].view(shape)
             self.roles[role] = dict(group=group, all=all_w, names=[it[1] for it in items], delta=delta, offset=offset,
                                     size=size, all_ptrs=ops.pointer_table(all_w))
-            offset += size
         self.t = 0
         self.steps = 0
         self.timing: Dict[str, float] = {}
@@ -271,7 +283,7 @@ class FastTonerCore:
             for info in self.roles.values():
                 shape = tuple(info["delta"].shape)
                 for r in range(self.world):   # rank r's block holds layers r*per .. (r+1)*per - 1 of this role
-                    block = self.gathered_flat[r, info["offset"]: info["offset"] + info["size"]].view(shape)
+                    block = gathered_block(self.gathered_flat, r, info["offset"], info["size"], shape)
                     ops.apply_delta(info["all_ptrs"][r * per:(r + 1) * per], block)
         self._ev[3].record(self.main_stream)
         self._ev_last = self._ev
