@@ -2,14 +2,19 @@
 // iteration with minimax scaling, every product on the tcgen05 GEMM in FP32-accurate split precision.
 //
 //   A   = sym(C) / mean(diag C) + damping * I                 (what the reference factors by eigh)
-//   M_0 = A / ||A||_F         (spectrum inside [l_0, 1],  l_0 >= damping / (n (1 + damping)))
+//   A'  = A - (lambda_1 - c) v v^T                            (dominant direction deflated when power iteration finds it)
+//   M_0 = A' / beta,  beta >= lambda_max(A')                  (beta = min(||A'||_F, 1.04 ||A'||_F ||P^2||_F^(1/2)), P = A'/||A'||_F)
 //   T_k = a_k I - b_k M_k ;  X_{k+1} = X_k T_k ;  M_{k+1} = T_k^p M_k          (X_0 = I)
-//   X_K ~ M_0^{-1/p}  =>  A^{-1/p} = X_K ||A||_F^{-1/p}
+//   X_K ~ M_0^{-1/p}  =>  A^{-1/p} = X_K beta^{-1/p} + (lambda_1^{-1/p} - c^{-1/p}) v v^T
 // (a_k, b_k) map the interval [l_k, 1] known to contain the spectrum of M_k onto [l_{k+1}, 1] with
 // l_{k+1} as large as a linear T allows (the ends of the interval and the interior maximum of
 // mu (a - b mu)^p are levelled, subject to a cap on b/a that bounds the dynamic range of T^p); once
 // l_k is close to 1 they become the Newton values ((p+1)/p, 1/p).
-// The schedule depends only on (n, damping, p), so the iteration count is fixed and stated.
+// l_0 is the caller's lower bound of the spectrum of M_0 (checked per statistic on the device), or
+// damping / (n (1 + damping)), which always holds; the schedule and the iteration count depend only on
+// (l_0, p), so they are fixed before anything is launched and stated by toner_inv_roots_iterations[_for].
+// Every operand of every product is a pair of FP16 hi/lo planes written by the epilogue of the product that
+// made it, scaled by a power of two taken from a norm bound known in advance.
 #include <cmath>
 #include <cstdlib>
 #include <vector>

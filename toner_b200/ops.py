@@ -16,7 +16,6 @@ from ._lib import GemmDesc, Operand, check
 
 PACKED, PACKED_ACC, EMA_FULL = 0, 1, 2
 PROMOTE_ACCURATE = 2  # k-blocks per tensor-core accumulation chain in FP32-accurate products
-PROMOTE_LINEAR = 8    # chain length for products whose error only propagates linearly (about 1e-6 relative)
 _FMT = {torch.float16: 0, torch.bfloat16: 1}
 
 
