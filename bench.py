@@ -236,7 +236,6 @@ def run_ours(args) -> None:
                 per_phase[name] = {"ms": round(ph[name], 3), "tflops_per_gpu": round(work / world / ph[name] / 1e9, 1)}
         if "exchange" in ph:
             per_phase["update"]["exchange_ms"] = round(ph["exchange"], 3)
-            per_phase["update"]["gather_ms"] = round(ph.get("gather", 0.0), 3)
         top = max(per_phase, key=lambda k: per_phase[k]["ms"]) if per_phase else None
         roof = None
         if top:

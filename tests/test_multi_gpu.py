@@ -1,0 +1,94 @@
+"""Layer-sharded engine on two GPUs (NCCL) against the same step on one GPU.
+
+Each rank captures its own microbatches (its share of the tokens), owns half of the layers, and after the step every
+rank must hold the weights a single process gets from all microbatches.  Two things differ between the runs: the order
+of FP32 additions in the statistic (packed partial Grams summed by reduce-scatter instead of one SYRK with a fused EMA)
+and the Newton schedule of the factor engine, whose spectrum bound is taken over the statistics a rank owns.  Both
+stay inside the factor engine's accuracy (1e-4 on a factor), hence the bound on the weights below.
+Needs two visible GPUs; skipped otherwise."""
+
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HID, MLP, SEQ, MB, ACC, LAYERS = 256, 512, 256, 2, 2, 2   # 704 sampled rows: full-rank statistics
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _microbatch(rank, mb_index):
+    g = torch.Generator().manual_seed(1000 + 17 * rank + mb_index)
+    return torch.randn(MB, SEQ, HID, generator=g)
+
+
+def _run(kind, world, rank, device, microbatches, steps=2):
+    """One process's part of `steps` optimizer steps; returns its weights."""
+    import toner_b200.fast as fast
+    from toner_b200.synthetic import make_stack
+    stack = make_stack("llama", LAYERS, HID, MLP, device, seed=0)
+    cls = fast.FastMuonT if kind == "muont" else fast.FastAdamT
+    extra = dict(ns_steps=2) if kind == "muont" else dict(betas=(0.9, 0.95), eps=1e-4)
+    opt = cls([fast.ProjectionBlock.from_module(b) for b in stack], 0.02 if kind == "muont" else 2e-3, weight_decay=0.1,
+              micro_batch_size=MB, sequence_length=SEQ, accumulation_steps=len(microbatches), statistic_head=32,
+              statistic_stride=4, **extra)
+    try:
+        for step in range(steps):
+            for x in microbatches:
+                with opt.capture_microbatch():
+                    with torch.autocast("cuda", dtype=torch.bfloat16):
+                        h = (x + step).to(device)
+                        for b in stack:
+                            h = b(h)
+            opt.begin()
+            g = torch.Generator().manual_seed(77 + step)     # gradients arrive already synchronised
+            for b in stack:
+                for p in b.parameters():
+                    if p.ndim == 2:
+                        p.grad = (torch.randn(p.shape, generator=g) * 1e-3).to(device)
+            opt.step()
+        torch.cuda.synchronize(device)
+        from toner_b200 import ops
+        ops.assert_healthy()
+        return [p.detach().cpu().clone() for b in stack for p in b.parameters() if p.ndim == 2]
+    finally:
+        opt.close()
+
+
+def _worker(rank, world, port, kind, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        weights = _run(kind, world, rank, device, [_microbatch(rank, i) for i in range(ACC)])
+        torch.save(weights, os.path.join(out_dir, f"w{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("kind", ["muont", "adamt"])
+def test_two_ranks_match_one_process(tmp_path, kind):
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), kind, str(tmp_path)), nprocs=world, join=True)
+    torch.cuda.set_device(0)
+    single = _run(kind, 1, 0, torch.device("cuda", 0), [_microbatch(r, i) for r in range(world) for i in range(ACC)])
+    for r in range(world):
+        got = torch.load(os.path.join(tmp_path, f"w{r}.pt"))
+        assert len(got) == len(single)
+        for a, b in zip(got, single):
+            rel = (a - b).norm().item() / b.norm().item()
+            assert rel < 3e-4, (kind, r, rel)

@@ -8,8 +8,8 @@ Work split on one multi-GPU box (one process per GPU):
   reduce-scatter of packed FP32 triangles, issued chunk by chunk so that it overlaps the SYRK of the
   next chunk), keep the statistic EMAs, compute the inverse-root factors and the parameter changes of
   their layers;
-* the changes of all roles sit in one flat buffer per rank; one NCCL all-gather after the last role moves
-  them, and every rank adds all of them to its replica of the weights.
+* the changes of the roles sit in two flat buffers per rank; each is moved by one NCCL all-gather, the first
+  while the second is still being computed, and every rank adds all of them to its replica of the weights.
 
 ``begin()`` runs statistics and factors on a high-priority side stream so that they overlap the
 last backward pass; ``step()`` joins it.  The only host synchronisation in ``step()`` is the wait
@@ -155,24 +155,42 @@ class FastTonerCore:
             if [it[0] for it in items] != list(range(layers)):
                 raise ValueError(f"role {role} must have exactly one matrix per layer")
             plan.append((role, items))
-        # One flat buffer holds this rank's changes of every role, so that a single all-gather moves them all
-        # (one large NCCL transfer after the last role instead of seven that fight the GEMMs for SMs).
+        # Exchange layout.  The roles are worked through largest matrices first, and their changes sit in two flat
+        # buffers: the first is all-gathered (one large NCCL transfer) while the roles of the second are still being
+        # computed, the second right after them.  One buffer when there is nothing to exchange.
+        plan.sort(key=lambda pr: -pr[1][0][2].numel())
         sizes = [self.per_layers * items[0][2].numel() for _, items in plan]
-        self.delta_flat = torch.empty(sum(sizes), device=device, dtype=torch.float32)
-        self.gathered_flat = (torch.empty(world, sum(sizes), device=device, dtype=torch.float32) if world > 1 else None)
-        for (role, items), size, offset in zip(plan, sizes, flat_layout(sizes)):
-            all_w = [it[2] for it in items]
-            own_w = all_w[lo_layer: lo_layer + self.per_layers]
-            stat_kind = ROLE_KIND[role]
-            if stat_kind == "down":
-                g, first, step = self.groups["f"], 0, 1
-            else:
-                g, first, step = self.groups["d"], KINDS_D.index(stat_kind), len(KINDS_D)
-            group = core.MatrixGroup(own_w, g.factors, first, step, kind)
-            shape = (self.per_layers,) + tuple(all_w[0].shape)
-            delta = self.delta_flat[offset: offset + size].view(shape)
-            self.roles[role] = dict(group=group, all=all_w, names=[it[1] for it in items], delta=delta, offset=offset,
-                                    size=size, all_ptrs=ops.pointer_table(all_w))
+        cut = len(plan)
+        if world > 1 and len(plan) > 1:
+            acc = 0
+            for i, size in enumerate(sizes[:-1]):
+                acc += size
+                if acc >= 0.55 * sum(sizes):
+                    cut = i + 1
+                    break
+        self.parts = []
+        for lo_i, hi_i in ((0, cut), (cut, len(plan))):
+            if lo_i == hi_i:
+                continue
+            total = sum(sizes[lo_i:hi_i])
+            part = dict(delta=torch.empty(total, device=device, dtype=torch.float32),
+                        gathered=(torch.empty(world, total, device=device, dtype=torch.float32) if world > 1 else None),
+                        roles=[])
+            for (role, items), size, offset in zip(plan[lo_i:hi_i], sizes[lo_i:hi_i], flat_layout(sizes[lo_i:hi_i])):
+                all_w = [it[2] for it in items]
+                own_w = all_w[lo_layer: lo_layer + self.per_layers]
+                stat_kind = ROLE_KIND[role]
+                if stat_kind == "down":
+                    g, first, step = self.groups["f"], 0, 1
+                else:
+                    g, first, step = self.groups["d"], KINDS_D.index(stat_kind), len(KINDS_D)
+                group = core.MatrixGroup(own_w, g.factors, first, step, kind)
+                shape = (self.per_layers,) + tuple(all_w[0].shape)
+                delta = part["delta"][offset: offset + size].view(shape)
+                self.roles[role] = dict(group=group, all=all_w, names=[it[1] for it in items], delta=delta, offset=offset,
+                                        size=size, all_ptrs=ops.pointer_table(all_w))
+                part["roles"].append(role)
+            self.parts.append(part)
         self.t = 0
         self.steps = 0
         self.timing: Dict[str, float] = {}
@@ -249,8 +267,7 @@ class FastTonerCore:
             self.gpu_ms = {"stats": e[0].elapsed_time(e[1]), "roots": e[1].elapsed_time(e[2]),
                            "update": e[2].elapsed_time(e[3])}
             if self.world > 1:   # the part of "update" spent gathering and applying the other ranks' changes
-                self.gpu_ms["exchange"] = e[4].elapsed_time(e[3])
-                self.gpu_ms["gather"] = e[4].elapsed_time(e[5])   # includes waiting for the slowest rank
+                self.gpu_ms["exchange"] = e[4].elapsed_time(e[5])   # not hidden behind the last roles' products
         t0 = time.perf_counter()
         if not self.begun:
             self.begin()
@@ -262,29 +279,35 @@ class FastTonerCore:
         self.main_stream.wait_stream(self.side)
         t1 = time.perf_counter()
         self.t += 1
-        for role, info in self.roles.items():
-            group: core.MatrixGroup = info["group"]
-            if group.count:
-                grads = [p.grad for p in group.weights]
-                if self.kind == "muont":
-                    core.muont_group_delta(group, grads, info["delta"], self.scratch, lr=lr, weight_decay=wd,
-                                           momentum=float(a.momentum), nesterov=bool(a.nesterov),
-                                           ns_steps=int(a.ns_steps), ns_eps=float(a.ns_eps))
-                else:
-                    core.adamt_group_delta(group, grads, info["delta"], self.scratch, lr=lr, weight_decay=wd,
-                                           betas=(float(a.beta1), float(a.beta2)), eps=float(a.eps), t=self.t)
-            if self.world == 1:
-                ops.apply_delta(info["all_ptrs"], info["delta"])
+        works = []
+        for part in self.parts:
+            for role in part["roles"]:
+                info = self.roles[role]
+                group: core.MatrixGroup = info["group"]
+                if group.count:
+                    grads = [p.grad for p in group.weights]
+                    if self.kind == "muont":
+                        core.muont_group_delta(group, grads, info["delta"], self.scratch, lr=lr, weight_decay=wd,
+                                               momentum=float(a.momentum), nesterov=bool(a.nesterov),
+                                               ns_steps=int(a.ns_steps), ns_eps=float(a.ns_eps))
+                    else:
+                        core.adamt_group_delta(group, grads, info["delta"], self.scratch, lr=lr, weight_decay=wd,
+                                               betas=(float(a.beta1), float(a.beta2)), eps=float(a.eps), t=self.t)
+                if self.world == 1:
+                    ops.apply_delta(info["all_ptrs"], info["delta"])
+            if self.world > 1:   # this part's changes travel while the next part is computed
+                works.append(dist.all_gather_into_tensor(part["gathered"], part["delta"], group=self.pg, async_op=True))
         self._ev[4].record(self.main_stream)
-        if self.world > 1:
-            dist.all_gather_into_tensor(self.gathered_flat, self.delta_flat, group=self.pg)
-            self._ev[5].record(self.main_stream)
-            per = self.per_layers
-            for info in self.roles.values():
+        per = self.per_layers
+        for part, work in zip(self.parts, works):
+            work.wait()
+            for role in part["roles"]:
+                info = self.roles[role]
                 shape = tuple(info["delta"].shape)
                 for r in range(self.world):   # rank r's block holds layers r*per .. (r+1)*per - 1 of this role
-                    block = gathered_block(self.gathered_flat, r, info["offset"], info["size"], shape)
+                    block = gathered_block(part["gathered"], r, info["offset"], info["size"], shape)
                     ops.apply_delta(info["all_ptrs"][r * per:(r + 1) * per], block)
+        self._ev[5].record(self.main_stream)
         self._ev[3].record(self.main_stream)
         self._ev_last = self._ev
         self.steps += 1
