@@ -176,3 +176,17 @@ def test_repair_round_when_the_bound_no_longer_holds(ops):
         c = f.ema[b].cpu()
         assert orc.rel_fro(f.root_lo[b].cpu(), orc.inverse_root_truth(c, 0.125, DAMPING)) < 5e-4
         assert orc.rel_fro(f.root_hi[b].cpu(), orc.inverse_root_truth(c, 0.5, DAMPING)) < 2e-3
+
+
+def test_non_finite_statistic_is_flagged_and_does_not_touch_its_neighbours(ops):
+    """Failure detection without a fault: a statistic full of NaN (or with an infinite entry) comes back with status 2,
+    nothing hangs or traps, and the healthy statistics of the same call are factored as if they were alone."""
+    good = spd(256, 1e3, 21)
+    bad_nan = torch.full((256, 256), float("nan"))
+    bad_inf = spd(256, 1e3, 22)
+    bad_inf[3, 3] = float("inf")
+    alone = ops.inv_roots(good.unsqueeze(0).cuda(), DAMPING, 4, 1)[0][0]
+    lo, _, _, status = ops.inv_roots(torch.stack([bad_nan, good, bad_inf]).cuda(), DAMPING, 4, 1)
+    ops.assert_healthy()                       # no bounded wait ran out: the kernels finished normally
+    assert status.tolist() == [2, 0, 2]
+    assert torch.equal(lo[1], alone)

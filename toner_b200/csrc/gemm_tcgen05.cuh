@@ -245,7 +245,8 @@ __device__ __forceinline__ void epilogue_block_vec(const GemmParams& p, const Ep
   ssq += p.tri ? 2.f * s : s;
   mabs = fmaxf(mabs, m);
   maff = fmaxf(maff, fabsf(p.aff_b) * m);  // off the diagonal the affine map is a plain scaling
-  mres = fmaxf(mres, m);                   // and the distance from the identity is |d|
+  // and the distance from the identity is |d|; fmaxf drops NaN, the sum of squares does not
+  mres = fmaxf(mres, isfinite(s) ? m : INFINITY);
   if (mirror) {
     __syncwarp();
     const int tcol = row_first + 4 * q;  // source rows 4q .. 4q+3 become four consecutive target columns
@@ -287,7 +288,7 @@ __device__ __forceinline__ void epilogue_block_scalar(const GemmParams& p, const
       const float dg = (col == row) ? 1.f : 0.f;
       if (e.S0b) store_split1(e.S0b + (long long)row * p.s_ld + col, p.s_plane, p.s0_scale * v);
       if (e.S1b) store_split1(e.S1b + (long long)row * p.s_ld + col, p.s_plane, p.s1_scale * fmaf(p.s1_aff_b, v, p.s1_aff_a * dg));
-      mres = fmaxf(mres, fabsf(dg - v));
+      mres = isfinite(v) ? fmaxf(mres, fabsf(dg - v)) : INFINITY;  // a non-finite result must not pass as converged
       const float w = (p.tri && col > row) ? 2.f : 1.f;
       ssq = fmaf(w * v, v, ssq);
       mabs = fmaxf(mabs, fabsf(v));
