@@ -35,6 +35,10 @@ long long toner_launch_count(void);       /* kernels launched by this library so
 /* Synchronise `stream`, then read and clear the device status word that kernels set when one of their
  * bounded waits runs out (0 = healthy). */
 int toner_device_status(void* stream, int* status_out);
+/* Self-test of that mechanism (the reference has no device-side waits): launches a one-warp kernel whose wait can
+ * never be satisfied and gives up after `limit_cycles` SM cycles (at most 2e9).  The kernel returns normally, the
+ * next toner_device_status reports 199, and the context stays usable. */
+int toner_selftest_bounded_wait(long long limit_cycles, void* stream);
 
 /* ------------------------------------------------------------------ generic tensor-core product
  * D[b] = alpha * sum_s A_s[b] * B_s[b]^T (+ beta * C[b]), 16-bit operands, FP32 accumulation in tensor

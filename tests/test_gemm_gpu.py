@@ -194,3 +194,20 @@ def test_cta_pair_symmetric_split_product_matches_single_cta_tiles(ops, promote)
         assert torch.equal(out[tile][0], out[tile][0].transpose(1, 2))
     assert torch.equal(out[256][0], out[512][0])        # same accumulation order, same bits
     assert torch.equal(out[256][1], out[512][1])
+
+
+def test_a_wait_that_runs_out_is_reported_not_fatal(ops):
+    """Failure detection on the device: a wait nothing will satisfy gives up after its limit, the kernel returns, the
+    host reads the status word (and clears it), and the next product on the same context is correct."""
+    import ctypes as C
+    from toner_b200 import _lib
+    lib = _lib.load()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.toner_selftest_bounded_wait(C.c_longlong(2_000_000), stream) == 0      # about a millisecond
+    assert ops.device_status() == 199
+    assert ops.device_status() == 0                                                    # read-and-clear
+    a, b = rnd((128, 64), torch.bfloat16, 5), rnd((128, 64), torch.bfloat16, 6)
+    d = torch.zeros(1, 128, 128, device="cuda")
+    ops.gemm(ops.operand(a), ops.operand(b), m=128, n=128, k=64, batch=1, fmt=1, d=d)
+    ops.assert_healthy()
+    close(d[0], ref_mm(a, b, False, False), 64)

@@ -33,7 +33,7 @@ constexpr int kMaxSegs = 3;
 constexpr int kGemmThreads = 384;      // warpgroup 0: TMA warp, MMA warp, two idle; warpgroups 1-2: epilogue
 constexpr long long kWaitCycles = 4000000000LL;  // about two seconds; a healthy wait is microseconds
 
-enum GemmStatus : int { kOk = 0, kTimeoutProducer = 101, kTimeoutMma = 102, kTimeoutEpilogue = 103 };
+enum GemmStatus : int { kOk = 0, kTimeoutProducer = 101, kTimeoutMma = 102, kTimeoutEpilogue = 103, kTimeoutSelftest = 199 };
 
 struct GemmParams {
   // operands: arrays of 3-D tensor maps (inner, outer, z) in global memory

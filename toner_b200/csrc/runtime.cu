@@ -251,6 +251,19 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
   return 0;
 }
 
+// A wait that nothing will ever satisfy: the barrier expects one arrival and gets none.  The wait gives up after
+// `limit_cycles`, reports through the status word like the GEMM's waits do, and the kernel returns normally.
+__global__ void bounded_wait_selftest_kernel(long long limit_cycles, int* status) {
+  __shared__ unsigned long long bar;
+  const uint32_t b = ptx::smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(b, 1);
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && !ptx::mbar_wait(b, 0, limit_cycles)) report(status, kTimeoutSelftest);
+}
+
 }  // namespace toner
 
 // ------------------------------------------------------------------ C ABI: library + generic GEMM
@@ -282,6 +295,17 @@ int toner_device_status(void* stream, int* status_out) {
   TONER_CUDA(cudaStreamSynchronize(s));
   if (v != 0) TONER_CUDA(cudaMemsetAsync(c->status_dev, 0, sizeof(int), s));
   *status_out = v;
+  return 0;
+}
+
+int toner_selftest_bounded_wait(long long limit_cycles, void* stream) {
+  toner::Context* c = toner::context();
+  if (!c) return toner::kErrCuda;
+  if (limit_cycles <= 0 || limit_cycles > 2000000000LL)
+    return toner::fail(toner::kErrArg, "selftest: the limit must be between 1 and 2e9 cycles");
+  toner::bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_cycles, c->status_dev);
+  toner::count_launch();
+  TONER_CUDA(cudaGetLastError());
   return 0;
 }
 
