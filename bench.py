@@ -219,15 +219,18 @@ def run_ours(args) -> None:
     if rank == 0:
         pk = peaks()
         # products per statistic: X T and T^2 T^4 T^8 T^8 M per Newton step (no X product in the first, no M update
-        # in the last), two squarings for A^-1/2; the step count follows each group's spectrum bound
-        it_d, it_f = core.groups["d"].factors.iterations, core.groups["f"].factors.iterations
+        # in the last), two squarings for A^-1/2 -- each three FP16 plane passes -- plus the single-pass products of
+        # the finishing series (its order - 1); the step count follows each group's spectrum bound
+        fd, ff = core.groups["d"].factors, core.groups["f"].factors
+        it_d, it_f = fd.iterations, ff.iterations
+        single_d, single_f = fd.finish_order - 1, ff.finish_order - 1
         if args.optimizer == "adamt":   # p = 4: X T, T^2, T^4, T^4 M per step, no squarings afterwards
-            gemms_d, gemms_f = (it_d - 1) * 4, (it_f - 1) * 4
-            fl = step_flops(layers, hidden, mlp, local_rows * world, gemms_d, gemms_f, ns_steps=0, products=5)
+            split_d, split_f = (it_d - 1) * 4, (it_f - 1) * 4
+            fl = step_flops(layers, hidden, mlp, local_rows * world, split_d + single_d, split_f + single_f, ns_steps=0,
+                            products=5)
         else:
-            gemms_d, gemms_f = (it_d - 1) * 5 + 2, (it_f - 1) * 5 + 2
-            fl = step_flops(layers, hidden, mlp, local_rows * world, gemms_d, gemms_f)
-        gemms = gemms_f
+            split_d, split_f = (it_d - 1) * 5 + 2, (it_f - 1) * 5 + 2
+            fl = step_flops(layers, hidden, mlp, local_rows * world, split_d + single_d, split_f + single_f)
         ph = phases[-1] if phases and phases[-1] else {}
         per_phase = {}
         for name, work in (("stats", fl["syrk"]), ("roots", fl["roots"]), ("update", fl["ns"] + fl["precond"])):
@@ -248,9 +251,10 @@ def run_ours(args) -> None:
             if top == "roots":
                 # what the tensor cores execute: three FP16 plane products per accumulator, on the 128x256 tiles
                 # that meet the upper triangle (fractions 0.5625 at n=2048, 0.523 at n=5632)
-                ex = (3 * layers * gemms_d * 2 * hidden ** 3 * 3 * tri_fraction(hidden, 256) +
-                      layers * gemms_f * 2 * mlp ** 3 * 3 * tri_fraction(mlp, 256)) / world / ph[top] / 1e9
+                ex = (3 * layers * (3 * split_d + single_d) * 2 * hidden ** 3 * tri_fraction(hidden, 256) +
+                      layers * (3 * split_f + single_f) * 2 * mlp ** 3 * tri_fraction(mlp, 256)) / world / ph[top] / 1e9
                 roof["newton_steps"] = {"hidden": it_d, "mlp": it_f}
+                roof["finish_order"] = {"hidden": fd.finish_order, "mlp": ff.finish_order}
                 roof["executed"] = round(ex, 1)
                 roof["frac_executed"] = round(ex / pk["tflops"], 4)
         line = {

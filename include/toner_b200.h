@@ -155,9 +155,12 @@ int toner_split16(const float* x, const float* const* x_list, int32_t batch, int
  *     fro2_lo[b] = ||root_lo[b]||_F^2  (gives the decay normalisation n / ||R||_F^2, src/toner/linalg.py:87-88)
  * Method: coupled Newton iteration T = a I - b M, X <- X T, M <- T^p M with minimax-scaled (a, b), batched
  * over the k statistics, all products FP32-accurate on tensor cores (FP16 hi/lo planes, three plane products
- * per accumulator).  `iters` <= 0 selects toner_inv_roots_iterations(n, damping, p), which depends only on
- * its arguments (9 for p = 8, 10 for p = 4, 12 for p = 2 at n = 5632, damping 1e-3).
- * status[b] (DEVICE, optional): 0 converged, 1 residual max|I - M| above 0.05 before the last step,
+ * per accumulator).  The last of the `iters` steps applies the binomial series of (I - R)^(-1/p), R = I - M, to X
+ * alone; its order (toner_inv_roots_finish_order_for) follows from the bound on R the schedule guarantees, and
+ * its order - 1 products are single passes over FP16 planes of R.
+ * `iters` <= 0 selects toner_inv_roots_iterations(n, damping, p), which depends only on
+ * its arguments (8 for p = 8, 9 for p = 4, 10 for p = 2 at n = 5632, damping 1e-3).
+ * status[b] (DEVICE, optional): 0 converged, 1 residual max|I - M| above 0.5 before the last step,
  * 2 non-finite.  The caller decides what to do with a non-zero status (the Python host recomputes that
  * statistic with an eigendecomposition, as the reference's fallback does, src/toner/fast/engine.py:714-731).
  * Workspace: toner_inv_roots_workspace_bytes(chunk, n) lets `chunk` statistics be processed at once; a
@@ -165,6 +168,8 @@ int toner_split16(const float* x, const float* const* x_list, int32_t batch, int
 size_t toner_inv_roots_workspace_bytes(int32_t chunk, int32_t n);
 int toner_inv_roots_iterations(int32_t n, float damping, int32_t p);
 int toner_inv_roots_iterations_for(float lower, int32_t p);   /* the count for a given spectrum lower bound */
+/* order of the finishing series for that bound and count (iters <= 0: the default count); 0 on bad arguments */
+int toner_inv_roots_finish_order_for(float lower, int32_t p, int32_t iters);
 int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
                     float* root_lo, float* root_hi, float* fro2_lo, int32_t* status, void* workspace,
                     size_t workspace_bytes, void* stream);

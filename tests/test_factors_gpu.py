@@ -110,10 +110,36 @@ def test_chunked_workspace_gives_identical_roots(ops):
 
 
 def test_iteration_counts_are_stated(ops):
-    assert ops.inv_roots_iterations(5632, 1e-3, 8) == 9
-    assert ops.inv_roots_iterations(5632, 1e-3, 4) == 10
-    assert ops.inv_roots_iterations(5632, 1e-3, 2) == 12
+    assert ops.inv_roots_iterations(5632, 1e-3, 8) == 8
+    assert ops.inv_roots_iterations(5632, 1e-3, 4) == 9
+    assert ops.inv_roots_iterations(5632, 1e-3, 2) == 10
     assert ops.inv_roots_iterations(768, 1e-3, 8) <= 10
+
+
+@pytest.mark.parametrize("p,q", [(8, 4), (4, 1), (2, 1)])
+def test_finishing_series_at_every_order(ops, p, q):
+    """The iteration stops as soon as the spectrum of M is within 0.4 of 1 and finishes with a series whose order
+    follows from that distance.  Sweeping the caller's bound moves the stopping point, so orders from 2 up to the
+    cap are exercised; every one must give the same roots as FP64 truth."""
+    n = 384
+    stats = torch.stack([spd(n, 3e2, 11), spd(n, 1e3, 12)]).cuda()
+    norms = torch.zeros(2, device="cuda")
+    ops.inv_roots(stats, DAMPING, p, q, norms=norms)
+    top = 0.99 * DAMPING / norms.max().item()          # the largest bound both statistics satisfy
+    truth = [(orc.inverse_root_truth(c.cpu(), 1.0 / p, DAMPING), orc.inverse_root_truth(c.cpu(), q / p, DAMPING))
+             for c in stats]
+    orders = set()
+    for k in range(14):
+        lower = top * 0.6 ** k
+        orders.add(ops.inv_roots_finish_order(n, DAMPING, p, lower))
+        lo, hi, _, st = ops.inv_roots(stats, DAMPING, p, q, lower=lower)
+        ops.assert_healthy()
+        assert st.tolist() == [0, 0], (k, st.tolist())
+        for b in range(2):
+            assert orc.rel_fro(lo[b].cpu(), truth[b][0]) < 5e-5, (k, b)
+            if q > 1:
+                assert orc.rel_fro(hi[b].cpu(), truth[b][1]) < 2e-4, (k, b)
+    assert min(orders) <= 4 and max(orders) >= 7 and len(orders) >= 4, orders
 
 
 def test_callers_spectrum_bound_saves_steps_and_is_checked(ops):

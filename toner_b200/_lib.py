@@ -66,6 +66,7 @@ SIGNATURES = {
     "toner_inv_roots_iterations": (C.c_int, [_i32, _f32, _i32]),
     "toner_inv_roots": (C.c_int, [_vp, _i32, _i32, _f32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "toner_inv_roots_iterations_for": (C.c_int, [_f32, _i32]),
+    "toner_inv_roots_finish_order_for": (C.c_int, [_f32, _i32, _i32]),
     "toner_inv_roots_ex": (C.c_int, [_vp, _i32, _i32, _f32, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "toner_ns_polar_workspace_bytes": (C.c_size_t, [_i32, _i32, _i32]),
     "toner_ns_polar": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _sz, _vp]),

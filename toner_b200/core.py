@@ -110,6 +110,7 @@ class FactorSet:
             chunk = max(1, min(k, budget // per))
         self.workspace = self.scratch.bytes_like("inv_roots", ops.inv_roots_workspace_bytes(chunk, n), device)
         self.iterations = ops.inv_roots_iterations(n, self.damping, self.p)
+        self.finish_order = ops.inv_roots_finish_order(n, self.damping, self.p)
         self.fallbacks = 0
         self.repairs = 0
 
@@ -144,6 +145,7 @@ class FactorSet:
                       norms=self.norms)
         self.iterations = (ops.inv_roots_iterations_for(self.lower, self.p) if self.lower > 0
                            else ops.inv_roots_iterations(self.n, self.damping, self.p))
+        self.finish_order = ops.inv_roots_finish_order(self.n, self.damping, self.p, self.lower)
         self._split()
         self.status_host.copy_(self.status, non_blocking=True)
         self.norms_host.copy_(self.norms, non_blocking=True)

@@ -5,6 +5,7 @@
 //   A'  = A - (lambda_1 - c) v v^T                            (dominant direction deflated when power iteration finds it)
 //   M_0 = A' / beta,  beta >= lambda_max(A')                  (beta = min(||A'||_F, 1.04 ||A'||_F ||P^2||_F^(1/2)), P = A'/||A'||_F)
 //   T_k = a_k I - b_k M_k ;  X_{k+1} = X_k T_k ;  M_{k+1} = T_k^p M_k          (X_0 = I)
+//   X_K = X_{K-1} (I + a1 R + a2 R^2 + a3 R^3),  R = I - M_{K-1}                (binomial series of (I - R)^(-1/p))
 //   X_K ~ M_0^{-1/p}  =>  A^{-1/p} = X_K beta^{-1/p} + (lambda_1^{-1/p} - c^{-1/p}) v v^T
 // (a_k, b_k) map the interval [l_k, 1] known to contain the spectrum of M_k onto [l_{k+1}, 1] with
 // l_{k+1} as large as a linear T allows (the ends of the interval and the interior maximum of
@@ -80,13 +81,34 @@ constexpr int kPromoteX = 0;
 // power-iteration steps spent on the dominant direction (each one pass over the statistic)
 constexpr int kPowerSteps = 6;
 
+// The last step does not square the error once more; it finishes with the binomial series of (I - R)^(-1/p),
+// R = I - M:  X <- X (I + a_1 R + a_2 R^2 + ... + a_m R^m), a_j = a_{j-1} (1/p + j - 1) / j.  The spectrum of R lies
+// in [0, e] with e known from the schedule, so the order m is fixed in advance: the smallest whose tail
+// a_{m+1} e^{m+1} / (1 - e) is below 4e-6.  The powers come from m - 1 single-pass products of FP16 planes in Horner
+// form (a third of a split-precision product each; R is small, so its rounding to FP16 costs about 5e-4 a_2 e^2), which
+// is cheaper than the log2(p) + 2 split-precision products of one more Newton step for every e up to kFinishRadius.
+constexpr double kFinishRadius = 0.4;
+constexpr int kMaxFinishOrder = 10;
+constexpr double kFinishTail = 4e-6;
+
+static double finish_coefficient(int p, int j) {
+  double a = 1.0;
+  for (int i = 1; i <= j; ++i) a *= (1.0 / p + i - 1) / i;
+  return a;
+}
+static int finish_order(int p, double e) {
+  if (e >= 1.0) return kMaxFinishOrder;
+  for (int m = 2; m < kMaxFinishOrder; ++m)
+    if (finish_coefficient(p, m + 1) * std::pow(e, m + 1) / (1.0 - e) < kFinishTail) return m;
+  return kMaxFinishOrder;
+}
+
 static int default_iterations(double l0, int p) {
-  // steps until the spectrum is within 4e-3 of 1, plus one last Newton step applied to X alone: it squares that
-  // distance ((p+1)/(2p) e^2 < 1e-5), which leaves X within 1e-6 of the root -- below the operand precision
+  // steps of M until its spectrum is within the finishing radius of 1, plus the finishing step applied to X alone
   for (int k = 1; k < 64; ++k) {
     double l;
     newton_schedule(l0, p, k, &l);
-    if (1.0 - l < 4e-3) return k + 1;
+    if (1.0 - l < kFinishRadius) return k + 1;
   }
   return 64;
 }
@@ -373,6 +395,15 @@ int toner_inv_roots_iterations_for(float lower, int32_t p) {
   return toner::default_iterations((double)lower, p);
 }
 
+int toner_inv_roots_finish_order_for(float lower, int32_t p, int32_t iters) {
+  if (!(lower > 0.f) || !(lower < 1.f) || p < 1) return 0;
+  if (iters <= 0) iters = toner::default_iterations((double)lower, p);
+  if (iters < 2) return 0;
+  double l_last;
+  toner::newton_schedule((double)lower, p, iters - 1, &l_last);
+  return toner::finish_order(p, 1.0 - l_last);
+}
+
 int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
                     float* root_lo, float* root_hi, float* fro2_lo, int32_t* status, void* workspace,
                     size_t workspace_bytes, void* stream_) {
@@ -403,6 +434,9 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
   if (iters <= 0) iters = default_iterations(l0, p);
   if (iters < 2) return fail(kErrArg, "inv_roots: at least two iterations are required");
   const std::vector<NewtonStep> sched = newton_schedule(l0, p, iters, nullptr);
+  double l_last;  // lower bound of the spectrum of the last M, i.e. after iters - 1 updates
+  newton_schedule(l0, p, iters - 1, &l_last);
+  const int order = finish_order(p, 1.0 - l_last);
   int log2p = 0;
   while ((1 << log2p) < p) ++log2p;
 
@@ -526,6 +560,9 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
       __half* s0 = nullptr; float s0_scale = 0.f;
       __half* s1 = nullptr; float s1_scale = 0.f, s1_a = 0.f, s1_b = 0.f;
       unsigned int* maxres = nullptr;
+      const float* c = nullptr; float beta = 0.f;  // result = gain * product + beta * c (c symmetric, FP32)
+      double gain = 1.0;
+      int segs = 3;                                // 1: hi planes only (a single pass)
     };
     auto sym_product = [&](const __half* ap, float sa, const __half* bp, float sb, const Out& o, int promote) -> int {
       toner_gemm_desc g = {};
@@ -535,9 +572,10 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
       g.b = op; g.b.base = bp;
       g.a.seg_z[0] = 0; g.a.seg_z[1] = 0; g.a.seg_z[2] = kc;   // Ah Ah Al
       g.b.seg_z[0] = 0; g.b.seg_z[1] = kc; g.b.seg_z[2] = 0;   // Bh Bl Bh
-      g.m = n; g.n = n; g.k = n; g.batch = kc; g.segs = 3; g.fmt = 0;
+      g.m = n; g.n = n; g.k = n; g.batch = kc; g.segs = o.segs; g.fmt = 0;
       g.tri = 1; g.mirror = 1;
-      g.alpha = (float)(1.0 / ((double)sa * (double)sb));
+      g.alpha = (float)(o.gain / ((double)sa * (double)sb));
+      g.c = o.c; g.ldc = n; g.c_bs = nn; g.beta = o.beta;
       g.alpha_a = o.alpha_a;
       g.alpha_b = o.alpha_b;
       g.d = o.d; g.ldd = n; g.d_bs = nn;
@@ -562,15 +600,37 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
         if (last) {
           // fold ||A||_F^{-1/p} into the product; the distance of M from I was gathered when M was produced
           finish_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(resid, sumsq_a, scale_lo, status ? status + k0 : nullptr,
-                                                            norm_out ? norm_out + k0 : nullptr, kc, p, 0.05f, damping,
+                                                            norm_out ? norm_out + k0 : nullptr, kc, p, 0.5f, damping,
                                                             lower_used);
           count_launch();
           TONER_CUDA(cudaGetLastError());
+          // Tcur holds planes of R = I - M and A32 the FP32 M (both from the last update of M).  Horner steps
+          // W_j = a_j R + R W_{j+1} (W_m = a_m R) build T = I + W_1; the terms linear in M enter in FP32 as beta * c.
+          const float s_w = plane_scale(1.0), s_f = plane_scale(2.0);
+          const __half* wcur = Tcur;
+          float s_cur = s_t;
+          double gain = finish_coefficient(p, order);
+          for (int j = order - 1; j >= 1; --j) {
+            const double aj = finish_coefficient(p, j);
+            Out w;
+            w.segs = 1;
+            w.gain = gain;
+            w.c = A32; w.beta = (float)-aj;
+            w.s1 = Mb[j & 1];
+            w.s1_scale = (j == 1) ? s_f : s_w;
+            w.s1_a = (float)(j == 1 ? 1.0 + aj : aj);
+            w.s1_b = 1.f;
+            rc = sym_product(Tcur, s_t, wcur, s_cur, w, 0);
+            if (rc) return rc;
+            wcur = w.s1;
+            s_cur = w.s1_scale;
+            gain = 1.0;
+          }
           float* R = root_lo + (long long)k0 * nn;
           Out o;
           o.d = R;
           o.alpha_a = scale_lo;
-          rc = sym_product(Xcur, s_x, Tcur, s_t, o, kPromoteX);
+          rc = sym_product(Xcur, s_x, Mb[1], s_f, o, kPromoteX);
           if (rc) return rc;
           // put the deflated direction back: A^{-1/p} = A'^{-1/p} + (lambda_1^{-1/p} - c^{-1/p}) v v^T
           rank1_update_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(R, pv, corr, n);
@@ -616,13 +676,21 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
         const float na = (float)sched[it + 1].a, nb = (float)sched[it + 1].b;
         const int tn = (log2p == 0) ? (ti ^ 1) : ti;  // with p == 1 the product reads T itself
         Out o;
-        o.s0 = Mb[mi ^ 1];
-        o.s0_scale = s_m;
         o.s1 = Tb[tn];
-        o.s1_scale = plane_scale(na);
-        o.s1_a = na;
-        o.s1_b = -nb;
-        if (it == iters - 2) o.maxres = resid;
+        if (it == iters - 2) {
+          // the last M: kept in FP32 with planes of R = I - M for the finishing series, and its distance from I
+          o.d = A32;
+          o.s1_scale = s_m;
+          o.s1_a = 1.f;
+          o.s1_b = -1.f;
+          o.maxres = resid;
+        } else {
+          o.s0 = Mb[mi ^ 1];
+          o.s0_scale = s_m;
+          o.s1_scale = plane_scale(na);
+          o.s1_a = na;
+          o.s1_b = -nb;
+        }
         rc = sym_product(pw, s_pw, Mb[mi], s_m, o, chain);
         if (rc) return rc;
         mi ^= 1;

@@ -258,6 +258,13 @@ def inv_roots_iterations_for(lower: float, p: int) -> int:
     return _lib.load().toner_inv_roots_iterations_for(lower, p)
 
 
+def inv_roots_finish_order(n: int, damping: float, p: int, lower: float = 0.0, iters: int = 0) -> int:
+    """Order of the series that finishes the iteration (its order - 1 products are single passes); `lower` = 0
+    means the bound damping / (n (1 + damping)) that always holds."""
+    worst = damping / (n * (1.0 + damping))
+    return _lib.load().toner_inv_roots_finish_order_for(max(lower, worst), p, iters)
+
+
 def inv_roots(ema: torch.Tensor, damping: float, p: int, q: int = 1, *, iters: int = 0,
               root_lo: Optional[torch.Tensor] = None, root_hi: Optional[torch.Tensor] = None,
               fro2_lo: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
