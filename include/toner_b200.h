@@ -130,6 +130,31 @@ int toner_syrk_upper(const void* const* x_list, const void* x_base, int64_t x_ba
 int toner_gather_rows(const void* x, int32_t x_is_fp32, int32_t batch, int32_t seq, int32_t n, int64_t batch_stride,
                       int64_t row_stride, const int32_t* positions, int32_t count, void* dst, void* stream);
 
+/* Row capture for a whole model in one launch: every job writes the sampled rows of one micro-batch into one
+ * statistic's row buffer, copied or recomputed from tensors the forward pass keeps anyway.  For job j and sampled
+ * row r = b * positions + p:   src = a + b * batch_stride + idx[p] * row_stride;   dst row = at[r]  (width elements)
+ *   TONER_CAPTURE_COPY      dst = a row                                         (a BF16)
+ *   TONER_CAPTURE_RMSNORM   out = bf16(x * rsqrt(mean(x^2) + eps)); dst = bf16(float(bf16(w)) * float(out))
+ *                           (a = x BF16, b = w FP32 of `width` elements: the model's BF16-residual RMSNorm)
+ *   TONER_CAPTURE_SILU_MUL  dst = bf16(g * (1 / (1 + exp(-g))) * u) in FP32     (a = g, b = u, both BF16, same strides)
+ * The job table is passed twice: `jobs_host` is validated, `jobs_device` (the same n_jobs entries in device memory)
+ * is what the kernel reads; a caller keeps both for as long as the tensors' addresses repeat.  `at` and `idx` are
+ * DEVICE int64 arrays of batch*positions and positions entries (not range-checked).  Widths and strides in
+ * elements, multiples of 8; pointers 16-byte aligned; destination buffers are (capacity, width) BF16, contiguous.
+ * Replaces capture_rows / capture_recomputed and their kernels _gather_rows, _norm_rows, _silu_mul_rows
+ * (reproduce/marin/ops.py:10-27,30-54,63-100,107-163), four launches per micro-batch there. */
+enum { TONER_CAPTURE_COPY = 0, TONER_CAPTURE_RMSNORM = 1, TONER_CAPTURE_SILU_MUL = 2 };
+typedef struct toner_capture_job {
+  const void* a;
+  const void* b;
+  void* dst;
+  int64_t batch_stride, row_stride;
+  int32_t width;
+  int32_t kind;
+} toner_capture_job;
+int toner_capture(const toner_capture_job* jobs_device, const toner_capture_job* jobs_host, int32_t n_jobs,
+                  const int64_t* at, const int64_t* idx, int32_t batch, int32_t positions, float eps, void* stream);
+
 /* C_b <- beta*C_b + gamma*S_b with S_b read from its packed upper triangle and mirrored.
  * Replaces unpack_ema_ (src/toner/fast/syrk.py:220-247); general-path EMA src/toner/reference.py:79. */
 int toner_unpack_ema(const float* packed, float* ema, int32_t k, int32_t n, float beta, float gamma, void* stream);

@@ -1,0 +1,121 @@
+"""Row capture on the GPU (toner_capture) against the CPU oracle and the reference-made fixture.
+
+Copied rows must be bit-exact.  The recomputed rows round an FP32 value to BF16 once or twice; the FP32 value can
+differ from the oracle's in its last bits (summation order of the mean square, exp), which moves a rounding now and
+then: at most one BF16 unit in the last place, on a small share of the elements."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import capture_oracle as cap
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "capture.npz"))
+
+
+@pytest.fixture(scope="module")
+def capture():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from toner_b200 import capture as _capture
+    return _capture
+
+
+def bf16(name):
+    return torch.from_numpy(GOLD[name].copy()).view(torch.bfloat16)
+
+
+def close_rows(got, want, share):
+    ulps = cap.bf16_ulps(got.cpu(), want)
+    assert int(ulps.max()) <= 1, int(ulps.max())
+    assert float((ulps > 0).float().mean()) <= share, float((ulps > 0).float().mean())
+
+
+def test_fixture_from_the_references_model(capture):
+    from toner_b200 import ops
+    idx, eps = torch.from_numpy(GOLD["idx"]).cuda(), float(GOLD["eps"])
+    rows, h = int(GOLD["batch"]) * idx.numel(), int(GOLD["hidden"])
+    g = torch.Generator().manual_seed(1)
+    gate = torch.randn(int(GOLD["batch"]), int(GOLD["seq"]), 2 * h, generator=g).to(torch.bfloat16)
+    up = torch.randn(int(GOLD["batch"]), int(GOLD["seq"]), 2 * h, generator=g).to(torch.bfloat16)
+    bufs = [torch.zeros(rows, w, dtype=torch.bfloat16, device="cuda") for w in (h, h, h, 2 * h)]
+    capture.capture_recomputed([bf16("x").cuda()], [bf16("attn").cuda()], [bf16("xmid").cuda()], [gate.cuda()], [up.cuda()],
+                               [torch.from_numpy(GOLD["w1"]).cuda()], [torch.from_numpy(GOLD["w2"]).cuda()], bufs,
+                               torch.arange(rows, device="cuda"), idx, eps)
+    ops.assert_healthy()
+    close_rows(bufs[0], bf16("rows_attn"), 0.01)
+    assert torch.equal(bufs[1].cpu(), bf16("rows_o"))
+    close_rows(bufs[2], bf16("rows_mlp"), 0.01)
+    close_rows(bufs[3], cap.silu_mul_rows(gate, up, idx.cpu()), 0.01)
+
+
+def test_two_llama_layers_at_full_width_into_the_middle_of_the_buffers(capture):
+    """Hidden 2048 / MLP 5632, 4096-token sequences, 286 sampled positions; the destination rows are a reversed range
+    starting at 100 (a later micro-batch's slot), and nothing else in the buffers may change."""
+    from toner_b200 import ops
+    from toner_b200.statistics import sample_positions
+    layers, batch, seq, d, dm, eps = 2, 2, 4096, 2048, 5632, 1e-5
+    idx = torch.tensor(sample_positions(seq, 32, 16))
+    rows = batch * idx.numel()
+    at = torch.arange(rows).flip(0) + 100
+    g = torch.Generator().manual_seed(3)
+    mk = lambda w, s: [(torch.randn(batch, seq, w, generator=g) * s).to(torch.bfloat16) for _ in range(layers)]
+    xs, attn, xmid, gs, us = mk(d, 1.0), mk(d, 0.3), mk(d, 4.0), mk(dm, 2.0), mk(dm, 1.0)
+    w1 = [1.0 + 0.1 * torch.randn(d, generator=g) for _ in range(layers)]
+    w2 = [1.0 + 0.1 * torch.randn(d, generator=g) for _ in range(layers)]
+    want = [torch.full((rows + 200, w), 3.0, dtype=torch.bfloat16) for _ in range(layers) for w in (d, d, d, dm)]
+    cap.capture_recomputed(xs, attn, xmid, gs, us, w1, w2, want, at, idx, eps)
+    bufs = [torch.full((rows + 200, w), 3.0, dtype=torch.bfloat16, device="cuda") for _ in range(layers) for w in (d, d, d, dm)]
+    cu = lambda ts: [t.cuda() for t in ts]
+    args = (cu(xs), cu(attn), cu(xmid), cu(gs), cu(us), cu(w1), cu(w2), bufs, at.cuda(), idx.cuda(), eps)
+    capture.capture_recomputed(*args)
+    tables = len(capture._TABLES)
+    capture.capture_recomputed(*args)                   # same addresses: the job table is reused
+    assert len(capture._TABLES) == tables
+    ops.assert_healthy()
+    for l in range(layers):
+        for j, share in enumerate((2e-3, 0.0, 2e-3, 2e-3)):
+            got, ref = bufs[4 * l + j], want[4 * l + j]
+            if share == 0.0:
+                assert torch.equal(got.cpu(), ref)
+            else:
+                close_rows(got, ref, share)
+            assert torch.all(got[:100] == 3.0) and torch.all(got[100 + rows:] == 3.0)
+
+
+def test_capture_rows_with_mixed_widths_and_strided_sources(capture):
+    from toner_b200 import ops
+    g = torch.Generator().manual_seed(9)
+    big = torch.randn(3, 64, 512, generator=g).to(torch.bfloat16)
+    a, b = big[:, :, :256], big[:, 8:40, 256:384]       # views: feature slices, a window of the sequence
+    c = torch.randn(3, 64, 64, generator=g).to(torch.bfloat16)
+    idx = torch.tensor([0, 3, 4, 31])
+    at = torch.tensor([5, 1, 7, 3, 0, 2, 9, 11, 4, 6, 8, 10])
+    want = [torch.zeros(12, w, dtype=torch.bfloat16) for w in (256, 128, 64)]
+    cap.capture_rows([a, b, c], want, at, idx)
+    dev = big.cuda()
+    bufs = [torch.zeros(12, w, dtype=torch.bfloat16, device="cuda") for w in (256, 128, 64)]
+    capture.capture_rows([dev[:, :, :256], dev[:, 8:40, 256:384], c.cuda()], bufs, at.cuda(), idx.cuda())
+    ops.assert_healthy()
+    for got, ref in zip(bufs, want):
+        assert torch.equal(got.cpu(), ref)
+
+
+def test_bad_arguments_are_refused(capture):
+    from toner_b200._lib import TonerError
+    x = torch.zeros(1, 16, 12, dtype=torch.bfloat16, device="cuda")      # width not a multiple of 8
+    buf = torch.zeros(4, 12, dtype=torch.bfloat16, device="cuda")
+    at, idx = torch.arange(4, device="cuda"), torch.arange(4, device="cuda")
+    with pytest.raises(TonerError):
+        capture.capture_rows([x], [buf], at, idx)
+    y = torch.zeros(1, 16, 16, dtype=torch.float32, device="cuda")
+    with pytest.raises(ValueError):
+        capture.capture_rows([y], [torch.zeros(4, 16, dtype=torch.bfloat16, device="cuda")], at, idx)
+    z = torch.zeros(1, 16, 16, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        capture.capture_rows([z], [torch.zeros(4, 16, dtype=torch.bfloat16, device="cuda")], at.int(), idx)
+    with pytest.raises(ValueError):
+        capture.capture_rows([z], [torch.zeros(4, 16, dtype=torch.bfloat16, device="cuda")], at[:3], idx)

@@ -29,6 +29,14 @@ class Operand(C.Structure):
     ]
 
 
+class CaptureJob(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("b", C.c_void_p), ("dst", C.c_void_p),
+        ("batch_stride", C.c_int64), ("row_stride", C.c_int64),
+        ("width", C.c_int32), ("kind", C.c_int32),
+    ]
+
+
 class GemmDesc(C.Structure):
     _fields_ = [
         ("a", Operand), ("b", Operand),
@@ -73,6 +81,7 @@ SIGNATURES = {
     "toner_sumsq_scratch_bytes": (C.c_size_t, [_i32]),
     "toner_sumsq": (C.c_int, [_vp, _i32, _i32, _i32, _i64, _i64, _vp, _vp, _vp]),
     "toner_gather_rows": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _i64, _i64, _vp, _i32, _vp, _vp]),
+    "toner_capture": (C.c_int, [_vp, _vp, _i32, _vp, _vp, _i32, _i32, _f32, _vp]),
     "toner_sumsq_static_max_batch": (C.c_int, []),
     "toner_sumsq_static": (C.c_int, [_vp, _i32, _i32, _i32, _i64, _i64, _vp, _vp]),
     "toner_muont_momentum": (C.c_int, [_vp, _vp, _vp, _i32, _i64, _f32, _i32, _vp, _vp]),

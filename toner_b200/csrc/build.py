@@ -16,7 +16,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-SOURCES = ["runtime.cu", "stat_ops.cu", "factor_ops.cu", "update_ops.cu"]
+SOURCES = ["runtime.cu", "stat_ops.cu", "factor_ops.cu", "update_ops.cu", "capture_ops.cu"]
 HEADERS = ["ptx.cuh", "gemm_tcgen05.cuh", "runtime.cuh", os.path.join(ROOT, "include", "toner_b200.h")]
 LIB = os.path.join(HERE, "libtoner_b200.so")
 STAMP = os.path.join(HERE, ".build_stamp")

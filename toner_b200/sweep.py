@@ -229,9 +229,30 @@ def bench_update(a):
     return None
 
 
+def bench_capture(a):
+    """Recomputed row capture of one micro-batch for `--count` layers of width --n / MLP width --m (one launch)."""
+    from . import capture
+    from .statistics import sample_positions
+    layers, batch, seq, d, dm = a.count, a.batch, 4096, a.n, a.m
+    idx = torch.tensor(sample_positions(seq, 32, 16), device="cuda")
+    rows = batch * idx.numel()
+    at = torch.arange(rows, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    mk = lambda w: [torch.randn(batch, seq, w, device="cuda", generator=g).to(torch.bfloat16) for _ in range(layers)]
+    xs, attn, xmid, gs, us = mk(d), mk(d), mk(d), mk(dm), mk(dm)
+    w1 = [torch.ones(d, device="cuda") for _ in range(layers)]
+    w2 = [torch.ones(d, device="cuda") for _ in range(layers)]
+    bufs = [torch.empty(rows, w, device="cuda", dtype=torch.bfloat16) for _ in range(layers) for w in (d, d, d, dm)]
+    fn = lambda: capture.capture_recomputed(xs, attn, xmid, gs, us, w1, w2, bufs, at, idx, 1e-5)
+    ms, best = timed(fn, a.warmup, a.reps, True)
+    byts = layers * rows * 2 * (3 * 2 * d + 3 * dm)      # 2 B in + 2 B out per element; the gated rows read two inputs
+    return report("capture_rows_kernel", {"layers": layers, "batch": batch, "seq": seq, "hidden": d, "mlp": dm, "rows": rows},
+                  ms, best, bytes_=byts)
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["syrk", "roots", "ns", "gemm", "ema", "update", "all"])
+    ap.add_argument("kernel", choices=["syrk", "roots", "ns", "gemm", "ema", "update", "capture", "all"])
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--n", type=int, default=2048)
     ap.add_argument("--m", type=int, default=2048)
@@ -258,7 +279,7 @@ def main():
         raise SystemExit("the kernel sweep needs a CUDA device (there is no CPU path)")
     torch.cuda.set_device(0)
     table = {"syrk": bench_syrk, "roots": bench_roots, "ns": bench_ns, "gemm": bench_gemm, "ema": bench_ema,
-             "update": bench_update}
+             "update": bench_update, "capture": bench_capture}
     if a.kernel != "all":
         table[a.kernel](a)
         return
@@ -276,6 +297,8 @@ def main():
     b = copy.copy(a); b.n, b.k = 2048, 16
     bench_ema(b)
     bench_update(a)
+    b = copy.copy(a); b.n, b.m, b.batch = 2048, 5632, 4
+    bench_capture(b)
 
 
 if __name__ == "__main__":
