@@ -28,8 +28,9 @@ def _microbatch(rank, mb_index):
     return torch.randn(MB, SEQ, HID, generator=g)
 
 
-def _run(kind, world, rank, device, microbatches, steps=2):
-    """One process's part of `steps` optimizer steps; returns its weights."""
+def _run(kind, world, rank, device, microbatches, steps=2, first_step=0, resume=None, save_to=None):
+    """One process's part of optimizer steps first_step .. steps-1; returns its weights.  `resume` = (weights,
+    checkpoint) continues a run saved after `first_step` steps; `save_to` writes rank zero's checkpoint at the end."""
     import toner_b200.fast as fast
     from toner_b200.synthetic import make_stack
     stack = make_stack("llama", LAYERS, HID, MLP, device, seed=0)
@@ -39,7 +40,13 @@ def _run(kind, world, rank, device, microbatches, steps=2):
               micro_batch_size=MB, sequence_length=SEQ, accumulation_steps=len(microbatches), statistic_head=32,
               statistic_stride=4, **extra)
     try:
-        for step in range(steps):
+        if resume is not None:
+            weights, ckpt = resume
+            with torch.no_grad():
+                for p, w in zip([p for b in stack for p in b.parameters() if p.ndim == 2], weights):
+                    p.copy_(w)
+            opt.load_state_dict(ckpt)
+        for step in range(first_step, steps):
             for x in microbatches:
                 with opt.capture_microbatch():
                     with torch.autocast("cuda", dtype=torch.bfloat16):
@@ -56,12 +63,16 @@ def _run(kind, world, rank, device, microbatches, steps=2):
         torch.cuda.synchronize(device)
         from toner_b200 import ops
         ops.assert_healthy()
+        if save_to is not None:
+            ckpt = opt.state_dict()                          # collective; the checkpoint comes back on rank zero
+            if rank == 0:
+                torch.save(ckpt, save_to)
         return [p.detach().cpu().clone() for b in stack for p in b.parameters() if p.ndim == 2]
     finally:
         opt.close()
 
 
-def _worker(rank, world, port, kind, out_dir):
+def _worker(rank, world, port, kind, out_dir, steps=2, save=False):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE="0")
@@ -69,8 +80,9 @@ def _worker(rank, world, port, kind, out_dir):
     device = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     try:
-        weights = _run(kind, world, rank, device, [_microbatch(rank, i) for i in range(ACC)])
-        torch.save(weights, os.path.join(out_dir, f"w{rank}.pt"))
+        weights = _run(kind, world, rank, device, [_microbatch(rank, i) for i in range(ACC)], steps=steps,
+                       save_to=os.path.join(out_dir, f"ckpt{steps}.pt") if save else None)
+        torch.save(weights, os.path.join(out_dir, f"w{rank}_{steps}.pt"))
     finally:
         dist.destroy_process_group()
 
@@ -87,8 +99,31 @@ def test_two_ranks_match_one_process(tmp_path, kind):
     torch.cuda.set_device(0)
     single = _run(kind, 1, 0, torch.device("cuda", 0), [_microbatch(r, i) for r in range(world) for i in range(ACC)])
     for r in range(world):
-        got = torch.load(os.path.join(tmp_path, f"w{r}.pt"))
+        got = torch.load(os.path.join(tmp_path, f"w{r}_2.pt"))
         assert len(got) == len(single)
         for a, b in zip(got, single):
             rel = (a - b).norm().item() / b.norm().item()
             assert rel < 3e-4, (kind, r, rel)
+
+
+def test_checkpoint_saved_by_two_ranks_resumes_on_one(tmp_path):
+    """A toner.fast.v3 checkpoint gathered from two ranks after two steps is loaded into a single process, which
+    takes the third step with all microbatches; the result must match three steps on two ranks."""
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world, kind = 2, "muont"
+    mp.spawn(_worker, args=(world, _free_port(), kind, str(tmp_path), 2, True), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), kind, str(tmp_path), 3, False), nprocs=world, join=True)
+    ckpt = torch.load(os.path.join(tmp_path, "ckpt2.pt"), weights_only=False)
+    assert ckpt["format"] == "toner.fast.v3" and ckpt["core"]["t"] == 2
+    after_two = torch.load(os.path.join(tmp_path, "w0_2.pt"))
+    torch.cuda.set_device(0)
+    resumed = _run(kind, 1, 0, torch.device("cuda", 0), [_microbatch(r, i) for r in range(world) for i in range(ACC)],
+                   steps=3, first_step=2, resume=(after_two, ckpt))
+    want = torch.load(os.path.join(tmp_path, "w1_3.pt"))
+    for a, b in zip(resumed, want):
+        rel = (a - b).norm().item() / b.norm().item()
+        assert rel < 3e-4, rel
