@@ -154,3 +154,58 @@ def test_lifecycle_errors_and_checkpoint_round_trip(fast):
         assert torch.equal(core.roles["q"]["group"].m[1].cpu(), ckpt["core"]["moments"]["body.blocks.1.q.weight"]["m"])
     finally:
         opt2.close()
+
+
+@pytest.mark.parametrize("kind", ["muont", "adamt"])
+def test_row_buffers_that_hold_half_a_step(fast, kind):
+    """row_pieces=2: the row buffers hold two of the four microbatches; the first piece is folded into the partial
+    Grams when its last forward has run (chunk_stats), the second by begin().  Same weights as with buffers for the
+    whole step, up to the summation order of the statistic; a failed forward discards the folded piece too."""
+    from toner_b200 import ops
+    extra = dict(ns_steps=2) if kind == "muont" else dict(betas=(0.9, 0.95), eps=ADAM_EPS)
+
+    def run(pieces):
+        from toner_b200.synthetic import make_stack
+        stack = make_stack("llama", LAYERS, HID, MLP, torch.device("cuda"), seed=0)
+        cls = fast.FastMuonT if kind == "muont" else fast.FastAdamT
+        opt = cls([fast.ProjectionBlock.from_module(b) for b in stack], 0.02 if kind == "muont" else 2e-3, weight_decay=0.1,
+                  micro_batch_size=MB, sequence_length=SEQ, accumulation_steps=4, statistic_head=8, statistic_stride=4,
+                  row_pieces=pieces, **extra)
+        try:
+            assert opt._core.groups["d"].rows_buf.shape[1] == 4 // pieces * MB * len(orc.sample_positions(SEQ, 8, 4))
+            gen = torch.Generator().manual_seed(11)
+            for step in range(2):
+                if step == 1 and pieces > 1:       # three good microbatches, then a forward that fails: all discarded
+                    for _ in range(3):
+                        with opt.capture_microbatch():
+                            forward(stack, torch.zeros(MB, SEQ, HID, device="cuda"))
+                    with pytest.raises(RuntimeError):
+                        with opt.capture_microbatch():
+                            pass
+                    assert opt._core.pieces_done == 0
+                for mb in range(4):
+                    x = torch.randn(MB, SEQ, HID, generator=gen).cuda()
+                    with opt.capture_microbatch():
+                        forward(stack, x)
+                opt.begin()
+                for b in stack:
+                    for p in b.parameters():
+                        if p.ndim == 2:
+                            p.grad = (torch.randn(p.shape, generator=gen) * 1e-3).cuda()
+                opt.step()
+            ops.assert_healthy()
+            assert opt.diagnostics["fallbacks"] == 0
+            return [p.detach().cpu().clone() for b in stack for p in b.parameters() if p.ndim == 2]
+        finally:
+            opt.close()
+
+    # 176 sampled rows for 256-wide statistics: rank-deficient, so the factors sit on the damping floor and carry
+    # the factor engine's own accuracy (1e-4) into the weights; the statistic itself differs only in its last bits
+    whole, halves = run(1), run(2)
+    for a, b in zip(whole, halves):
+        assert orc.rel_fro(b, a) < 3e-4
+
+
+def test_row_pieces_must_divide_the_accumulation(fast):
+    with pytest.raises(ValueError):
+        make(fast, "llama", "muont", row_pieces=3)

@@ -123,7 +123,7 @@ class _FastToner(torch.optim.Optimizer):
                  inner_strength=0.5, outer_strength=0.125, statistic_momentum=0.938, statistic_head=32,
                  statistic_stride=16, ns_steps=10, ns_eps=1e-5, root_refresh=4, root_iterations=2,
                  root_inline_steps=20, root_repair_rounds=3, root_graphs=True, host_workers=2, host_threads=4,
-                 statistic_chunks=4):
+                 statistic_chunks=4, row_pieces=1):
         if len(_LIVE):
             raise RuntimeError("another fast Toner optimizer is alive in this process; close() it first")
         strengths = (float(inner_strength), float(outer_strength))
@@ -133,7 +133,7 @@ class _FastToner(torch.optim.Optimizer):
             counts=dict(micro_batch_size=micro_batch_size, sequence_length=sequence_length,
                         accumulation_steps=accumulation_steps, statistic_stride=statistic_stride, ns_steps=ns_steps,
                         root_refresh=root_refresh, root_iterations=root_iterations, host_workers=host_workers,
-                        host_threads=host_threads, statistic_chunks=statistic_chunks),
+                        host_threads=host_threads, statistic_chunks=statistic_chunks, row_pieces=row_pieces),
             nonnegative_counts=dict(root_inline_steps=root_inline_steps, root_repair_rounds=root_repair_rounds))
         self.blocks = [_as_block(b) for b in blocks]
         if len(self.blocks) == 0:
@@ -203,6 +203,11 @@ class _FastToner(torch.optim.Optimizer):
         self._positions = torch.tensor(positions, device=device, dtype=torch.int32)
         self._rows_per_microbatch = micro_batch_size * len(positions)
         local_rows = self._rows_per_microbatch * accumulation_steps
+        # Optional (not in the reference's adapter; its engine has it as chunk_stats / chunk_wait): the row buffers hold
+        # only accumulation_steps / row_pieces microbatches, and each full piece is folded into the partial Grams.
+        if accumulation_steps % row_pieces:
+            raise ValueError("row_pieces must divide accumulation_steps")
+        self._piece_microbatches = accumulation_steps // row_pieces
         args = SimpleNamespace(
             statistic_momentum=float(statistic_momentum), inner_strength=strengths[0], outer_strength=strengths[1],
             damping=1e-3, weight_decay=float(weight_decay), beta1=float(betas[0]), beta2=float(betas[1]),
@@ -218,7 +223,8 @@ class _FastToner(torch.optim.Optimizer):
         from .engine import KINDS_D, FastTonerCore  # CUDA library is loaded here, not at package import
 
         self._core = FastTonerCore(named, bindings, kind, layers=len(self.blocks), hid=hidden, mlp=mlp,
-                                   local_rows=local_rows, args=args, world=world, rank=rank, device=device)
+                                   local_rows=local_rows, args=args, world=world, rank=rank, device=device,
+                                   row_capacity=self._rows_per_microbatch * self._piece_microbatches)
         # per-layer views of the stacked row buffers, under the reference's attribute names
         self._buffers = []
         d, f = self._core.groups["d"], self._core.groups["f"]
@@ -267,7 +273,7 @@ class _FastToner(torch.optim.Optimizer):
             self._seen.add((layer, role))
             if previous is None:
                 self._input_signatures[(layer, stat)] = signature
-                lo = self._microbatches * self._rows_per_microbatch
+                lo = (self._microbatches % self._piece_microbatches) * self._rows_per_microbatch
                 dst = getattr(self._buffers[layer], f"input_rows_{stat}")[lo: lo + self._rows_per_microbatch]
                 if x.stride(2) != 1 or (x.stride(1) * x.element_size()) % 16 or (x.stride(0) * x.element_size()) % 16 \
                         or x.data_ptr() % 16:
@@ -286,6 +292,8 @@ class _FastToner(torch.optim.Optimizer):
             raise RuntimeError("all microbatches of this step are captured; call step() before the next forward")
         self._seen = set()
         self._input_signatures = {}
+        if self._microbatches and self._microbatches % self._piece_microbatches == 0:
+            self._core.chunk_wait()               # the previous piece's Grams must have read the row buffers
         self._capturing = True
         complete = False
         try:
@@ -298,6 +306,10 @@ class _FastToner(torch.optim.Optimizer):
             self._capturing = False
             # a failed or partial forward discards every microbatch captured so far in this step
             self._microbatches = self._microbatches + 1 if complete else 0
+            if not complete:
+                self._core.discard_pieces()
+            elif self._microbatches % self._piece_microbatches == 0 and self._microbatches < self.accumulation_steps:
+                self._core.chunk_stats()          # a full piece that is not the step's last
 
     def begin(self):
         """Start statistics and factors asynchronously after the final forward, before backward."""

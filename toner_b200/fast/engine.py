@@ -106,7 +106,8 @@ class StatGroup:
         self.chunk_stats = self.per // chunks
         dev = self.rows_buf.device
         self.partial = torch.empty(chunks, self.world, self.chunk_stats, self.tri, device=dev, dtype=torch.float32)
-        self.summed = torch.empty(chunks, self.chunk_stats, self.tri, device=dev, dtype=torch.float32)
+        self.summed = (torch.empty(chunks, self.chunk_stats, self.tri, device=dev, dtype=torch.float32)
+                       if self.world > 1 else None)
         # row buffers feeding chunk c, in (rank, j) order: statistic r*per + c*cs + j
         self.chunk_lists = [[self.rows_buf[s] for s in chunk_members(self.world, self.per, chunks, c)]
                             for c in range(chunks)]
@@ -117,9 +118,17 @@ class FastTonerCore:
 
     def __init__(self, named: Dict[str, torch.Tensor], bindings: Dict[str, Tuple[int, str, str]], kind: str, *,
                  layers: int, hid: int, mlp: int, local_rows: int, args, world: int, rank: int,
-                 device: torch.device) -> None:
+                 device: torch.device, row_capacity: Optional[int] = None) -> None:
+        """`row_capacity` (default: `local_rows`) is what the row buffers hold: with a smaller capacity the step's
+        rows arrive in local_rows / row_capacity pieces, each folded into the partial Grams by chunk_stats()."""
         if kind not in ("adamt", "muont"):
             raise ValueError("kind must be 'adamt' or 'muont'")
+        row_capacity = local_rows if row_capacity is None else int(row_capacity)
+        if row_capacity <= 0 or local_rows % row_capacity:
+            raise ValueError("the row buffers' capacity must divide this rank's rows per step")
+        self.row_pieces = local_rows // row_capacity
+        self.pieces_done = 0
+        self.ev_chunk: Optional[torch.cuda.Event] = None
         self.kind, self.args, self.world, self.rank, self.device = kind, args, world, rank, device
         self.L = layers
         self.rows_total = local_rows * world
@@ -131,9 +140,9 @@ class FastTonerCore:
         strengths = (float(args.inner_strength), float(args.outer_strength))
         damping = float(getattr(args, "damping", 1e-3))
         self.groups = {
-            "d": StatGroup("d", [(i, k) for i in range(layers) for k in KINDS_D], hid, local_rows,
+            "d": StatGroup("d", [(i, k) for i in range(layers) for k in KINDS_D], hid, row_capacity,
                            len(KINDS_D) * self.per_layers, rank, world, device, strengths, damping, self.scratch),
-            "f": StatGroup("f", [(i, "down") for i in range(layers)], mlp, local_rows, self.per_layers, rank, world,
+            "f": StatGroup("f", [(i, "down") for i in range(layers)], mlp, row_capacity, self.per_layers, rank, world,
                            device, strengths, damping, self.scratch),
         }
         self.weight = 0.0
@@ -198,9 +207,9 @@ class FastTonerCore:
         self.main_stream = torch.cuda.current_stream(device)
         self.side = torch.cuda.Stream(device=device, priority=-1)
         self.pg = dist.new_group(backend="nccl") if world > 1 else None
-        if world > 1:
+        if world > 1 or self.row_pieces > 1:   # packed partial Grams: summed over ranks, or over the pieces of a step
             for g in self.groups.values():
-                g.plan_chunks(int(getattr(args, "stat_chunks", 4)))
+                g.plan_chunks(int(getattr(args, "stat_chunks", 4)) if world > 1 else 1)
         self.begun = False
         self._ev: Optional[List[torch.cuda.Event]] = None
         self._ev_last: Optional[List[torch.cuda.Event]] = None
@@ -216,18 +225,58 @@ class FastTonerCore:
         return sum(g.factors.repairs for g in self.groups.values())
 
     # ------------------------------------------------------------------ statistics (side stream)
+    def _partial_grams(self, g: "StatGroup", c: int) -> None:
+        """Packed Grams of statistic chunk c from the rows now in the buffers, added to earlier pieces of the step."""
+        mode = ops.PACKED_ACC if self.pieces_done else ops.PACKED
+        ops.syrk_upper(g.chunk_lists[c], g.partial[c].view(-1, g.tri), mode)
+
+    def chunk_stats(self) -> None:
+        """Fold the rows now in the buffers into the step's partial Grams (side stream); the buffers then take the
+        next piece of the step.  Call after the forward of a piece's last microbatch, except for the step's last
+        piece, which begin() handles (chunk_stats, src/toner/fast/engine.py:348-363)."""
+        if self.row_pieces == 1:
+            raise RuntimeError("the row buffers hold the whole step; there are no pieces to fold")
+        if self.begun or self.pieces_done >= self.row_pieces - 1:
+            raise RuntimeError("the last piece of a step belongs to begin()")
+        ev = torch.cuda.Event()
+        ev.record(self.main_stream)
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ev)
+            for g in self.groups.values():
+                for c in range(g.chunks):
+                    self._partial_grams(g, c)
+            self.ev_chunk = torch.cuda.Event()
+            self.ev_chunk.record(self.side)
+        self.pieces_done += 1
+
+    def chunk_wait(self) -> None:
+        """The main stream waits until the last piece's Grams have read the row buffers; call before the next piece's
+        first forward overwrites them (chunk_wait, src/toner/fast/engine.py:365-369)."""
+        if self.ev_chunk is not None:
+            self.main_stream.wait_event(self.ev_chunk)
+
+    def discard_pieces(self) -> None:
+        """Forget the pieces folded so far (a failed forward discards the step's captured rows)."""
+        self.pieces_done = 0
+
     def _stats(self) -> None:
         """Partial Grams of every statistic from this rank's rows, summed over ranks at the owners, EMA."""
         b = self.decay
         gamma = (1 - b) / self.rows_total
-        if self.world == 1:
+        if self.pieces_done != self.row_pieces - 1:
+            raise RuntimeError(f"{self.pieces_done + 1} of the step's {self.row_pieces} row pieces were captured")
+        if self.world == 1 and self.row_pieces == 1:
             for g in self.groups.values():
                 ops.syrk_upper(g.rows_buf, g.factors.ema, ops.EMA_FULL, b, gamma)   # SYRK with the EMA fused
+        elif self.world == 1:
+            for g in self.groups.values():
+                self._partial_grams(g, 0)
+                ops.unpack_ema(g.partial[0, 0], g.factors.ema, b, gamma)
         else:
             pending = []
             for g in self.groups.values():
                 for c in range(g.chunks):
-                    ops.syrk_upper(g.chunk_lists[c], g.partial[c].view(-1, g.tri), ops.PACKED)
+                    self._partial_grams(g, c)
                     # NCCL waits for the SYRK just enqueued and runs on its own stream: the next chunk's SYRK overlaps it
                     work = dist.reduce_scatter_tensor(g.summed[c], g.partial[c], group=self.pg, async_op=True)
                     pending.append((g, c, work))
@@ -235,6 +284,7 @@ class FastTonerCore:
                 work.wait()
                 cs = g.chunk_stats
                 ops.unpack_ema(g.summed[c], g.factors.ema[c * cs:(c + 1) * cs], b, gamma)
+        self.pieces_done = 0
         self.weight = b * self.weight + (1 - b)
 
     @torch.no_grad()
