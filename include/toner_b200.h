@@ -292,6 +292,10 @@ int toner_scale_stack(const float* x, const float* coeff, float* out, int32_t co
 
 /* W_b += delta_b.  Replaces torch._foreach_add_ (src/toner/fast/engine.py:875). */
 int toner_apply_delta(float* const* weight_ptrs, const float* delta, int32_t count, int64_t per, void* stream);
+/* W_b <- weight_scale * W_b + delta_scale * delta_b: the plain Muon baseline's decoupled decay p.mul_(1 - lr wd)
+ * and p.add_(o, alpha = -lr sqrt(max(1, rows / cols))) in one pass (src/toner/fast/muon.py:118-119,160-164). */
+int toner_apply_scaled(float* const* weight_ptrs, const float* delta, int32_t count, int64_t per, float weight_scale,
+                       float delta_scale, void* stream);
 
 #ifdef __cplusplus
 }

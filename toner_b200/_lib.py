@@ -93,6 +93,7 @@ SIGNATURES = {
     "toner_axpby": (C.c_int, [_vp, _vp, _vp, _i64, _f32, _f32, _vp]),
     "toner_scale_stack": (C.c_int, [_vp, _vp, _vp, _i32, _i64, _vp]),
     "toner_apply_delta": (C.c_int, [_vp, _vp, _i32, _i64, _vp]),
+    "toner_apply_scaled": (C.c_int, [_vp, _vp, _i32, _i64, _f32, _f32, _vp]),
     "toner_split16": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _i64, _f32, _f32, _vp, _vp, _vp, _vp, _vp]),
 }
 

@@ -154,6 +154,22 @@ __global__ void __launch_bounds__(256) apply_delta_kernel(float* const* __restri
   }
 }
 
+// W_b <- ws * W_b + ds * delta_b (decoupled weight decay and a scaled change in one pass)
+__global__ void __launch_bounds__(256) apply_scaled_kernel(float* const* __restrict__ weights, const float* __restrict__ delta,
+                                                           long long per, float ws, float ds) {
+  const int b = blockIdx.y;
+  float4* W = reinterpret_cast<float4*>(weights[b]);
+  const float4* D = reinterpret_cast<const float4*>(delta + (long long)b * per);
+  const long long n4 = per / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 w = W[i];
+    const float4 d = D[i];
+    w.x = fmaf(ds, d.x, ws * w.x); w.y = fmaf(ds, d.y, ws * w.y);
+    w.z = fmaf(ds, d.z, ws * w.z); w.w = fmaf(ds, d.w, ws * w.w);
+    W[i] = w;
+  }
+}
+
 __global__ void __launch_bounds__(256) scale_stack_kernel(const float* __restrict__ x, const float* __restrict__ coeff,
                                                           float* __restrict__ out, long long per) {
   const int b = blockIdx.y;
@@ -397,6 +413,19 @@ int toner_apply_delta(float* const* weight_ptrs, const float* delta, int32_t cou
   if (!weight_ptrs || !delta || count <= 0) return fail(kErrArg, "apply_delta: bad arguments");
   if (int rc = check_stack("apply_delta", per)) return rc;
   apply_delta_kernel<<<dim3(ew_grid(per / 4, ctx->num_sms), count), 256, 0, static_cast<cudaStream_t>(stream)>>>(weight_ptrs, delta, per);
+  count_launch();
+  TONER_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int toner_apply_scaled(float* const* weight_ptrs, const float* delta, int32_t count, int64_t per, float weight_scale,
+                       float delta_scale, void* stream) {
+  Context* ctx = context();
+  if (!ctx) return kErrCuda;
+  if (!weight_ptrs || !delta || count <= 0) return fail(kErrArg, "apply_scaled: bad arguments");
+  if (int rc = check_stack("apply_scaled", per)) return rc;
+  apply_scaled_kernel<<<dim3(ew_grid(per / 4, ctx->num_sms), count), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      weight_ptrs, delta, per, weight_scale, delta_scale);
   count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;

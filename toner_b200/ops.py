@@ -402,6 +402,12 @@ def apply_delta(weight_ptrs: torch.Tensor, delta: torch.Tensor) -> None:
                                         _stream()), "toner_apply_delta")
 
 
+def apply_scaled(weight_ptrs: torch.Tensor, delta: torch.Tensor, weight_scale: float, delta_scale: float) -> None:
+    """W_b <- weight_scale * W_b + delta_scale * delta_b over a pointer table of weights (toner_apply_scaled)."""
+    check(_lib.load().toner_apply_scaled(weight_ptrs.data_ptr(), delta.data_ptr(), delta.shape[0], delta[0].numel(),
+                                         weight_scale, delta_scale, _stream()), "toner_apply_scaled")
+
+
 def split16_list(ptrs: torch.Tensor, batch: int, rows: int, cols: int, planes: torch.Tensor, inv_scale: torch.Tensor,
                  scratch: torch.Tensor) -> None:
     """split16 of separately allocated contiguous (rows, cols) FP32 matrices given by a device pointer table."""
