@@ -184,7 +184,8 @@ int toner_split16(const float* x, const float* const* x_list, int32_t batch, int
  * alone; its order (toner_inv_roots_finish_order_for) follows from the bound on R the schedule guarantees, and
  * its order - 1 products are single passes over FP16 planes of R.
  * `iters` <= 0 selects toner_inv_roots_iterations(n, damping, p), which depends only on
- * its arguments (8 for p = 8, 9 for p = 4, 10 for p = 2 at n = 5632, damping 1e-3).
+ * its arguments (8 for p = 8, 8 for p = 4, 10 for p = 2 at n = 5632, damping 1e-3): the count with the fewest
+ * plane passes, Newton steps and series together.
  * status[b] (DEVICE, optional): 0 converged, 1 residual max|I - M| above 0.5 before the last step,
  * 2 non-finite.  The caller decides what to do with a non-zero status (the Python host recomputes that
  * statistic with an eigendecomposition, as the reference's fallback does, src/toner/fast/engine.py:714-731).

@@ -111,16 +111,17 @@ def test_chunked_workspace_gives_identical_roots(ops):
 
 def test_iteration_counts_are_stated(ops):
     assert ops.inv_roots_iterations(5632, 1e-3, 8) == 8
-    assert ops.inv_roots_iterations(5632, 1e-3, 4) == 9
+    assert ops.inv_roots_iterations(5632, 1e-3, 4) == 8
     assert ops.inv_roots_iterations(5632, 1e-3, 2) == 10
     assert ops.inv_roots_iterations(768, 1e-3, 8) <= 10
 
 
 @pytest.mark.parametrize("p,q", [(8, 4), (4, 1), (2, 1)])
 def test_finishing_series_at_every_order(ops, p, q):
-    """The iteration stops as soon as the spectrum of M is within 0.4 of 1 and finishes with a series whose order
-    follows from that distance.  Sweeping the caller's bound moves the stopping point, so orders from 2 up to the
-    cap are exercised; every one must give the same roots as FP64 truth."""
+    """The iteration stops where Newton steps plus finishing series cost the fewest plane passes (the spectrum of M is
+    then within 0.5 of 1) and the order of the series follows from that distance.  Sweeping the caller's bound moves
+    the stopping point, so orders from 2 up to the cap are exercised; every one must give the same roots as FP64
+    truth."""
     n = 384
     stats = torch.stack([spd(n, 3e2, 11), spd(n, 1e3, 12)]).cuda()
     norms = torch.zeros(2, device="cuda")

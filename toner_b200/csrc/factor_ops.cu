@@ -86,9 +86,10 @@ constexpr int kPowerSteps = 6;
 // in [0, e] with e known from the schedule, so the order m is fixed in advance: the smallest whose tail
 // a_{m+1} e^{m+1} / (1 - e) is below 4e-6.  The powers come from m - 1 single-pass products of FP16 planes in Horner
 // form (a third of a split-precision product each; R is small, so its rounding to FP16 costs about 5e-4 a_2 e^2), which
-// is cheaper than the log2(p) + 2 split-precision products of one more Newton step for every e up to kFinishRadius.
-constexpr double kFinishRadius = 0.4;
-constexpr int kMaxFinishOrder = 10;
+// is cheaper than the log2(p) + 2 split-precision products of one more Newton step; the step count is the one with
+// the fewest plane passes in total.
+constexpr double kFinishRadius = 0.5;
+constexpr int kMaxFinishOrder = 12;
 constexpr double kFinishTail = 4e-6;
 
 static double finish_coefficient(int p, int j) {
@@ -96,21 +97,40 @@ static double finish_coefficient(int p, int j) {
   for (int i = 1; i <= j; ++i) a *= (1.0 / p + i - 1) / i;
   return a;
 }
-static int finish_order(int p, double e) {
-  if (e >= 1.0) return kMaxFinishOrder;
-  for (int m = 2; m < kMaxFinishOrder; ++m)
+// 0: no order up to the cap reaches the tail bound at this distance
+static int finish_order_or_zero(int p, double e) {
+  if (e >= 1.0) return 0;
+  for (int m = 2; m <= kMaxFinishOrder; ++m)
     if (finish_coefficient(p, m + 1) * std::pow(e, m + 1) / (1.0 - e) < kFinishTail) return m;
-  return kMaxFinishOrder;
+  return 0;
+}
+static int finish_order(int p, double e) {
+  const int m = finish_order_or_zero(p, e);
+  return m ? m : kMaxFinishOrder;  // a caller's own (too small) step count: the best the cap allows; status reports it
 }
 
 static int default_iterations(double l0, int p) {
-  // steps of M until its spectrum is within the finishing radius of 1, plus the finishing step applied to X alone
+  // k steps of M, then the finishing step on X alone: the k with the fewest plane passes,
+  // 3 (log2 p + 2) per step of M and order - 1 for the series, among those the series can finish
+  int log2p = 0;
+  while ((1 << log2p) < p) ++log2p;
+  int best = 0;
+  long best_cost = 0;
   for (int k = 1; k < 64; ++k) {
     double l;
     newton_schedule(l0, p, k, &l);
-    if (1.0 - l < kFinishRadius) return k + 1;
+    const double e = 1.0 - l;
+    const int m = e < kFinishRadius ? finish_order_or_zero(p, e) : 0;
+    if (m) {
+      const long cost = 3L * k * (log2p + 2) + (m - 1);
+      if (!best || cost < best_cost) {
+        best = k + 1;
+        best_cost = cost;
+      }
+      if (m == 2) break;  // further steps only add cost
+    }
   }
-  return 64;
+  return best ? best : 64;
 }
 
 // ------------------------------------------------------------------ elementwise helpers
