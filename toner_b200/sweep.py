@@ -142,12 +142,15 @@ def bench_roots(a):
     fn = lambda: ops.inv_roots(c, 1e-3, a.p, a.q, root_lo=lo, root_hi=hi, workspace=ws)
     ms, best = timed(fn, a.warmup, a.reps, False)
     log2p, log2q = int(math.log2(a.p)), int(math.log2(a.q))
-    products = (iters - 1) * (log2p + 2) - 1 + 1 + log2q  # X T and T^p M per step (no X product first, no M last)
-    flops = a.k * products * 2 * a.n ** 3
+    order = ops.inv_roots_finish_order(a.n, 1e-3, a.p)
+    split = (iters - 1) * (log2p + 2) + log2q     # X T and T^p M per step (no X product first, no M last), squarings
+    single = order - 1                            # Horner steps of the finishing series
+    flops = a.k * (split + single) * 2 * a.n ** 3
     return report("inv_roots", {"k": a.k, "n": a.n, "p": a.p, "q": a.q, "cond": a.cond}, ms, best, flops=flops,
-                  extra={"iterations": iters, "damping": 1e-3, "products_per_statistic": products,
-                         "note": "single-pass dense count per product; each product runs 3 FP16 plane passes over "
-                                 "the tiles meeting the upper triangle"})
+                  extra={"iterations": iters, "finish_order": order, "damping": 1e-3, "split_products": split,
+                         "single_pass_products": single,
+                         "note": "dense count 2 n^3 per product; a split product runs 3 FP16 plane passes, a "
+                                 "single-pass one 1, over the tiles meeting the upper triangle"})
 
 
 def bench_ns(a):
