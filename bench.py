@@ -201,13 +201,43 @@ def run_ours(args) -> None:
     checksum = torch.zeros(1, dtype=torch.float32).pin_memory()
     h2d = layers * (host_rows_d.numel() * 2 + host_rows_f.numel() * 2 + sum(g.numel() * 4 for g in host_grads))
 
+    # The copies run on their own stream in the order the step consumes them -- the wide (MLP) statistics first, whose
+    # factors are most of the step, then the hidden-width ones, then the gradients -- four layers per event, and
+    # begin(ready=...) lets each slice's SYRK and each group's factors start as soon as their rows have landed.
+    copy_stream = torch.cuda.Stream(device=dev)
+    main_stream = torch.cuda.current_stream(dev)
+    per_event = 4
+
     def e2e_step():
-        for i in range(layers):
-            d.rows_buf[3 * i: 3 * i + 3].copy_(host_rows_d, non_blocking=True)
-            f.rows_buf[i].copy_(host_rows_f, non_blocking=True)
-            for info, hg in zip(roles, host_grads):
-                info["all"][i].grad.copy_(hg, non_blocking=True)
-        one_step()
+        ready = []
+        copy_stream.wait_stream(main_stream)      # the previous step has read the rows and gradients
+        with torch.cuda.stream(copy_stream):
+            for lo in range(0, layers, per_event):
+                hi = min(layers, lo + per_event)
+                for i in range(lo, hi):
+                    f.rows_buf[i].copy_(host_rows_f, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(copy_stream)
+                ready.append(("f", lo, hi, ev))
+            for lo in range(0, layers, per_event):
+                hi = min(layers, lo + per_event)
+                for i in range(lo, hi):
+                    d.rows_buf[3 * i: 3 * i + 3].copy_(host_rows_d, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(copy_stream)
+                ready.append(("d", 3 * lo, 3 * hi, ev))
+            for i in range(layers):
+                for info, hg in zip(roles, host_grads):
+                    info["all"][i].grad.copy_(hg, non_blocking=True)
+            grads_in = torch.cuda.Event()
+            grads_in.record(copy_stream)
+        if world == 1:
+            core.begin(ready=ready)
+        else:                                      # several ranks: statistics start when all local rows are in
+            main_stream.wait_event(ready[-1][3])
+            core.begin()
+        main_stream.wait_event(grads_in)
+        core.step()
         checksum.copy_(roles[0]["all"][0][0, :1], non_blocking=True)
 
     e2e_ms = None

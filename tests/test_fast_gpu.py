@@ -209,3 +209,39 @@ def test_row_buffers_that_hold_half_a_step(fast, kind):
 def test_row_pieces_must_divide_the_accumulation(fast):
     with pytest.raises(ValueError):
         make(fast, "llama", "muont", row_pieces=3)
+
+
+def test_statistics_follow_rows_that_arrive_in_slices(fast):
+    """begin(ready=...): each slice of statistics waits for its own event and a group's factors start when its last
+    slice is in.  Statistics are independent of one another, so the weights are bit-identical to a plain begin()."""
+    def run(streamed):
+        stack, opt = make(fast, "llama", "muont", ns_steps=2)
+        try:
+            gen = torch.Generator().manual_seed(21)
+            for step in range(2):
+                for mb in range(ACC):
+                    with opt.capture_microbatch():
+                        forward(stack, torch.randn(MB, SEQ, HID, generator=gen).cuda())
+                if streamed:
+                    ev = torch.cuda.Event()
+                    ev.record()
+                    core = opt._core
+                    if step == 0:
+                        with pytest.raises(ValueError):
+                            core.begin(ready=[("d", 1, 3, ev)])           # does not start at the first statistic
+                    core.begin(ready=[("f", 0, 1, ev), ("d", 0, 2, ev), ("f", 1, 2, ev), ("d", 2, 5, ev), ("d", 5, 6, ev)])
+                else:
+                    opt.begin()
+                for b in stack:
+                    for p in b.parameters():
+                        if p.ndim == 2:
+                            p.grad = (torch.randn(p.shape, generator=gen) * 1e-3).cuda()
+                opt.step()
+            torch.cuda.synchronize()
+            return [p.detach().cpu().clone() for b in stack for p in b.parameters() if p.ndim == 2]
+        finally:
+            opt.close()
+
+    plain, streamed = run(False), run(True)
+    for a, b in zip(plain, streamed):
+        assert torch.equal(a, b)

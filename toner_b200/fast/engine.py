@@ -288,8 +288,34 @@ class FastTonerCore:
         self.weight = b * self.weight + (1 - b)
 
     @torch.no_grad()
-    def begin(self) -> None:
-        """Statistics and factors on the side stream; call right after the last microbatch's forward."""
+    def _stats_as_rows_arrive(self, ready) -> None:
+        """Single rank, rows still arriving (for example copied from host memory on another stream): `ready` lists
+        (group name, first statistic, one past the last, event) in the order the rows land.  Each slice's SYRK + EMA
+        waits for its event only, and a group's factors are enqueued as soon as its last slice is in, so the
+        remaining transfers overlap them."""
+        if self.world != 1 or self.row_pieces != 1:
+            raise RuntimeError("streamed rows need a single rank and row buffers that hold the whole step")
+        b = self.decay
+        gamma = (1 - b) / self.rows_total
+        done = {name: 0 for name in self.groups}
+        for name, lo, hi, event in ready:
+            g = self.groups[name]
+            if lo != done[name] or not lo < hi <= g.k_all:
+                raise ValueError(f"slices of group {name} must be contiguous and in order")
+            self.side.wait_event(event)
+            ops.syrk_upper(g.rows_buf[lo:hi], g.factors.ema[lo:hi], ops.EMA_FULL, b, gamma)
+            done[name] = hi
+            if hi == g.k_all:
+                g.factors.compute()
+        if any(done[name] != g.k_all for name, g in self.groups.items()):
+            raise ValueError("the slices must cover every statistic")
+        self.weight = b * self.weight + (1 - b)
+
+    @torch.no_grad()
+    def begin(self, ready=None) -> None:
+        """Statistics and factors on the side stream; call right after the last microbatch's forward.  With `ready`
+        (see _stats_as_rows_arrive) the work follows the rows as they arrive; gpu_ms then reports statistics and
+        factors together under "stats"."""
         t0 = time.perf_counter()
         ev_fwd = torch.cuda.Event()
         ev_fwd.record(self.main_stream)
@@ -297,10 +323,14 @@ class FastTonerCore:
         with torch.cuda.stream(self.side):
             self.side.wait_event(ev_fwd)
             self._ev[0].record(self.side)
-            self._stats()
-            self._ev[1].record(self.side)
-            for g in self.groups.values():
-                g.factors.compute()
+            if ready is None:
+                self._stats()
+                self._ev[1].record(self.side)
+                for g in self.groups.values():
+                    g.factors.compute()
+            else:
+                self._stats_as_rows_arrive(ready)
+                self._ev[1].record(self.side)
             self._ev[2].record(self.side)
             self.ev_done = torch.cuda.Event()
             self.ev_done.record(self.side)
