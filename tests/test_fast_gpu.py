@@ -245,3 +245,77 @@ def test_statistics_follow_rows_that_arrive_in_slices(fast):
     plain, streamed = run(False), run(True)
     for a, b in zip(plain, streamed):
         assert torch.equal(a, b)
+
+
+def test_direct_construction_from_a_model_that_owns_its_row_buffers(fast):
+    """FastTonerCore.from_blocks: a trainer-side model with `input_rows_*` buffers and `body.blocks.<i>.<role>.weight`
+    names, the reference's argument namespace, rows written by capture_recomputed-style code straight into the
+    (rebound) buffers, lr set on param_groups.  Must give the same weights as FastMuonT fed the same rows."""
+    from types import SimpleNamespace
+    from toner_b200 import ops
+    from toner_b200.fast.engine import FastTonerCore
+    from toner_b200.synthetic import make_stack
+    dev = torch.device("cuda")
+    positions = orc.sample_positions(SEQ, 8, 4)
+    rows = ACC * MB * len(positions)
+    gen = torch.Generator().manual_seed(31)
+    xs = [torch.randn(MB, SEQ, HID, generator=gen) for _ in range(2 * ACC)]
+    grads_seed = 77
+
+    def grads_for(stack, step):
+        g = torch.Generator().manual_seed(grads_seed + step)
+        for b in stack:
+            for p in b.parameters():
+                if p.ndim == 2:
+                    p.grad = (torch.randn(p.shape, generator=g) * 1e-3).cuda()
+
+    # reference run through the adapter, recording the rows each statistic saw
+    stack, opt = make(fast, "llama", "muont", ns_steps=2)
+    seen = []
+    try:
+        for step in range(2):
+            for mb in range(ACC):
+                with opt.capture_microbatch():
+                    forward(stack, xs[step * ACC + mb].cuda())
+            core = opt._core
+            seen.append((core.groups["d"].rows_buf.clone(), core.groups["f"].rows_buf.clone()))
+            opt.begin()
+            grads_for(stack, step)
+            opt.step()
+        want = [p.detach().cpu().clone() for b in stack for p in b.parameters() if p.ndim == 2]
+    finally:
+        opt.close()
+
+    # the same through the direct seam
+    stack2 = make_stack("llama", LAYERS, HID, MLP, dev, seed=0)
+    blocks = []
+    for b in stack2:
+        holder = torch.nn.Module()
+        for k, w in (("attn", HID), ("o", HID), ("mlp", HID), ("down", MLP)):
+            holder.register_buffer(f"input_rows_{k}", torch.zeros(rows, w, dtype=torch.bfloat16, device=dev), persistent=False)
+        blocks.append(holder)
+    named = {f"body.blocks.{i}.{r}.weight": getattr(b, r).weight for i, b in enumerate(stack2)
+             for r in ("q", "k", "v", "o", "gate", "up", "down")}
+    named["body.emb.weight"] = torch.zeros(8, 8, device=dev)              # not a block matrix: ignored
+    args = SimpleNamespace(toner_decay=0.95, toner_split=True, toner_alpha=0.5, toner_alpha_in=0.5, toner_alpha_out=0.125,
+                           wd=0.1, beta1=0.9, beta2=0.98, eps=1e-15, muon_momentum=0.95, muon_nesterov=True,
+                           muon_ns_steps=2, muon_eps=1e-5, muon_ns_mode="tpu", toner_lr_mult=1.0)
+    core = FastTonerCore.from_blocks(blocks, named, "muont", hid=HID, mlp=MLP, rows_total=rows, args=args, world=1, rank=0,
+                                     device=dev)
+    assert blocks[0].input_rows_attn.data_ptr() == core.groups["d"].rows_buf[0].data_ptr()
+    core.param_groups[0]["lr"] = 0.02
+    for step in range(2):
+        d_rows, f_rows = seen[step]
+        for i, holder in enumerate(blocks):
+            for j, k in enumerate(("attn", "o", "mlp")):
+                getattr(holder, f"input_rows_{k}").copy_(d_rows[3 * i + j])
+            holder.input_rows_down.copy_(f_rows[i])
+        core.begin()
+        grads_for(stack2, step)
+        core.step()
+    core.side.synchronize()
+    core.pool.shutdown(wait=True)
+    ops.assert_healthy()
+    got = [p.detach().cpu().clone() for b in stack2 for p in b.parameters() if p.ndim == 2]
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)

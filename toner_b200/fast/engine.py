@@ -215,6 +215,67 @@ class FastTonerCore:
         self._ev_last: Optional[List[torch.cuda.Event]] = None
         self.ev_done: Optional[torch.cuda.Event] = None
 
+    @classmethod
+    def from_blocks(cls, blocks, named: Dict[str, torch.Tensor], kind: str, *, hid: int, mlp: int, rows_total: int, args,
+                    world: int, rank: int, device: torch.device) -> "FastTonerCore":
+        """Direct construction the way a trainer that owns the model does it (the reference's
+        ``FastTonerCore(blocks, named, kind, hid=..., mlp=..., rows_total=..., args=..., world, rank, device)``,
+        src/toner/fast/engine.py:176-190, used by reproduce/marin/optimizer.py:67-78).
+
+        ``blocks[i]`` carries the row buffers ``input_rows_{attn,o,mlp,down}`` of capacity (rows, width); ``named``
+        maps ``body.blocks.<i>.<q|k|v|o|gate|up|down>.weight`` to the FP32 matrices; ``args`` is the reference's
+        argument namespace (``toner_decay``, ``toner_alpha[_in|_out]``, ``toner_split``, ``wd``, ``beta1``, ``beta2``,
+        ``eps``, ``muon_*``).  The blocks' row-buffer attributes are rebound to views of this engine's stacked
+        buffers, so the model's capture writes where the SYRK reads; a capacity below the rank's rows per step means
+        the trainer folds pieces with chunk_stats() / chunk_wait()."""
+        from types import SimpleNamespace
+        layers = len(blocks)
+        matrices, bindings = {}, {}
+        for name, p in named.items():
+            if not (name.startswith("body.blocks.") and p.ndim == 2):
+                continue
+            parts = name.split(".")
+            if len(parts) != 5 or parts[3] not in ROLE_KIND:
+                raise ValueError(f"cannot bind matrix {name} to an input statistic")
+            matrices[name] = p
+            bindings[name] = (int(parts[2]), parts[3], ROLE_KIND[parts[3]])
+        if getattr(args, "muon_ns_mode", "tpu") != "tpu":
+            raise ValueError("the CUDA Newton-Schulz kernel implements ns_mode='tpu' only")
+        if kind == "muont":
+            split = bool(getattr(args, "toner_split", False))
+            inner = float(args.toner_alpha_in if split else args.toner_alpha)
+            outer = float(args.toner_alpha_out if split else args.toner_alpha)
+        else:
+            inner = outer = 0.25
+        ours = SimpleNamespace(
+            statistic_momentum=float(args.toner_decay), inner_strength=inner, outer_strength=outer, damping=1e-3,
+            weight_decay=float(args.wd), beta1=float(getattr(args, "beta1", 0.9)), beta2=float(getattr(args, "beta2", 0.98)),
+            eps=float(getattr(args, "eps", 1e-15)), momentum=float(getattr(args, "muon_momentum", 0.95)),
+            nesterov=bool(getattr(args, "muon_nesterov", True)), ns_steps=int(getattr(args, "muon_ns_steps", 10)),
+            ns_eps=float(getattr(args, "muon_eps", 1e-5)), stat_chunks=4)
+        if rows_total % world:
+            raise ValueError("rows_total must be a multiple of the number of ranks")
+        capacity = int(blocks[0].input_rows_attn.size(0))
+        core_ = cls(matrices, bindings, kind, layers=layers, hid=hid, mlp=mlp, local_rows=rows_total // world, args=ours,
+                    world=world, rank=rank, device=device, row_capacity=capacity)
+        d, f_ = core_.groups["d"], core_.groups["f"]
+        for i, block in enumerate(blocks):
+            for j, k in enumerate(KINDS_D):
+                setattr(block, f"input_rows_{k}", d.rows_buf[len(KINDS_D) * i + j])
+            block.input_rows_down = f_.rows_buf[i]
+        # stored for the trainer's schedule, as in the reference (src/toner/fast/engine.py:265-272); step() uses "lr"
+        core_.param_groups[0]["lr_scale"] = float(getattr(args, "toner_lr_mult", 1.0))
+        return core_
+
+    class _NoPool:
+        """The reference keeps a thread pool for host eigendecompositions and trainers shut it down at exit; there is
+        no host work here."""
+
+        def shutdown(self, wait: bool = True) -> None:
+            return None
+
+    pool = _NoPool()
+
     @property
     def fallbacks(self) -> int:
         return sum(g.factors.fallbacks for g in self.groups.values())
