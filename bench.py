@@ -152,7 +152,7 @@ def run_ours(args) -> None:
     # Engine-level seam (what the reference's second trainer uses): the sampled rows of this rank's tokens
     # are written straight into the row buffers, gradients into .grad, then begin() and step().
     for gi, g in enumerate(core.groups.values()):
-        fill_rows(g.rows_buf, seed=1 + rank * 7 + gi)
+        fill_rows(g.rows_buf, seed=1 + rank * 7 + gi, mean_seed=1000 + gi)   # every rank's tokens share the model's mean activation
     gen = torch.Generator(device=dev).manual_seed(99)   # gradients are replicated (already synchronised)
     for p in core.params:
         p.grad = torch.randn(p.shape, device=dev, generator=gen) * 1e-3
@@ -231,11 +231,7 @@ def run_ours(args) -> None:
                     info["all"][i].grad.copy_(hg, non_blocking=True)
             grads_in = torch.cuda.Event()
             grads_in.record(copy_stream)
-        if world == 1:
-            core.begin(ready=ready)
-        else:                                      # several ranks: statistics start when all local rows are in
-            main_stream.wait_event(ready[-1][3])
-            core.begin()
+        core.begin(ready=ready)
         main_stream.wait_event(grads_in)
         core.step()
         checksum.copy_(roles[0]["all"][0][0, :1], non_blocking=True)

@@ -28,7 +28,7 @@ def _microbatch(rank, mb_index):
     return torch.randn(MB, SEQ, HID, generator=g)
 
 
-def _run(kind, world, rank, device, microbatches, steps=2, first_step=0, resume=None, save_to=None):
+def _run(kind, world, rank, device, microbatches, steps=2, first_step=0, resume=None, save_to=None, streamed=False):
     """One process's part of optimizer steps first_step .. steps-1; returns its weights.  `resume` = (weights,
     checkpoint) continues a run saved after `first_step` steps; `save_to` writes rank zero's checkpoint at the end."""
     import toner_b200.fast as fast
@@ -53,7 +53,12 @@ def _run(kind, world, rank, device, microbatches, steps=2, first_step=0, resume=
                         h = (x + step).to(device)
                         for b in stack:
                             h = b(h)
-            opt.begin()
+            if streamed:    # rows "arrive" group by group: wide statistics first, then the hidden-width ones in two slices
+                ev = torch.cuda.Event()
+                ev.record()
+                opt._core.begin(ready=[("f", 0, LAYERS, ev), ("d", 0, 2, ev), ("d", 2, 3 * LAYERS, ev)])
+            else:
+                opt.begin()
             g = torch.Generator().manual_seed(77 + step)     # gradients arrive already synchronised
             for b in stack:
                 for p in b.parameters():
@@ -72,7 +77,7 @@ def _run(kind, world, rank, device, microbatches, steps=2, first_step=0, resume=
         opt.close()
 
 
-def _worker(rank, world, port, kind, out_dir, steps=2, save=False):
+def _worker(rank, world, port, kind, out_dir, steps=2, save=False, streamed=False):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       NCCL_NVLS_ENABLE="0")
@@ -81,8 +86,8 @@ def _worker(rank, world, port, kind, out_dir, steps=2, save=False):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     try:
         weights = _run(kind, world, rank, device, [_microbatch(rank, i) for i in range(ACC)], steps=steps,
-                       save_to=os.path.join(out_dir, f"ckpt{steps}.pt") if save else None)
-        torch.save(weights, os.path.join(out_dir, f"w{rank}_{steps}.pt"))
+                       save_to=os.path.join(out_dir, f"ckpt{steps}.pt") if save else None, streamed=streamed)
+        torch.save(weights, os.path.join(out_dir, f"w{rank}_{steps}{'s' if streamed else ''}.pt"))
     finally:
         dist.destroy_process_group()
 
@@ -127,3 +132,20 @@ def test_checkpoint_saved_by_two_ranks_resumes_on_one(tmp_path):
     for a, b in zip(resumed, want):
         rel = (a - b).norm().item() / b.norm().item()
         assert rel < 3e-4, rel
+
+
+def test_streamed_rows_on_two_ranks_change_nothing(tmp_path):
+    """begin(ready=...) with several ranks: each group's SYRK / reduce-scatter / factors start when that group's rows
+    are in.  Statistics are independent, so the weights are bit-identical to the plain order."""
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), "muont", str(tmp_path), 2, False, False), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), "muont", str(tmp_path), 2, False, True), nprocs=world, join=True)
+    for r in range(world):
+        plain = torch.load(os.path.join(tmp_path, f"w{r}_2.pt"))
+        streamed = torch.load(os.path.join(tmp_path, f"w{r}_2s.pt"))
+        assert all(torch.equal(a, b) for a, b in zip(plain, streamed))

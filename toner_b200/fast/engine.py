@@ -350,26 +350,39 @@ class FastTonerCore:
 
     @torch.no_grad()
     def _stats_as_rows_arrive(self, ready) -> None:
-        """Single rank, rows still arriving (for example copied from host memory on another stream): `ready` lists
-        (group name, first statistic, one past the last, event) in the order the rows land.  Each slice's SYRK + EMA
-        waits for its event only, and a group's factors are enqueued as soon as its last slice is in, so the
-        remaining transfers overlap them."""
-        if self.world != 1 or self.row_pieces != 1:
-            raise RuntimeError("streamed rows need a single rank and row buffers that hold the whole step")
+        """Rows still arriving (for example copied from host memory on another stream): `ready` lists (group name,
+        first statistic, one past the last, event) in the order the rows land, each group's slices contiguous and in
+        order.  On a single rank each slice's SYRK + EMA waits for its own event; with several ranks a group's
+        chunked SYRK / reduce-scatter waits for the group's last event.  Either way a group's factors are enqueued
+        as soon as its statistics are, so the remaining transfers overlap them."""
+        if self.row_pieces != 1:
+            raise RuntimeError("streamed rows need row buffers that hold the whole step")
         b = self.decay
         gamma = (1 - b) / self.rows_total
         done = {name: 0 for name in self.groups}
-        for name, lo, hi, event in ready:
-            g = self.groups[name]
-            if lo != done[name] or not lo < hi <= g.k_all:
+        for name, lo, hi, _ in ready:
+            if name not in done or lo != done[name] or not lo < hi <= self.groups[name].k_all:
                 raise ValueError(f"slices of group {name} must be contiguous and in order")
-            self.side.wait_event(event)
-            ops.syrk_upper(g.rows_buf[lo:hi], g.factors.ema[lo:hi], ops.EMA_FULL, b, gamma)
             done[name] = hi
-            if hi == g.k_all:
-                g.factors.compute()
         if any(done[name] != g.k_all for name, g in self.groups.items()):
             raise ValueError("the slices must cover every statistic")
+        for name, lo, hi, event in ready:
+            g = self.groups[name]
+            self.side.wait_event(event)
+            if self.world == 1:
+                ops.syrk_upper(g.rows_buf[lo:hi], g.factors.ema[lo:hi], ops.EMA_FULL, b, gamma)
+            if hi != g.k_all:
+                continue
+            if self.world > 1:   # all of the group's rows are in: partial Grams, sums at the owners, EMA
+                pending = []
+                for c in range(g.chunks):
+                    self._partial_grams(g, c)
+                    pending.append((c, dist.reduce_scatter_tensor(g.summed[c], g.partial[c], group=self.pg, async_op=True)))
+                cs = g.chunk_stats
+                for c, work in pending:
+                    work.wait()
+                    ops.unpack_ema(g.summed[c], g.factors.ema[c * cs:(c + 1) * cs], b, gamma)
+            g.factors.compute()
         self.weight = b * self.weight + (1 - b)
 
     @torch.no_grad()

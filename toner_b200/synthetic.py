@@ -70,11 +70,14 @@ def make_stack(layout: str, layers: int, hidden: int, mlp: int, device, seed: in
     return [cls(hidden, mlp, device) for _ in range(layers)]
 
 
-def fill_rows(buf: torch.Tensor, seed: int) -> None:
-    """Activation-like BF16 rows: unit-variance noise plus a shared mean direction (as residual streams have)."""
+def fill_rows(buf: torch.Tensor, seed: int, mean_seed: int = None) -> None:
+    """Activation-like BF16 rows: unit-variance noise plus a shared mean direction (as residual streams have).
+    `mean_seed` fixes the mean direction separately from the noise: ranks that hold different tokens of the same
+    model see different rows around the same mean."""
     g = torch.Generator(device=buf.device).manual_seed(seed)
     k, rows, n = buf.shape
-    mean = torch.randn(1, 1, n, device=buf.device, generator=g) * 0.5
+    gm = g if mean_seed is None else torch.Generator(device=buf.device).manual_seed(mean_seed)
+    mean = torch.randn(1, 1, n, device=buf.device, generator=gm) * 0.5
     step = max(1, min(k, (1 << 28) // max(1, rows * n)))
     for s in range(0, k, step):
         e = min(k, s + step)
