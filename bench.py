@@ -199,7 +199,11 @@ def run_ours(args) -> None:
     roles = list(core.roles.values())
     host_grads = [torch.randn(info["all"][0].shape).mul_(1e-3).pin_memory() for info in roles]
     checksum = torch.zeros(1, dtype=torch.float32).pin_memory()
-    h2d = layers * (host_rows_d.numel() * 2 + host_rows_f.numel() * 2 + sum(g.numel() * 4 for g in host_grads))
+    # a rank reads the gradients of the layers it owns only (the other layers' changes arrive by all-gather)
+    own_lo = sum(core.layer_counts[:rank])
+    own_layers = range(own_lo, own_lo + core.per_layers)
+    h2d = world * (layers * (host_rows_d.numel() * 2 + host_rows_f.numel() * 2) +
+                   len(own_layers) * sum(g.numel() * 4 for g in host_grads))        # all ranks together
 
     # The copies run on their own stream in the order the step consumes them -- the wide (MLP) statistics first, whose
     # factors are most of the step, then the hidden-width ones, then the gradients -- four layers per event, and
@@ -226,7 +230,7 @@ def run_ours(args) -> None:
                 ev = torch.cuda.Event()
                 ev.record(copy_stream)
                 ready.append(("d", 3 * lo, 3 * hi, ev))
-            for i in range(layers):
+            for i in own_layers:
                 for info, hg in zip(roles, host_grads):
                     info["all"][i].grad.copy_(hg, non_blocking=True)
             grads_in = torch.cuda.Event()
