@@ -24,13 +24,15 @@ def fast():
     return f
 
 
-def make(fast, layout, kind, **kw):
+def make(fast, layout, kind, dims=None, **kw):
     from toner_b200.synthetic import make_stack
-    stack = make_stack(layout, LAYERS, HID, MLP, torch.device("cuda"), seed=0)
+    hid, mlp, seq, mb, acc, layers, head, stride = dims or (HID, MLP, SEQ, MB, ACC, LAYERS, 8, 4)
+    stack = make_stack(layout, layers, hid, mlp, torch.device("cuda"), seed=0)
     wrap = fast.ProjectionBlock if layout == "llama" else fast.NanoGPTBlock
     cls = fast.FastMuonT if kind == "muont" else fast.FastAdamT
     opt = cls([wrap.from_module(b) for b in stack], 0.02 if kind == "muont" else 2e-3, weight_decay=0.1,
-              micro_batch_size=MB, sequence_length=SEQ, accumulation_steps=ACC, statistic_head=8, statistic_stride=4, **kw)
+              micro_batch_size=mb, sequence_length=seq, accumulation_steps=acc, statistic_head=head,
+              statistic_stride=stride, **kw)
     return stack, opt
 
 
@@ -38,6 +40,8 @@ def forward(stack, x):
     with torch.autocast("cuda", dtype=torch.bfloat16):
         for b in stack:
             x = b(x)
+            if len(stack) > 4:   # deep stacks: keep the residual stream O(1), as the real blocks' norms do
+                x = torch.nn.functional.layer_norm(x.float(), (x.shape[-1],))
     return x
 
 
@@ -50,15 +54,27 @@ def role_modules(block, layout):
 
 @pytest.mark.parametrize("layout,kind", [("llama", "muont"), ("nanogpt", "muont"), ("llama", "adamt")])
 def test_two_steps_match_oracle(fast, layout, kind):
+    steps_against_oracle(fast, layout, kind, (HID, MLP, SEQ, MB, ACC, LAYERS, 8, 4), 2)
+
+
+def test_nanogpt_stack_at_full_size(fast):
+    """The 12-layer modded-nanoGPT shape (hidden 768, MLP 3072, six matrices per layer), 4 x 16 sequences of 1024
+    tokens per update sampled with head 32 / stride 16: 6016 rows per statistic, 36 statistics of 768^2 and 12 of
+    3072^2, 72 matrices -- one FastMuonT step against the oracle's general path on the same rows."""
+    steps_against_oracle(fast, "nanogpt", "muont", (768, 3072, 1024, 16, 4, 12, 32, 16), 1)
+
+
+def steps_against_oracle(fast, layout, kind, dims, steps):
+    HID, MLP, SEQ, MB, ACC, LAYERS, head, stride = dims
     extra = dict(ns_steps=2) if kind == "muont" else dict(betas=(0.9, 0.95), eps=ADAM_EPS)
-    stack, opt = make(fast, layout, kind, **extra)
+    stack, opt = make(fast, layout, kind, dims, **extra)
     try:
-        positions = orc.sample_positions(SEQ, 8, 4)
+        positions = orc.sample_positions(SEQ, head, stride)
         params = [(li, k, m) for li, b in enumerate(stack) for k, ms in role_modules(b, layout).items() for m in ms]
         ref_w = {id(m): m.weight.detach().cpu().clone() for _, _, m in params}
         states = {id(m): (orc.MuonTState() if kind == "muont" else orc.AdamTState()) for _, _, m in params}
         gen = torch.Generator().manual_seed(5)
-        for step in range(2):
+        for step in range(steps):
             captured = {}
             hooks = []
             for li, k, m in params:  # record what each projection really read (after autocast rounding)

@@ -197,3 +197,72 @@ def test_activation_statistics_matches_golden(tb, golden):
     with pytest.raises(RuntimeError):
         with stats.capture():
             pass
+
+
+def test_nanogpt_stack_with_activation_statistics_and_adamt(tb):
+    """The 12-layer modded-nanoGPT shape: ActivationStatistics(head 32, stride 16) over its 72 projections on one
+    batch of 8 x 1024 tokens under BF16 autocast (752 rows per statistic), committed to AdamT(betas=(0.9, 0.95)),
+    one step.  Every statistic against the oracle's Gram of the rows that projection read; every weight against
+    the oracle's AdamT step.  Adam's eps is 1e-4 here: with the default 1e-20 the first update is g / |g R| entry by
+    entry, unbounded wherever (g R) happens to vanish -- one such entry (1e9) in one of the 72 matrices is enough
+    to rescale that whole matrix through ||U|| / ||U R||, on either side of the comparison, so no two correct
+    implementations agree there.  Gradients are ~1e-3, so eps 1e-4 keeps the same arithmetic and bounds the ratio."""
+    from toner_b200 import ops
+    from toner_b200.synthetic import make_stack
+    stack = make_stack("nanogpt", 12, 768, 3072, torch.device("cuda"), seed=0)
+    layers = {}
+    for i, b in enumerate(stack):
+        for name, lin in (("q", b.attn.q), ("k", b.attn.k), ("v", b.attn.v), ("proj", b.attn.proj), ("fc", b.mlp.fc),
+                          ("mproj", b.mlp.proj)):
+            layers[f"{i}.{name}"] = lin
+    params = [lin.weight for lin in layers.values()]
+    opt = tb.AdamT(params, lr=2e-3, weight_decay=0.1, betas=(0.9, 0.95), eps=1e-4)
+    stats = tb.ActivationStatistics(layers, head=32, stride=16, distributed=False)
+    seen, hooks = {}, []
+    for name, lin in layers.items():
+        hooks.append(lin.register_forward_pre_hook(
+            lambda mod, inp, key=name: seen.__setitem__(key, inp[0].detach().to(torch.bfloat16).cpu())))
+    gen = torch.Generator().manual_seed(1)
+    x = torch.randn(8, 1024, 768, generator=gen).cuda()
+    with stats.capture():
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            h = x
+            for b in stack:   # keep the residual stream O(1) between blocks, as the real blocks' norms do
+                h = torch.nn.functional.layer_norm(b(h).float(), (768,))
+    for h_ in hooks:
+        h_.remove()
+    means = {}
+
+    class Tee:
+        def update_statistics(self, m):
+            means.update(m)
+            opt.update_statistics(m)
+
+    stats.commit(Tee())
+    stats.close()
+    before = {name: lin.weight.detach().cpu().clone() for name, lin in layers.items()}
+    grads = {name: torch.randn(lin.weight.shape, generator=gen) * 1e-3 for name, lin in layers.items()}
+    for name, lin in layers.items():
+        lin.weight.grad = grads[name].cuda()
+    opt.step()
+    ops.assert_healthy()
+    assert opt.fallbacks == 0
+    positions = orc.sample_positions(1024, 32, 16)
+    assert len(positions) == 94
+    worst_stat = worst_w = worst_u = 0.0
+    for name, lin in layers.items():
+        rows = seen[name][:, positions].reshape(-1, seen[name].shape[-1])
+        assert rows.shape[0] == 752
+        mean = orc.gram(rows) / rows.shape[0]
+        worst_stat = max(worst_stat, orc.rel_fro(means[lin.weight].cpu(), mean))
+        state = orc.AdamTState()
+        state.ema, state.weight = orc.ema_update(None, 0.0, mean, 0.95)
+        want = orc.adamt_step(before[name], grads[name], state, lr=2e-3, weight_decay=0.1, betas=(0.9, 0.95), eps=1e-4)
+        got = lin.weight.detach().cpu()
+        worst_w = max(worst_w, orc.rel_fro(got, want))
+        worst_u = max(worst_u, orc.rel_fro(got - before[name], want - before[name]))
+    assert worst_stat < 1e-5, worst_stat
+    # Adam's first step is m / (|g R| + eps) entry by entry: where |g R| is small against eps-scale noise the ratio
+    # moves by far more than the factors differ (1e-3), most on the deep layers' rank-deficient statistics
+    # (752 rows, 3072 columns); measured 1.6e-3 on the weights, 1.7e-2 on the update
+    assert worst_w < 6e-3 and worst_u < 6e-2, (worst_w, worst_u)
