@@ -149,6 +149,8 @@ def run_ours(args) -> None:
         opt = FastMuonT(blocks, LR, weight_decay=WD, momentum=MOMENTUM, micro_batch_size=micro,
                         sequence_length=SEQ_LEN, accumulation_steps=acc)
     core = opt._core
+    if args.sm_reserve is not None and world > 1:
+        core.sm_reserve = int(args.sm_reserve)
     # Engine-level seam (what the reference's second trainer uses): the sampled rows of this rank's tokens
     # are written straight into the row buffers, gradients into .grad, then begin() and step().
     for gi, g in enumerate(core.groups.values()):
@@ -387,6 +389,8 @@ def main() -> None:
     ap.add_argument("--sequences", type=int, default=SEQUENCES)
     ap.add_argument("--optimizer", default="muont", choices=["muont", "adamt"], help="FastMuonT (headline) or FastAdamT")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--sm-reserve", type=int, default=None,
+                    help="SMs the GEMMs leave to NCCL while a collective overlaps them (several ranks; default: the engine's)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (for profiler runs)")
     args = ap.parse_args()
     if args.impl == "reference":

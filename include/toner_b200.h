@@ -35,6 +35,12 @@ long long toner_launch_count(void);       /* kernels launched by this library so
 /* Synchronise `stream`, then read and clear the device status word that kernels set when one of their
  * bounded waits runs out (0 = healthy). */
 int toner_device_status(void* stream, int* status_out);
+/* CTAs the persistent GEMM kernel launches from now on (this device): 0 = one per SM (default), else at most `sms`
+ * (rounded down to an even count).  The kernel assigns its tiles to CTAs up front, so a CTA that finds no free SM --
+ * because a collective running on another stream holds some -- starts only when a whole CTA's share of tiles has
+ * finished elsewhere.  A host that overlaps collectives with these products leaves the collective's SMs free
+ * instead.  Host-side state read at launch time; no counterpart in the reference (its kernels are not persistent). */
+int toner_set_gemm_sm_limit(int32_t sms);
 /* Self-test of that mechanism (the reference has no device-side waits): launches a one-warp kernel whose wait can
  * never be satisfied and gives up after `limit_cycles` SM cycles (at most 2e9).  The kernel returns normally, the
  * next toner_device_status reports 199, and the context stays usable. */

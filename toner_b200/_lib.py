@@ -66,6 +66,7 @@ SIGNATURES = {
     "toner_launch_count": (C.c_longlong, []),
     "toner_device_status": (C.c_int, [_vp, C.POINTER(C.c_int)]),
     "toner_gemm": (C.c_int, [C.POINTER(GemmDesc), _vp]),
+    "toner_set_gemm_sm_limit": (C.c_int, [_i32]),
     "toner_selftest_bounded_wait": (C.c_int, [C.c_longlong, _vp]),
     "toner_gemm_phase_cycles": (C.c_int, [C.c_int, _vp, C.POINTER(C.c_uint64)]),
     "toner_syrk_upper": (C.c_int, [C.POINTER(_vp), _vp, _i64, _i32, _i32, _i32, _i64, _vp, _i32, _f32, _f32, _vp]),

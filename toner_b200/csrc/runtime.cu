@@ -60,6 +60,7 @@ Context* context() {
     return nullptr;
   }
   c.num_sms = prop.multiProcessorCount;
+  c.gemm_sms = c.num_sms;
   c.arena_cap = 32768;
   if (cudaMalloc(&c.arena_dev, sizeof(CUtensorMap) * c.arena_cap) != cudaSuccess ||
       cudaMallocHost(&c.arena_host, sizeof(CUtensorMap) * c.arena_cap) != cudaSuccess ||
@@ -154,11 +155,11 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
   if (bn == 0) {
     const long long tpair = (long long)gemm_tiles_per_batch(d.m, d.n, 256, d.tri, 256) * d.batch;
     const long long t256 = (long long)gemm_tiles_per_batch(d.m, d.n, 256, d.tri) * d.batch;
-    if (tpair >= ctx->num_sms / 2) {
+    if (tpair >= ctx->gemm_sms / 2) {
       bn = 256;
       pair = true;
     } else {
-      bn = (t256 >= ctx->num_sms) ? 256 : 128;
+      bn = (t256 >= ctx->gemm_sms) ? 256 : 128;
     }
   } else if (bn == 512) {
     bn = 256;
@@ -220,7 +221,7 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
   if (total > 0x7fffffffLL) return fail(kErrArg, "gemm: too many tiles");
   const bool chained = p.promote > 0;
   if (pair) {
-    const int pairs = (int)(total < ctx->num_sms / 2 ? total : ctx->num_sms / 2);
+    const int pairs = (int)(total < ctx->gemm_sms / 2 ? total : ctx->gemm_sms / 2);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
     cfg.blockDim = dim3(kGemmThreads);
@@ -238,7 +239,7 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
     count_launch();
     return 0;
   }
-  const int grid = (int)(total < ctx->num_sms ? total : ctx->num_sms);
+  const int grid = (int)(total < ctx->gemm_sms ? total : ctx->gemm_sms);
   if (bn == 256) {
     if (chained) gemm_tcgen05_kernel<256, true><<<grid, kGemmThreads, GemmSmem<256>::kTotal, stream>>>(p);
     else gemm_tcgen05_kernel<256, false><<<grid, kGemmThreads, GemmSmem<256>::kTotal, stream>>>(p);
@@ -283,6 +284,16 @@ long long toner_launch_count(void) { return toner::g_launches.load(std::memory_o
 int toner_sm_count(void) {
   toner::Context* c = toner::context();
   return c ? c->num_sms : 0;
+}
+
+int toner_set_gemm_sm_limit(int32_t sms) {
+  toner::Context* c = toner::context();
+  if (!c) return toner::kErrCuda;
+  if (sms < 0) return toner::fail(toner::kErrArg, "gemm sm limit: must be 0 (all) or a positive count");
+  int n = sms == 0 || sms > c->num_sms ? c->num_sms : sms;
+  n &= ~1;  // CTA pairs
+  c->gemm_sms = n < 2 ? 2 : n;
+  return 0;
 }
 
 int toner_device_status(void* stream, int* status_out) {

@@ -207,6 +207,9 @@ class FastTonerCore:
         self.main_stream = torch.cuda.current_stream(device)
         self.side = torch.cuda.Stream(device=device, priority=-1)
         self.pg = dist.new_group(backend="nccl") if world > 1 else None
+        # SMs left free for NCCL's kernels while a collective overlaps the persistent GEMMs (see _beside_collective)
+        # (off by default: on two ranks reserving 8-32 SMs changed nothing or cost 1-2 %)
+        self.sm_reserve = int(getattr(args, "nccl_sm_reserve", 0)) if world > 1 else 0
         if world > 1 or self.row_pieces > 1:   # packed partial Grams: summed over ranks, or over the pieces of a step
             for g in self.groups.values():
                 g.plan_chunks(int(getattr(args, "stat_chunks", 4)) if world > 1 else 1)
@@ -286,6 +289,14 @@ class FastTonerCore:
         return sum(g.factors.repairs for g in self.groups.values())
 
     # ------------------------------------------------------------------ statistics (side stream)
+    def _beside_collective(self, active: bool) -> None:
+        """Products launched from here on run beside a collective (True) or alone (False).  The persistent GEMM
+        assigns tiles to its CTAs up front; with all 148 launched while NCCL holds some SMs, the CTAs that find no
+        SM start only after others have finished their whole share, which can double the product's duration.
+        Leaving `sm_reserve` SMs unclaimed costs that fraction of throughput instead."""
+        if self.sm_reserve > 0:
+            ops.set_gemm_sm_limit(max(2, ops.sm_count() - self.sm_reserve) if active else 0)
+
     def _partial_grams(self, g: "StatGroup", c: int) -> None:
         """Packed Grams of statistic chunk c from the rows now in the buffers, added to earlier pieces of the step."""
         mode = ops.PACKED_ACC if self.pieces_done else ops.PACKED
@@ -341,6 +352,8 @@ class FastTonerCore:
                     # NCCL waits for the SYRK just enqueued and runs on its own stream: the next chunk's SYRK overlaps it
                     work = dist.reduce_scatter_tensor(g.summed[c], g.partial[c], group=self.pg, async_op=True)
                     pending.append((g, c, work))
+                    self._beside_collective(True)
+            self._beside_collective(False)
             for g, c, work in pending:
                 work.wait()
                 cs = g.chunk_stats
@@ -378,6 +391,8 @@ class FastTonerCore:
                 for c in range(g.chunks):
                     self._partial_grams(g, c)
                     pending.append((c, dist.reduce_scatter_tensor(g.summed[c], g.partial[c], group=self.pg, async_op=True)))
+                    self._beside_collective(True)
+                self._beside_collective(False)
                 cs = g.chunk_stats
                 for c, work in pending:
                     work.wait()
@@ -451,6 +466,8 @@ class FastTonerCore:
                     ops.apply_delta(info["all_ptrs"], info["delta"])
             if self.world > 1:   # this part's changes travel while the next part is computed
                 works.append(dist.all_gather_into_tensor(part["gathered"], part["delta"], group=self.pg, async_op=True))
+                self._beside_collective(True)
+        self._beside_collective(False)
         self._ev[4].record(self.main_stream)
         per = self.per_layers
         for part, work in zip(self.parts, works):

@@ -37,6 +37,11 @@ def sm_count() -> int:
     return _lib.load().toner_sm_count()
 
 
+def set_gemm_sm_limit(sms: int) -> None:
+    """CTAs the persistent GEMM launches from now on (0: one per SM); see toner_set_gemm_sm_limit."""
+    check(_lib.load().toner_set_gemm_sm_limit(int(sms)), "toner_set_gemm_sm_limit")
+
+
 def launch_count() -> int:
     """Kernels launched by the CUDA library so far."""
     return int(_lib.load().toner_launch_count())
