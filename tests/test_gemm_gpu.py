@@ -211,3 +211,26 @@ def test_a_wait_that_runs_out_is_reported_not_fatal(ops):
     ops.gemm(ops.operand(a), ops.operand(b), m=128, n=128, k=64, batch=1, fmt=1, d=d)
     ops.assert_healthy()
     close(d[0], ref_mm(a, b, False, False), 64)
+
+
+def test_fewer_ctas_give_the_same_bits(ops):
+    """toner_set_gemm_sm_limit: the persistent kernel on 64 CTAs (32 pairs) walks the same tiles in the same order per
+    tile, so results are bit-identical to the full grid; 0 restores one CTA per SM."""
+    a, b = rnd((1024, 512), torch.bfloat16, 7), rnd((1536, 512), torch.bfloat16, 8)
+
+    def run():
+        d = torch.zeros(1, 1024, 1536, device="cuda")
+        ops.gemm(ops.operand(a), ops.operand(b), m=1024, n=1536, k=512, batch=1, fmt=1, d=d)
+        return d
+
+    full = run()
+    try:
+        ops.set_gemm_sm_limit(64)
+        limited = run()
+        ops.set_gemm_sm_limit(3)      # rounded down to one pair
+        tiny = run()
+    finally:
+        ops.set_gemm_sm_limit(0)
+    ops.assert_healthy()
+    assert torch.equal(full, limited) and torch.equal(full, tiny)
+    close(full[0], ref_mm(a, b, False, False), 512)
