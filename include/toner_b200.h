@@ -13,6 +13,13 @@
  *   - the library never allocates caller-visible memory: scratch is a caller-provided workspace whose
  *     size comes from the matching *_workspace_bytes query.  (The per-device context keeps one small
  *     private arena for TMA tensor maps, created on first use.)
+ *   - streams and the tensor-map arena: the first product that reads an operand (address, shape, strides)
+ *     encodes its TMA tensor maps on the host and uploads them with an asynchronous copy on that call's
+ *     stream; later products find them by that key.  A product launched on ANOTHER stream before the upload
+ *     has finished is made to wait for it (an event recorded after the copy), so any stream may be passed
+ *     to any call.  The arena holds 32768 maps; when it is full the library synchronises the device once
+ *     and starts over (not allowed during stream capture: a captured region should reuse operand addresses,
+ *     which costs no new map)
  *   - matrices are row-major FP32 unless said otherwise; "stack" means `batch` equally shaped matrices
  *     stored back to back
  *   - there is no CPU fallback: without a CUDA device every compute entry point fails
@@ -35,6 +42,11 @@ long long toner_launch_count(void);       /* kernels launched by this library so
 /* Synchronise `stream`, then read and clear the device status word that kernels set when one of their
  * bounded waits runs out (0 = healthy). */
 int toner_device_status(void* stream, int* status_out);
+/* The same word without a synchronisation: an asynchronous copy into `host_out` (pinned HOST memory, one int32)
+ * enqueued on `stream`; the word is not cleared.  A host that already waits for something later on that stream (the
+ * factor engine's status flags, an event after the update) reads it then, and so learns of a product that gave up
+ * a wait before it uses the product's result.  The reference has no counterpart (its kernels do not wait). */
+int toner_status_snapshot(int32_t* host_out, void* stream);
 /* CTAs the persistent GEMM kernel launches from now on (this device): 0 = one per SM (default), else at most `sms`
  * (rounded down to an even count).  The kernel assigns its tiles to CTAs up front, so a CTA that finds no free SM --
  * because a collective running on another stream holds some -- starts only when a whole CTA's share of tiles has

@@ -64,6 +64,53 @@ def test_nanogpt_stack_at_full_size(fast):
     steps_against_oracle(fast, "nanogpt", "muont", (768, 3072, 1024, 16, 4, 12, 32, 16), 1)
 
 
+def test_llama_layer_at_full_width(fast):
+    """One layer of the benchmark's Llama shape -- hidden 2048, MLP 5632, sequences of 4096 tokens sampled with head
+    32 / stride 16 -- with 5 x 4 sequences per update: 5720 rows per statistic, so the 5632-wide statistic has full
+    rank.  One FastMuonT step against the oracle's general path on the rows every projection read."""
+    steps_against_oracle(fast, "llama", "muont", (2048, 5632, 4096, 4, 5, 1, 32, 16), 1)
+
+
+def test_status_word_is_read_at_the_step(fast):
+    """The engine reads the kernels' status word where it waits for the factors anyway: a kernel that gave up a wait
+    (here the library's self-test kernel, which waits a millisecond for a barrier nothing arrives at) makes step()
+    raise before any change is applied; the optimizer works again afterwards."""
+    import ctypes as C
+    from toner_b200 import _lib, ops
+    stack, opt = make(fast, "llama", "muont", ns_steps=2)
+    try:
+        gen = torch.Generator().manual_seed(3)
+        weights = [p for b in stack for p in b.parameters() if p.ndim == 2]
+
+        def one(expect_error):
+            for _ in range(ACC):
+                with opt.capture_microbatch():
+                    forward(stack, torch.randn(MB, SEQ, HID, generator=gen).cuda())
+            if expect_error:
+                stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+                assert _lib.load().toner_selftest_bounded_wait(2_000_000, stream) == 0
+            opt.begin()
+            for p in weights:
+                p.grad = (torch.randn(p.shape, generator=gen) * 1e-3).cuda()
+            if expect_error:
+                with pytest.raises(_lib.TonerError, match="gave up a bounded wait"):
+                    opt.step()
+            else:
+                opt.step()
+            torch.cuda.synchronize()
+
+        one(False)
+        before = [p.detach().clone() for p in weights]
+        one(True)
+        assert all(torch.equal(a, p.detach()) for a, p in zip(before, weights))
+        assert ops.device_status() == 0
+        one(False)
+        assert not torch.equal(before[0], weights[0].detach())
+        ops.assert_healthy()
+    finally:
+        opt.close()
+
+
 def steps_against_oracle(fast, layout, kind, dims, steps):
     HID, MLP, SEQ, MB, ACC, LAYERS, head, stride = dims
     extra = dict(ns_steps=2) if kind == "muont" else dict(betas=(0.9, 0.95), eps=ADAM_EPS)
@@ -91,7 +138,7 @@ def steps_against_oracle(fast, layout, kind, dims, steps):
             for _, _, m in params:
                 m.weight.grad = (torch.randn(m.weight.shape, generator=gen) * 1e-3).cuda()
             opt.step()
-            worst = 0.0
+            worst = worst_update = 0.0
             for li, k, m in params:
                 rows = torch.cat([t[:, positions].reshape(-1, t.shape[-1]) for t in captured[(li, k)][::len(role_modules(stack[li], layout)[k])]])
                 st = states[id(m)]
@@ -103,8 +150,13 @@ def steps_against_oracle(fast, layout, kind, dims, steps):
                 else:
                     after = orc.adamt_step(before, g, st, lr=2e-3, weight_decay=0.1, betas=(0.9, 0.95), eps=ADAM_EPS)
                 ref_w[id(m)] = after
-                worst = max(worst, orc.rel_fro(m.weight.detach().cpu(), after))
+                got = m.weight.detach().cpu()
+                worst = max(worst, orc.rel_fro(got, after))
+                if step == 0:   # later steps start from weights that already differ: compare the first change
+                    worst_update = max(worst_update, orc.rel_fro(got - before, after - before))
+            print(f"{layout} {kind} hidden {HID} step {step}: weights {worst:.2e}, first change {worst_update:.2e}")
             assert worst < 2e-3, (layout, kind, step, worst)
+            assert worst_update < 4e-3, (layout, kind, step, worst_update)
             if kind == "adamt":  # the moments themselves are smooth functions of the factors
                 for li, k, m in params[:3]:
                     role = [r for r, info in opt._core.roles.items() if any(w is m.weight for w in info["all"])][0]

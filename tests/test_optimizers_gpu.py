@@ -266,3 +266,84 @@ def test_nanogpt_stack_with_activation_statistics_and_adamt(tb):
     # moves by far more than the factors differ (1e-3), most on the deep layers' rank-deficient statistics
     # (752 rows, 3072 columns); measured 1.6e-3 on the weights, 1.7e-2 on the update
     assert worst_w < 6e-3 and worst_u < 6e-2, (worst_w, worst_u)
+
+
+@pytest.mark.parametrize("kind", ["muont", "adamt"])
+def test_checkpoint_resume_of_the_general_optimizers(tb, golden, kind):
+    """state_dict() after two steps, load_state_dict() into a fresh optimizer, two more steps: the loaded statistic
+    EMA and moments are bit-identical to the saved ones, they are what the kernels read (views of the stacked
+    storage), and the continued run follows the uninterrupted one.  The match is not bitwise: the resumed optimizer
+    has no spectrum bound from a previous factorisation and runs the Newton schedule of the bound that always holds,
+    so its factors differ from the uninterrupted run's inside the factor engine's accuracy (1e-4)."""
+    import copy
+    g = golden(f"{kind}_small.npz")
+    steps = g["w"].shape[0]
+    kw = dict(ns_steps=2) if kind == "muont" else dict(eps=1e-4)
+    straight, _ = run_cuda(tb, kind, g, steps, **kw)
+
+    w = torch.nn.Parameter(t(g["w0"]).clone().cuda())
+    make = (lambda p: tb.MuonT([p], lr=0.02, weight_decay=0.1, momentum=0.95, **kw)) if kind == "muont" else \
+           (lambda p: tb.AdamT([p], lr=2e-3, weight_decay=0.1, betas=(0.9, 0.95), **kw))
+    opt = make(w)
+
+    def advance(o, p, s):
+        x, grad = t(g["x"][s]).cuda(), t(g["g"][s]).cuda()
+        o.update_statistics({p: x.T @ x / x.shape[0]})
+        p.grad = grad.clone()
+        o.step()
+
+    for s in range(2):
+        advance(opt, w, s)
+    saved = copy.deepcopy(opt.state_dict())
+    keys = ("input_ema", "momentum_buffer") if kind == "muont" else ("input_ema", "exp_avg", "exp_avg_sq")
+    assert set(keys) <= set(saved["state"][0])
+
+    w2 = torch.nn.Parameter(w.detach().clone())
+    fresh = make(w2)
+    fresh.load_state_dict(saved)
+    for s in range(2, steps):
+        if s == 2:   # before the first resumed step the loaded values must be the ones in the state
+            for key in keys:
+                assert torch.equal(fresh.state[w2][key].cpu(), saved["state"][0][key].cpu()), key
+        advance(fresh, w2, s)
+        bucket, i = fresh._bucket_of[w2]
+        for key, stack in bucket.stacks().items():   # the state keys alias the storage the kernels use
+            assert fresh.state[w2][key].data_ptr() == stack[i].data_ptr(), key
+        rel = orc.rel_fro(w2.detach().cpu(), straight[s])
+        assert rel < 1e-3, (kind, s, rel)
+    if kind == "adamt":
+        assert fresh.state[w2]["step"] == steps
+    assert float(fresh.state[w2]["input_weight"]) == pytest.approx(1 - 0.95 ** steps, rel=1e-6)
+
+
+def test_a_kernel_that_gave_up_a_wait_stops_the_next_step(tb, golden):
+    """Failure detection without a fault: the library's self-test kernel waits on a barrier nothing arrives at, gives
+    up after a millisecond and sets the status word exactly as a product that gave up would.  The next step() must
+    raise before it applies anything, clear the condition, and the step after it must work."""
+    import ctypes as C
+    from toner_b200 import _lib, ops
+    g = golden("muont_small.npz")
+    w = torch.nn.Parameter(t(g["w0"]).clone().cuda())
+    opt = tb.MuonT([w], lr=0.02, weight_decay=0.1, momentum=0.95, ns_steps=2)
+
+    def feed(s):
+        x, grad = t(g["x"][s]).cuda(), t(g["g"][s]).cuda()
+        opt.update_statistics({w: x.T @ x / x.shape[0]})
+        w.grad = grad.clone()
+
+    feed(0)
+    opt.step()
+    after_first = w.detach().clone()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert _lib.load().toner_selftest_bounded_wait(2_000_000, stream) == 0   # about a millisecond
+    feed(1)
+    with pytest.raises(_lib.TonerError, match="gave up a bounded wait"):
+        opt.step()
+    torch.cuda.synchronize()
+    assert torch.equal(w.detach(), after_first)        # nothing was applied
+    assert ops.device_status() == 0                     # the condition was cleared when it was reported
+    opt.state[w]["statistics_ready"] = True             # the statistics of the refused step are still current
+    opt.step()
+    torch.cuda.synchronize()
+    assert not torch.equal(w.detach(), after_first)
+    ops.assert_healthy()

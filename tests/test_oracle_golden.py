@@ -44,6 +44,42 @@ def test_newton_schulz_f32(golden, tag):
     assert orc.rel_fro(got, t(g[f"{tag}_out"])) < 1e-4
 
 
+@pytest.mark.parametrize("tag", ["square", "wide", "tall", "mid"])
+def test_newton_schulz_tpu_against_the_reference_on_cuda(golden, tag):
+    """The restated "tpu" arithmetic (operands rounded to BF16, FP32 products) against the reference's own
+    toner.linalg.newton_schulz(mode="tpu") run on a B200 (tests/golden/make_tpu_golden.py).  The two differ by the
+    summation order inside each product only; the iteration multiplies that by up to 3.44 per step in directions
+    that have not converged (measured here: 7e-7 after one step, 1e-5 after two, 9e-4 after three, 3.6e-2 after ten,
+    the same as the reference's tpu mode against its own f32 mode)."""
+    g = golden("newton_schulz_tpu.npz")
+    m = t(g[f"{tag}_in"])
+    for steps, bound in ((1, 1e-6), (2, 2e-5), (3, 2e-3), (5, 3e-2), (10, 6e-2)):
+        got = orc.newton_schulz(m, steps, 1e-5, "tpu")
+        assert orc.rel_fro(got, t(g[f"{tag}_out{steps}"])) < bound, (tag, steps)
+    # the reference's batched and per-matrix products agree bit for bit on that device; its tpu and f32 modes do not
+    assert float(g["self_noise_batched_vs_single"].max()) == 0.0
+    assert 2e-2 < float(g["self_noise_tpu_vs_f32"][-1]) < 6e-2
+
+
+@pytest.mark.parametrize("tag,update_bound,weight_bound", [("small2", 2e-3, 1e-4), ("small", 8e-2, 2e-2),
+                                                           ("tall", 8e-2, 2e-2)])
+def test_muont_tpu_against_the_reference_on_cuda(golden, tag, update_bound, weight_bound):
+    """muont_step(ns_mode="tpu") against toner.MuonT(ns_mode="tpu") run on a B200: with two Newton-Schulz steps every
+    step's change agrees to 2e-3 (measured 1e-4 .. 3e-4); with ten, the iteration's sensitivity shows (4e-2 .. 5e-2 on
+    a change, up to 1e-2 on these small weights, which move by 15 % of their norm per step)."""
+    g = golden(f"muont_tpu_{tag}.npz")
+    w, state, prev = t(g["w0"]).clone(), orc.MuonTState(), t(g["w0"])
+    for s in range(g["w"].shape[0]):
+        x, grad = t(g["x"][s]), t(g["g"][s])
+        state.ema, state.weight = orc.ema_update(state.ema, state.weight, x.T @ x / x.shape[0], 0.95)
+        mine = orc.muont_step(w, grad, state, lr=0.02, weight_decay=0.1, momentum=0.95, ns_mode="tpu",
+                              ns_steps=int(g["ns_steps"]))
+        want = t(g["w"][s])
+        assert orc.rel_fro(mine - w, want - prev) < update_bound, (tag, s)
+        assert orc.rel_fro(mine, want) < weight_bound, (tag, s)
+        w, prev = mine, want
+
+
 def test_newton_schulz_tpu_restatement_is_a_polar_approximation():
     m = torch.randn(64, 96, generator=torch.Generator().manual_seed(2))
     x = orc.newton_schulz(m, 10, 1e-5, "tpu")

@@ -65,6 +65,7 @@ SIGNATURES = {
     "toner_sm_count": (C.c_int, []),
     "toner_launch_count": (C.c_longlong, []),
     "toner_device_status": (C.c_int, [_vp, C.POINTER(C.c_int)]),
+    "toner_status_snapshot": (C.c_int, [_vp, _vp]),
     "toner_gemm": (C.c_int, [C.POINTER(GemmDesc), _vp]),
     "toner_set_gemm_sm_limit": (C.c_int, [_i32]),
     "toner_selftest_bounded_wait": (C.c_int, [C.c_longlong, _vp]),

@@ -95,6 +95,7 @@ class FactorSet:
         self.norms_host = torch.zeros(k, dtype=torch.float32).pin_memory()
         self.lower = 0.0
         self.status_event: Optional[torch.cuda.Event] = None
+        self.health = ops.Health()
         self.lo_planes = torch.empty(2, k, n, n, device=device, dtype=torch.float16)
         self.lo_inv = torch.empty(k, device=device, dtype=torch.float32)
         if self.q > 1:
@@ -149,6 +150,7 @@ class FactorSet:
         self._split()
         self.status_host.copy_(self.status, non_blocking=True)
         self.norms_host.copy_(self.norms, non_blocking=True)
+        self.health.arm("the factor computation")
         self.status_event = torch.cuda.Event()
         self.status_event.record(torch.cuda.current_stream())
 
@@ -167,6 +169,7 @@ class FactorSet:
             return 0
         self.status_event.synchronize()
         self.status_event = None
+        self.health.check()   # a product of the factor engine that gave up a wait: raise before the factors are used
         bad = [i for i, s in enumerate(self.status_host.tolist()) if s != 0]
         # Next step's bound: damping / ||A'||_F of the widest statistic, with room for one step of EMA drift.
         # A flagged statistic (not converged, or below the bound used) sends the next step back to the bound

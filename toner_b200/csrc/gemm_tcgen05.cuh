@@ -32,6 +32,8 @@ constexpr int kUmmaK = 16;        // K per tcgen05.mma for 16-bit operands
 constexpr int kMaxSegs = 3;
 constexpr int kGemmThreads = 384;      // warpgroup 0: TMA warp, MMA warp, two idle; warpgroups 1-2: epilogue
 constexpr long long kWaitCycles = 4000000000LL;  // about two seconds; a healthy wait is microseconds
+constexpr long long kDrainCycles = 2000000LL;    // per stage, after an abort: about a millisecond for copies in flight
+constexpr long long kSettleCycles = 200000LL;    // after an abort: a CTA of a pair lets copies it cannot observe land
 
 enum GemmStatus : int { kOk = 0, kTimeoutProducer = 101, kTimeoutMma = 102, kTimeoutEpilogue = 103, kTimeoutSelftest = 199 };
 
@@ -341,6 +343,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
   auto tempty_bar = [&](int s) { return bars + 8u * (2 * S::kStages + 2 + s); };
   volatile uint32_t* const tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + S::kTileBytes + 8 * (2 * S::kStages + 4));
   volatile int* const abort_flag = reinterpret_cast<volatile int*>(smem + S::kTileBytes + 8 * (2 * S::kStages + 4) + 8);
+  // A role that gives up stops its own CTA and, in a pair, the peer as well: both CTAs' roles poll their CTA's flag
+  // between waits, so neither keeps issuing copies or MMAs for two more seconds.  The peer's shared memory is valid
+  // until the closing cluster barrier, which every thread of both CTAs reaches.
+  auto raise_abort = [&]() {
+    *abort_flag = 1;
+    if constexpr (kPair)
+      ptx::st_cluster_u32(ptx::mapa(ptx::smem_u32(const_cast<int*>(abort_flag)), cta_rank ^ 1u), 1u);
+  };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = (p.N + BN - 1) / BN;
@@ -440,7 +450,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
             if (p.prof) prof_wait += clock64() - w0;
             if (!got || *abort_flag) {
               report(p.status, kTimeoutProducer);
-              *abort_flag = 1;
+              raise_abort();
               ok = false;
               break;
             }
@@ -485,9 +495,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         }
       }
       if (p.prof) atomicAdd(p.prof + 3, (unsigned long long)prof_wait);
-      if (!ok && !kPair) {
-        // give copies already in flight time to land before the CTA gives its shared memory back
-        for (int s = 0; s < S::kStages; ++s) ptx::mbar_wait(full_bar(s), 0, 2000000LL);
+      if (!ok || *abort_flag) {
+        // Copies already issued must land before this CTA gives its shared memory back (the closing barrier waits
+        // for threads, not for bulk copies).  Stage s was last filled in this round if s < stage, else in the round
+        // before (a stage never filled is "complete" at once: its barrier has not left phase 0).  In a pair every
+        // copy of both CTAs reports to the leader's barriers, so the leader waits for them; a barrier whose other
+        // half was never issued cannot complete, hence the bound.  Copies the leader cannot account for (the peer
+        // ran a few stages ahead of it) get a fixed settling time in both CTAs: a copy lands within microseconds.
+        if (!kPair || leader) {
+          for (int s = 0; s < S::kStages; ++s)
+            ptx::mbar_wait(full_bar(s), (s < stage) ? phase : (phase ^ 1u), kDrainCycles);
+        }
+        if constexpr (kPair) {
+          const long long t0 = clock64();
+          while (clock64() - t0 < kSettleCycles) {
+          }
+        }
       }
     }
   } else if (warp == 1) {
@@ -515,7 +538,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
           if (p.prof) prof_acc += clock64() - w0;
           if (!got_acc || *abort_flag) {
             report(p.status, kTimeoutMma);
-            *abort_flag = 1;
+            raise_abort();
             ok = false;
             break;
           }
@@ -527,7 +550,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
             if (p.prof) prof_ops += clock64() - w1;
             if (!got_ops || *abort_flag) {
               report(p.status, kTimeoutMma);
-              *abort_flag = 1;
+              raise_abort();
               ok = false;
               break;
             }
@@ -601,7 +624,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         if (!waited || *abort_flag) {
           if (lane == 0) {
             report(p.status, kTimeoutEpilogue);
-            *abort_flag = 1;
+            raise_abort();
           }
           return false;
         }

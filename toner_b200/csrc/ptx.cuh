@@ -125,6 +125,10 @@ __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Store one word into shared memory of a CTA of the cluster (address from mapa).
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t value) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(value) : "memory");
+}
 // Arrive on an mbarrier that may live in the peer CTA (address from mapa).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");

@@ -13,6 +13,15 @@ static thread_local std::string g_error;
 static std::mutex g_mutex;
 static Context g_ctx[16];
 
+// One cached operand description: where its tensor maps sit in the arena, and the upload that put them there.
+struct MapEntry {
+  int slot = 0;
+  cudaStream_t stream = nullptr;  // stream the upload was enqueued on
+  cudaEvent_t uploaded = nullptr; // recorded right after the upload
+  bool settled = false;           // the upload is known to have finished: no ordering needed any more
+};
+using MapCache = std::unordered_map<std::string, MapEntry>;
+
 static std::atomic<long long> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
@@ -68,7 +77,7 @@ Context* context() {
     set_error("could not allocate the tensor-map arena");
     return nullptr;
   }
-  c.map_cache = new std::unordered_map<std::string, int>();
+  c.map_cache = new MapCache();
   cudaFuncSetAttribute(gemm_tcgen05_kernel<256, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256>::kTotal);
   cudaFuncSetAttribute(gemm_tcgen05_kernel<256, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256>::kTotal);
   cudaFuncSetAttribute(gemm_tcgen05_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<128>::kTotal);
@@ -109,15 +118,29 @@ int get_maps(Context* ctx, const toner_operand& op, int batch, int box_rows, cud
     put(&op.base, sizeof(void*));
   }
   std::lock_guard<std::mutex> lock(g_mutex);
-  auto* cache = static_cast<std::unordered_map<std::string, int>*>(ctx->map_cache);
+  auto* cache = static_cast<MapCache*>(ctx->map_cache);
   auto it = cache->find(key);
   if (it != cache->end()) {
-    *out = ctx->arena_dev + it->second;
+    // The maps were uploaded by an asynchronous copy on the stream of the call that first used this operand.  A
+    // launch on that stream is ordered after the copy by the stream itself; a launch on any other stream waits for
+    // the copy's event (until the copy is known to be done, after which the entry needs no ordering at all).
+    MapEntry& e = it->second;
+    if (!e.settled) {
+      if (cudaEventQuery(e.uploaded) == cudaSuccess) {
+        e.settled = true;
+      } else {
+        (void)cudaGetLastError();  // cudaErrorNotReady is not an error here
+        if (e.stream != stream) TONER_CUDA(cudaStreamWaitEvent(stream, e.uploaded, 0));
+      }
+    }
+    *out = ctx->arena_dev + e.slot;
     return 0;
   }
   if (ctx->arena_used + count > ctx->arena_cap) {
     // Start over: wait for everything that may still read old maps, then reuse the arena from slot 0.
     TONER_CUDA(cudaDeviceSynchronize());
+    for (auto& kv : *cache)
+      if (kv.second.uploaded) cudaEventDestroy(kv.second.uploaded);
     cache->clear();
     ctx->arena_used = 0;
     if (count > ctx->arena_cap) return fail(kErrArg, "too many separately allocated operands in one call");
@@ -129,10 +152,15 @@ int get_maps(Context* ctx, const toner_operand& op, int batch, int box_rows, cud
     int rc = encode_one(ctx->arena_host + slot + i, base, op.rows, op.cols, op.ld, op.z_stride, op.list ? 1 : op.nz, brows);
     if (rc) return rc;
   }
+  MapEntry e;
+  e.slot = slot;
+  e.stream = stream;
+  TONER_CUDA(cudaEventCreateWithFlags(&e.uploaded, cudaEventDisableTiming));
   TONER_CUDA(cudaMemcpyAsync(ctx->arena_dev + slot, ctx->arena_host + slot, sizeof(CUtensorMap) * count,
                              cudaMemcpyHostToDevice, stream));
+  TONER_CUDA(cudaEventRecord(e.uploaded, stream));
   ctx->arena_used += count;
-  (*cache)[key] = slot;
+  (*cache)[key] = e;
   *out = ctx->arena_dev + slot;
   return 0;
 }
@@ -306,6 +334,14 @@ int toner_device_status(void* stream, int* status_out) {
   TONER_CUDA(cudaStreamSynchronize(s));
   if (v != 0) TONER_CUDA(cudaMemsetAsync(c->status_dev, 0, sizeof(int), s));
   *status_out = v;
+  return 0;
+}
+
+int toner_status_snapshot(int32_t* host_out, void* stream) {
+  toner::Context* c = toner::context();
+  if (!c) return toner::kErrCuda;
+  if (!host_out) return toner::fail(toner::kErrArg, "status_snapshot: host_out is null");
+  TONER_CUDA(cudaMemcpyAsync(host_out, c->status_dev, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
   return 0;
 }
 

@@ -40,7 +40,7 @@ struct Context {
   int arena_cap = 0, arena_used = 0;
   int* status_dev = nullptr;          // set by a kernel whose bounded wait ran out
   unsigned long long* prof_dev = nullptr;  // eight cycle counters, allocated when phase profiling is switched on
-  void* map_cache = nullptr;          // std::unordered_map<std::string, int>*
+  void* map_cache = nullptr;          // operand description -> arena slot and upload event (runtime.cu)
 };
 
 // Number of kernels this library has launched (all devices, all streams).

@@ -349,6 +349,7 @@ int toner_sumsq_static(const float* x, int32_t batch, int32_t rows, int32_t cols
                        void* stream) {
   using namespace toner;
   if (!x || !out || batch <= 0 || rows <= 0 || cols <= 0) return fail(kErrArg, "sumsq_static: bad arguments");
+  if (ld < cols) return fail(kErrArg, "sumsq_static: ld (elements between rows) must be at least cols");
   if (batch > kStaticSumsqMaxBatch)
     return fail(kErrArg, "sumsq_static: batch " + std::to_string(batch) + " exceeds the built-in scratch (" +
                              std::to_string(kStaticSumsqMaxBatch) + " matrices); use toner_sumsq with caller scratch");

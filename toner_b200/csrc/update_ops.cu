@@ -329,6 +329,7 @@ int toner_sumsq(const float* x, int32_t batch, int32_t rows, int32_t cols, int64
                 float* out, void* stream) {
   if (!context()) return kErrCuda;
   if (!x || !scratch || !out || batch <= 0 || rows <= 0 || cols <= 0) return fail(kErrArg, "sumsq: bad arguments");
+  if (ld < cols) return fail(kErrArg, "sumsq: ld (elements between rows) must be at least cols");
   return sumsq_det(x, batch, rows, cols, ld, bs, scratch, out, static_cast<cudaStream_t>(stream));
 }
 

@@ -332,8 +332,10 @@ class _FastToner(torch.optim.Optimizer):
         for p in self.param_groups[0]["params"]:
             if p.grad is None or p.grad.is_sparse:
                 raise RuntimeError("every projection weight needs a dense gradient (already synchronised across ranks)")
-        self._core.step()
-        self._microbatches = 0
+        try:
+            self._core.step()
+        finally:
+            self._microbatches = 0   # the captured rows were consumed by begin(), whether or not the step went through
 
     # ------------------------------------------------------------------ checkpoints
     def state_dict(self):

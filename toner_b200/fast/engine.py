@@ -214,6 +214,7 @@ class FastTonerCore:
             for g in self.groups.values():
                 g.plan_chunks(int(getattr(args, "stat_chunks", 4)) if world > 1 else 1)
         self.begun = False
+        self.health = ops.Health()   # the update phase's products: armed at the end of step(), read in the next one
         self._ev: Optional[List[torch.cuda.Event]] = None
         self._ev_last: Optional[List[torch.cuda.Event]] = None
         self.ev_done: Optional[torch.cuda.Event] = None
@@ -442,10 +443,14 @@ class FastTonerCore:
             self.begin()
         self.begun = False
         flagged = 0
-        with torch.cuda.stream(self.side):
-            for g in self.groups.values():
-                flagged += g.factors.finish()       # host waits for the convergence flags only
-        self.main_stream.wait_stream(self.side)
+        try:
+            with torch.cuda.stream(self.side):
+                for g in self.groups.values():
+                    flagged += g.factors.finish()       # host waits for the convergence flags only
+            # The previous step's update finished long before these flags arrived: its status costs no extra wait.
+            self.health.check()
+        finally:
+            self.main_stream.wait_stream(self.side)
         t1 = time.perf_counter()
         self.t += 1
         works = []
@@ -480,6 +485,7 @@ class FastTonerCore:
                     ops.apply_delta(info["all_ptrs"][r * per:(r + 1) * per], block)
         self._ev[5].record(self.main_stream)
         self._ev[3].record(self.main_stream)
+        self.health.arm("the previous step's update")
         self._ev_last = self._ev
         self.steps += 1
         self.timing.update(roots_host=t1 - t0, update_host=time.perf_counter() - t1)

@@ -26,13 +26,36 @@ from torch.optim import Optimizer
 from . import core, ops
 
 
-def _finite_number(name: str, value, *, lower: float = 0.0, upper: Optional[float] = None) -> None:
-    ok = isinstance(value, (int, float)) and math.isfinite(value) and value >= lower
-    if ok and upper is not None:
-        ok = value < upper
-    if not ok:
-        tail = f" and less than {upper}" if upper is not None else ""
-        raise ValueError(f"{name} must be finite, at least {lower}{tail}")
+# Hyper-parameter ranges: name -> (smallest allowed value, exclusive upper limit or None).  The limits and the
+# exception types are those of the reference's general optimizers (src/toner/reference.py:17-36,153-166,266-273);
+# the checks themselves are table-driven here.
+_RANGES = {
+    "lr": (0.0, None), "weight_decay": (0.0, None), "statistic_momentum": (0.0, 1.0), "damping": (1e-30, None),
+    "inner_strength": (0.0, None), "outer_strength": (0.0, None), "strength": (0.0, None), "momentum": (0.0, 1.0),
+    "ns_eps": (1e-30, None), "eps": (1e-30, None), "beta": (0.0, 1.0),
+}
+
+
+def _in_range(name: str, value, key: Optional[str] = None) -> None:
+    """ValueError unless `value` is a real, finite number inside the range registered under `key` (default: name)."""
+    low, high = _RANGES[key or name]
+    real = isinstance(value, (int, float)) and not isinstance(value, complex)
+    if real and math.isfinite(value) and value >= low and (high is None or value < high):
+        return
+    span = f"[{low}, {high})" if high is not None else f"[{low}, inf)"
+    raise ValueError(f"{name} = {value!r} is outside {span}")
+
+
+def _check_matrix(p: Tensor) -> None:
+    """What the CUDA path needs of a weight: a non-empty FP32 matrix on a CUDA device, dimensions multiples of 8."""
+    if p.ndim != 2 or p.numel() == 0:
+        raise ValueError("Toner expects nonempty 2-D matrix weights; optimize other parameters separately")
+    if p.dtype != torch.float32:
+        raise ValueError("Toner keeps FP32 master weights; use FP32 parameters")
+    if p.device.type != "cuda":
+        raise ValueError("toner_b200 runs on CUDA (sm_100a) only; move the parameters to the GPU")
+    if p.shape[0] % 8 or p.shape[1] % 8:
+        raise ValueError("toner_b200 needs matrix dimensions that are multiples of 8")
 
 
 class _Bucket:
@@ -47,34 +70,37 @@ class _Bucket:
         self.delta = torch.empty_like(self.group.m)
         self.index = {p: i for i, p in enumerate(params)}
 
+    def stacks(self) -> Dict[str, Tensor]:
+        """Per-parameter state keys of the reference (src/toner/reference.py:76-81,198-199,297-300) and the stacked
+        storage row i of which holds parameter i's value."""
+        out = {"input_ema": self.factors.ema}
+        if self.group.kind == "muont":
+            out["momentum_buffer"] = self.group.m
+        else:
+            out["exp_avg"], out["exp_avg_sq"] = self.group.m, self.group.v
+        return out
+
 
 class _TonerGeneral(Optimizer):
     """Statistic EMA, validation and bookkeeping common to MuonT and AdamT."""
 
     _kind = ""
+    _group_ranges: Tuple[str, ...] = ("lr", "weight_decay", "statistic_momentum", "damping")
 
     def __init__(self, params, defaults) -> None:
         super().__init__(params, defaults)
         self._scratch = core.Scratch()
         self._buckets: Optional[Dict[Tuple, _Bucket]] = None
         self._bucket_of: Dict[Tensor, Tuple[_Bucket, int]] = {}
+        self._health: Optional[ops.Health] = None   # the update kernels of the last step (created with the buckets)
 
     # ------------------------------------------------------------------ validation
     def _validate_common(self) -> None:
         for group in self.param_groups:
-            _finite_number("lr", group["lr"])
-            _finite_number("weight_decay", group["weight_decay"])
-            _finite_number("statistic_momentum", group["statistic_momentum"], upper=1)
-            _finite_number("damping", group["damping"], lower=1e-30)
+            for name in self._group_ranges:
+                _in_range(name, group[name])
             for p in group["params"]:
-                if p.ndim != 2 or p.numel() == 0:
-                    raise ValueError("Toner expects nonempty 2-D matrix weights; optimize other parameters separately")
-                if p.dtype != torch.float32:
-                    raise ValueError("Toner keeps FP32 master weights; use FP32 parameters")
-                if p.device.type != "cuda":
-                    raise ValueError("toner_b200 runs on CUDA (sm_100a) only; move the parameters to the GPU")
-                if p.shape[0] % 8 or p.shape[1] % 8:
-                    raise ValueError("toner_b200 needs matrix dimensions that are multiples of 8")
+                _check_matrix(p)
 
     def _strengths(self, group) -> Tuple[float, float]:
         raise NotImplementedError
@@ -84,9 +110,11 @@ class _TonerGeneral(Optimizer):
         self._buckets = None  # rebuilt lazily; optimizer state is kept in self.state
 
     def _build(self) -> None:
-        """Stack equally shaped parameters of each group (first use, or after add_param_group)."""
+        """Stack equally shaped parameters of each group (first use, after add_param_group or load_state_dict)."""
         old = self._bucket_of
         self._buckets, self._bucket_of = {}, {}
+        if self._health is None:
+            self._health = ops.Health()
         for gi, group in enumerate(self.param_groups):
             by_shape: Dict[Tuple[int, int], List[Tensor]] = {}
             for p in group["params"]:
@@ -99,19 +127,31 @@ class _TonerGeneral(Optimizer):
                 self._buckets[(gi, shape)] = bucket
                 for i, p in enumerate(ps):
                     self._bucket_of[p] = (bucket, i)
-                    if p in old:  # carry state over when the grouping is rebuilt
+                    if p in old:  # carry values over when the grouping is rebuilt
                         ob, oi = old[p]
-                        bucket.factors.ema[i].copy_(ob.factors.ema[oi])
-                        bucket.group.m[i].copy_(ob.group.m[oi])
-                        if bucket.group.v is not None:
-                            bucket.group.v[i].copy_(ob.group.v[oi])
-                    self._expose(p, bucket, i)
+                        for key, stack in bucket.stacks().items():
+                            stack[i].copy_(ob.stacks()[key][oi])
+                    self._adopt(p, bucket, i)
 
-    def _expose(self, p: Tensor, bucket: _Bucket, i: int) -> None:
-        """Keep the reference's per-parameter state keys as views of the stacked storage."""
+    def _adopt(self, p: Tensor, bucket: _Bucket, i: int) -> None:
+        """Make the reference's per-parameter state keys views of the stacked storage.  A tensor that is already in
+        the state but lives elsewhere -- loaded from a checkpoint -- is copied into its row first, so its value is
+        the one the kernels read."""
         state = self.state[p]
-        if "input_ema" in state:
-            state["input_ema"] = bucket.factors.ema[i]
+        for key, stack in bucket.stacks().items():
+            if key not in state:
+                continue
+            held, row = state[key], stack[i]
+            if held.data_ptr() != row.data_ptr():
+                row.copy_(held.to(device=row.device, dtype=row.dtype))
+            state[key] = row
+
+    def load_state_dict(self, state_dict) -> None:
+        """torch's loader puts fresh tensors into ``self.state``; the stacks the kernels read are rebuilt from them
+        at the next use (the factors are recomputed, so the first step after a resume runs the Newton schedule of
+        the bound that always holds)."""
+        super().load_state_dict(state_dict)
+        self._buckets, self._bucket_of = None, {}
 
     def _ensure_built(self) -> None:
         if self._buckets is None:
@@ -126,11 +166,11 @@ class _TonerGeneral(Optimizer):
         The whole mapping is validated before any state changes; calling twice without ``step()`` is an
         error (src/toner/reference.py:51-81)."""
         self._ensure_built()
-        groups = {p: g for g in self.param_groups for p in g["params"]}
-        for p, cov in second_moments.items():
-            if p not in groups:
+        owner = {p: g for g in self.param_groups for p in g["params"]}
+        for p, cov in second_moments.items():   # nothing is touched until every entry has passed
+            if p not in owner:
                 raise ValueError("Received a statistic for a parameter not owned by this optimizer")
-            if cov.shape != (p.shape[1], p.shape[1]):
+            if tuple(cov.shape) != (p.shape[1], p.shape[1]):
                 raise ValueError("Statistic shape must match the matrix weight's input dimension")
             if cov.device != p.device:
                 raise ValueError("Input statistics and matrix weights must be on the same device")
@@ -140,7 +180,7 @@ class _TonerGeneral(Optimizer):
                 raise RuntimeError("Statistics already updated; aggregate microbatches before update_statistics()")
         for p, cov in second_moments.items():
             bucket, i = self._bucket_of[p]
-            state, beta = self.state[p], groups[p]["statistic_momentum"]
+            state, beta = self.state[p], owner[p]["statistic_momentum"]
             if "input_ema" not in state:
                 bucket.factors.ema[i].zero_()
                 state["input_ema"] = bucket.factors.ema[i]
@@ -179,6 +219,15 @@ class _TonerGeneral(Optimizer):
                                    "gradients, or put the ones without into a separate parameter group")
             yield group, bucket
 
+    def _factor_all(self, work) -> None:
+        """Factors of every active bucket: enqueue all, then wait for their flags (and for the status of the previous
+        step's update kernels, which finished before them)."""
+        for _, bucket in work:
+            bucket.factors.compute()
+        for _, bucket in work:
+            bucket.factors.finish()
+        self._health.check()
+
     @property
     def fallbacks(self) -> int:
         """Statistics whose Newton factors were flagged and recomputed by eigendecomposition so far."""
@@ -215,24 +264,17 @@ class MuonT(_TonerGeneral):
 
     def _validate_muon(self) -> None:
         for group in self.param_groups:
-            for name in ("inner_strength", "outer_strength"):
-                _finite_number(name, group[name])
+            for name in ("inner_strength", "outer_strength", "momentum", "ns_eps"):
+                _in_range(name, group[name])
             core.root_orders(*self._strengths(group))
             if group["outer_strength"] == 0:
                 raise ValueError("outer_strength 0 is not supported by the CUDA path")
-            _finite_number("momentum", group["momentum"], upper=1)
-            _finite_number("ns_eps", group["ns_eps"], lower=1e-30)
             if group["ns_mode"] not in {"tpu", "f32", "bf16"}:
                 raise ValueError("ns_mode must be 'tpu', 'f32', or 'bf16'")
             if group["ns_mode"] != "tpu":
                 raise ValueError("toner_b200 implements ns_mode='tpu' (BF16 operands, FP32 accumulation) only")
             if not isinstance(group["ns_steps"], int) or isinstance(group["ns_steps"], bool) or group["ns_steps"] < 1:
                 raise ValueError("ns_steps must be a positive integer")
-
-    def _expose(self, p, bucket, i) -> None:
-        super()._expose(p, bucket, i)
-        if "momentum_buffer" in self.state[p]:
-            self.state[p]["momentum_buffer"] = bucket.group.m[i]
 
     @torch.no_grad()
     def step(self, closure: Optional[Callable] = None):
@@ -244,10 +286,8 @@ class MuonT(_TonerGeneral):
         self._check_step()
         self._validate_muon()
         work = list(self._active_buckets())
-        for _, bucket in work:
-            bucket.factors.compute()
+        self._factor_all(work)
         for group, bucket in work:
-            bucket.factors.finish()
             grads = [p.grad for p in bucket.params]
             core.muont_group_delta(bucket.group, grads, bucket.delta, self._scratch, lr=group["lr"],
                                    weight_decay=group["weight_decay"], momentum=group["momentum"],
@@ -255,6 +295,8 @@ class MuonT(_TonerGeneral):
             core.apply_group_delta(bucket.group, bucket.delta)
             for i, p in enumerate(bucket.params):
                 self.state[p]["momentum_buffer"] = bucket.group.m[i]
+        if work:
+            self._health.arm("the previous step's update")
         self._consume_statistics()
         return loss
 
@@ -287,21 +329,15 @@ class AdamT(_TonerGeneral):
 
     def _validate_adam(self) -> None:
         for group in self.param_groups:
-            _finite_number("strength", group["strength"])
+            _in_range("strength", group["strength"])
             core.root_orders(*self._strengths(group))
             if group["strength"] == 0:
                 raise ValueError("strength 0 is not supported by the CUDA path")
-            _finite_number("eps", group["eps"], lower=1e-30)
+            _in_range("eps", group["eps"])
             if len(group["betas"]) != 2:
                 raise ValueError("betas must contain two coefficients")
-            for beta in group["betas"]:
-                _finite_number("beta", beta, upper=1)
-
-    def _expose(self, p, bucket, i) -> None:
-        super()._expose(p, bucket, i)
-        if "exp_avg" in self.state[p]:
-            self.state[p]["exp_avg"] = bucket.group.m[i]
-            self.state[p]["exp_avg_sq"] = bucket.group.v[i]
+            for j, beta in enumerate(group["betas"]):
+                _in_range(f"betas[{j}]", beta, key="beta")
 
     @torch.no_grad()
     def step(self, closure: Optional[Callable] = None):
@@ -313,10 +349,8 @@ class AdamT(_TonerGeneral):
         self._check_step()
         self._validate_adam()
         work = list(self._active_buckets())
-        for _, bucket in work:
-            bucket.factors.compute()
+        self._factor_all(work)
         for group, bucket in work:
-            bucket.factors.finish()
             steps = {self.state[p].get("step", 0) for p in bucket.params}
             if len(steps) != 1:
                 raise RuntimeError("parameters stacked together must have taken the same number of steps")
@@ -329,5 +363,7 @@ class AdamT(_TonerGeneral):
                 st = self.state[p]
                 st["step"] = t
                 st["exp_avg"], st["exp_avg_sq"] = bucket.group.m[i], bucket.group.v[i]
+        if work:
+            self._health.arm("the previous step's update")
         self._consume_statistics()
         return loss

@@ -60,6 +60,38 @@ def assert_healthy() -> None:
         raise _lib.TonerError(f"a CUDA kernel gave up a bounded wait (status {code})")
 
 
+class Health:
+    """The kernels' status word, read without a synchronisation of its own.
+
+    ``arm()`` enqueues a copy of the word into pinned host memory on the current stream and records an event;
+    ``check()`` waits for that event (the callers place it where they wait for the stream anyway) and raises
+    TonerError if a kernel had given up a bounded wait by then: a product that gave up has written only part of
+    its result.  The word is cleared when the error is raised, so the optimizer can be used again."""
+
+    def __init__(self) -> None:
+        self._host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._event: Optional[torch.cuda.Event] = None
+        self._what = ""
+
+    def arm(self, what: str) -> None:
+        check(_lib.load().toner_status_snapshot(self._host.data_ptr(), _stream()), "toner_status_snapshot")
+        self._event = torch.cuda.Event()
+        self._event.record(torch.cuda.current_stream())
+        self._what = what
+
+    def check(self) -> None:
+        if self._event is None:
+            return
+        self._event.synchronize()
+        self._event = None
+        code = int(self._host[0])
+        if code:
+            self._host.zero_()
+            device_status()   # clears the word on the device
+            raise _lib.TonerError(f"a CUDA kernel gave up a bounded wait (status {code}) during {self._what}: "
+                                  "its results are incomplete and were not applied")
+
+
 def gemm_phase_cycles(enable: bool):
     """Read and clear the GEMM kernels' phase cycle counters, then switch the counting on or off
     (toner_gemm_phase_cycles).  Returns a dict of per-CTA averages, or None if nothing was counted."""
