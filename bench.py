@@ -248,6 +248,7 @@ def run_ours(args) -> None:
         e2e_ms = timed(e2e_step, max(1, min(args.steps, 3)))
         ops.assert_healthy()
 
+    check = check_results(core, world, dev)
     if rank == 0:
         pk = peaks()
         # products per statistic: X T and T^2 T^4 T^8 T^8 M per Newton step (no X product in the first, no M update
@@ -305,13 +306,53 @@ def run_ours(args) -> None:
             "phases": per_phase,
             "algorithmic_flops": fl,
             "fallbacks": core.fallbacks,
+            "check": check,
         }
+        mhz = line["clocks"]["sm_mhz"]
+        if mhz:   # time x clock: comparable between runs whose power-capped clocks differ
+            line["mhz_ms"] = round(ms * mhz, 1)
+            for ph in per_phase.values():
+                ph["mhz_ms"] = round(ph["ms"] * mhz, 1)
         if not args.no_cpu and world == 1:
             line["cpu_baseline"] = cpu_baseline(args, sample_rows=2048)
         print(json.dumps(line), flush=True)
     opt.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def check_results(core, world: int, dev) -> dict:
+    """Results, not timings: (1) every rank must hold bit-identical weights after the exchange (FP64 sums of every
+    matrix and of its square, compared through MIN / MAX all-reduces); (2) on every rank the factors of one owned
+    hidden-width statistic -- they went through SYRK, reduce-scatter, EMA and the Newton engine -- against an FP64
+    eigendecomposition of that rank's EMA on the host (src/toner/linalg.py:54-89 in double precision), worst rank
+    reported.  Runs after the timed regions."""
+    import torch.distributed as dist
+    sums = torch.stack([torch.stack([p.detach().double().sum(), p.detach().double().square().sum()]) for p in core.params])
+    agree = True
+    if world > 1:
+        lo, hi = sums.clone(), sums.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        agree = bool(torch.equal(lo, hi))
+    f = core.groups["d"].factors
+    torch.cuda.synchronize()
+    c = f.ema[0].double().cpu()
+    lam, vec = torch.linalg.eigh(0.5 * (c + c.T))
+    lam = lam.clamp_min(0)
+    unit = lam / lam.mean().clamp_min(1e-30) + f.damping
+    errs = []
+    for root, power in ((f.root_lo, 1.0 / f.p), (f.root_hi, float(f.q) / f.p)):
+        if root is None:
+            continue
+        want = (vec * unit.pow(-power)) @ vec.T
+        errs.append(float((root[0].double().cpu() - want).norm() / want.norm()))
+    err = torch.tensor([max(errs)], device=dev)
+    if world > 1:
+        dist.all_reduce(err, op=dist.ReduceOp.MAX)
+    finite = bool(torch.isfinite(sums).all())
+    return {"ranks_agree": agree, "weights_finite": finite, "factor_err": float(f"{float(err.item()):.3e}"),
+            "factor_err_bound": 2e-3, "ok": bool(agree and finite and float(err.item()) <= 2e-3)}
 
 
 def cpu_baseline(args, sample_rows: int = 2048):

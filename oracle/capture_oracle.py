@@ -7,10 +7,11 @@ in plain torch on CPU:
   * RMSNorm rows          bf16(x rsqrt(mean x^2 + eps)) then bf16(w) * that, rounded to BF16      (ops.py:63-79)
                           -- the arithmetic of the model's own norm(), reproduce/marin/model.py:10-15
   * SiLU-gated rows       bf16(g (1 / (1 + exp(-g))) u), FP32 arithmetic and one rounding          (ops.py:82-100)
-Pinned against the reference where it runs on CPU: the gathered and RMSNorm rows are checked against the model's
-norm() and plain indexing (tests/golden/capture.npz, made by tests/golden/make_capture_golden.py).  The SiLU-gated
-rows are PARITY UNPINNED: the reference computes them only in a Triton kernel, which cannot run without a GPU here;
-the formula above is restated from that kernel's source.
+Pinned against the reference: the gathered and RMSNorm rows against the model's norm() and plain indexing on CPU
+(tests/golden/capture.npz, made by tests/golden/make_capture_golden.py), and all four kinds of rows -- the SiLU-gated
+ones exist only as a Triton kernel -- against capture_recomputed itself, run on a B200
+(tests/golden/capture_recomputed.npz, made by tests/golden/make_tpu_golden.py): SiLU-gated and copied rows bit for bit,
+RMSNorm rows within one BF16 unit in the last place.
 """
 
 from __future__ import annotations

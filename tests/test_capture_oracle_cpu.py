@@ -47,6 +47,29 @@ def test_recomputed_capture_fills_the_four_buffers_of_each_layer():
     assert (bufs[3].float() - want).abs().max() <= 2.0 ** -8 * want.abs().max()   # one BF16 rounding of the FP32 value
 
 
+def test_recomputed_rows_against_the_references_triton_kernels():
+    """capture_recomputed of the reference (reproduce/marin/ops.py:107-163) run on a B200 by
+    tests/golden/make_tpu_golden.py: two layers, hidden 64, gated width 160.  The SiLU-gated and copied rows agree
+    bit for bit; the RMSNorm rows within one BF16 unit in the last place on a few elements in ten thousand (the
+    kernel's mean square is summed in another order)."""
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "capture_recomputed.npz"))
+    batch, seq, hidden, mlp, layers = (int(v) for v in g["dims"])
+    idx, eps = torch.from_numpy(g["idx"]), float(g["eps"])
+
+    def b16(name):
+        return torch.from_numpy(g[name].copy()).view(torch.bfloat16)
+
+    for l in range(layers):
+        norm1 = cap.norm_rows(b16(f"x{l}"), torch.from_numpy(g[f"w1{l}"]), idx, eps)
+        norm2 = cap.norm_rows(b16(f"xmid{l}"), torch.from_numpy(g[f"w2{l}"]), idx, eps)
+        for got, want in ((norm1, b16(f"rows_attn{l}")), (norm2, b16(f"rows_mlp{l}"))):
+            ulps = cap.bf16_ulps(got.contiguous(), want)
+            assert int(ulps.max()) <= 1 and float((ulps > 0).float().mean()) < 2e-3
+        assert torch.equal(b16(f"attn{l}")[:, idx].reshape(-1, hidden), b16(f"rows_o{l}"))
+        gated = cap.silu_mul_rows(b16(f"g{l}"), b16(f"u{l}"), idx)
+        assert torch.equal(gated.view(torch.int16), b16(f"rows_down{l}").view(torch.int16))
+
+
 def test_ulps_helper():
     a = torch.tensor([1.0, -1.0, 0.0], dtype=torch.bfloat16)
     b = torch.tensor([1.0078125, -1.0078125, 0.0], dtype=torch.bfloat16)
