@@ -205,7 +205,7 @@ int toner_split16(const float* x, const float* const* x_list, int32_t batch, int
  * its arguments (8 for p = 8, 8 for p = 4, 10 for p = 2 at n = 5632, damping 1e-3): the count with the fewest
  * plane passes, Newton steps and series together.
  * status[b] (DEVICE, optional): 0 converged, 1 residual max|I - M| above 0.5 before the last step,
- * 2 non-finite.  The caller decides what to do with a non-zero status (the Python host recomputes that
+ * 2 non-finite, 3 / 4 a caller's spectrum bound that did not hold (toner_inv_roots_ex / _tracked).  The caller decides what to do with a non-zero status (the Python host recomputes that
  * statistic with an eigendecomposition, as the reference's fallback does, src/toner/fast/engine.py:714-731).
  * Workspace: toner_inv_roots_workspace_bytes(chunk, n) lets `chunk` statistics be processed at once; a
  * smaller workspace makes the call loop over chunks (it must hold at least one statistic). */
@@ -222,10 +222,10 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
  *             damping / (n (1 + damping)) that always holds).  A larger bound means fewer Newton steps
  *             (toner_inv_roots_iterations_for).  The bound is checked on the device: status[b] = 3 where
  *             damping / norm_out[b] lies below it, and the caller recomputes that statistic.
- *   norm_out  (DEVICE, optional, k floats) the bound of lambda_max(A'_b) the engine normalised by: the smaller of ||A'||_F
- *             and 1.04 ||A'||_F ||P^2||_F^(1/2) with P = A' / ||A'||_F (one extra single-pass product; (sum lambda^4)^(1/4)
- *             bounds lambda_max far more tightly than the Frobenius norm when the spectrum is flat).  The caller derives
- *             next step's bound from it: lower = margin * damping / max_b norm_out[b].
+ *   norm_out  (DEVICE, optional, k floats) the bound of lambda_max(A'_b) the engine normalised by: the smallest of ||A'||_F
+ *             and 1.03 ||A'||_F ||P^(2^j)||_F^(1/2^j), j = 1, 2, 3, with P = A' / ||A'||_F (three extra single-pass
+ *             products; (sum lambda^16)^(1/16) bounds lambda_max far more tightly than the Frobenius norm when the spectrum
+ *             is flat).  The caller derives next step's bound from it: lower = margin * damping / max_b norm_out[b].
  * A' is A with its dominant eigen-direction deflated: six power-iteration steps find (lambda_1, v); where they
  * converged (residual below 1e-5) and lambda_1 stands above 8x the mean of the rest, the engine factors
  * A' = A - (lambda_1 - c) v v^T and adds (lambda_1^(-1/p) - c^(-1/p)) v v^T back to the root.  This is what the
@@ -234,6 +234,31 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
 int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
                        float lower, float* root_lo, float* root_hi, float* fro2_lo, int32_t* status, float* norm_out,
                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* The same for a caller that factors the same slowly changing statistics step after step and wants the schedule to
+ * follow the actual spectrum instead of the bound damping / norm that always holds (the reference's engine exploits
+ * the same slowness with a cached eigenbasis and two warm iterations, src/toner/fast/engine.py:504-553):
+ *   track          (DEVICE, k * n floats, kept by the caller between calls) for each statistic a unit vector along the
+ *                  eigenvector of the smallest eigenvalue of A.  After the roots are computed the call advances it by
+ *                  `track_sweeps` power-iteration steps on the highest inverse power (A^(-q/p)), where that eigenvalue
+ *                  is the dominant one however small it is next to lambda_max(A); track_sweeps + 256 starts from a
+ *                  fixed vector instead of the buffer's content (first call, or after the statistics were replaced).
+ *   lmin_out       (DEVICE, optional, k floats) the estimate of lambda_min(A_b) that comes with it: a Rayleigh quotient,
+ *                  so it errs on the high side (by 5-25 % after 8 sweeps from scratch, less once tracking).
+ *   lower, lower_is_estimate
+ *                  with lower_is_estimate = 1, `lower` is the caller's ESTIMATE of the lower end of the spectrum of
+ *                  A' / norm, typically margin * min_b lmin_out[b] / norm_out[b] of the previous call.  Such a bound
+ *                  cannot be checked in advance; it is verified after the chain: four power-iteration steps on
+ *                  R = I - M of the last M, from the tracked direction, estimate ||R||_2, and status[b] = 4 where that
+ *                  exceeds what the finishing series was cut for (by 15 % + 1e-3).  The caller recomputes such a
+ *                  statistic with the bound that always holds.  resid_out (DEVICE, optional, k floats) receives the
+ *                  estimate.  With lower_is_estimate = 0 the call is toner_inv_roots_ex (plus tracking).
+ * The upper end needs no estimate: norm_out is a certified bound, the smallest of ||A'||_F times ||P^2||_F^(1/2),
+ * ||P^4||_F^(1/4), ||P^8||_F^(1/8) (three single-pass squarings). */
+int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
+                            float lower, int32_t lower_is_estimate, float* root_lo, float* root_hi, float* fro2_lo,
+                            int32_t* status, float* norm_out, float* track, float* lmin_out, float* resid_out,
+                            int32_t track_sweeps, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------ Newton-Schulz polar iteration
  * x = u / (||u||_F + eps); `steps` times  A = x x^T (on the short side),  x <- a x + (b A + c A A) x  with

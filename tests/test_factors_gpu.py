@@ -217,3 +217,116 @@ def test_non_finite_statistic_is_flagged_and_does_not_touch_its_neighbours(ops):
     ops.assert_healthy()                       # no bounded wait ran out: the kernels finished normally
     assert status.tolist() == [2, 0, 2]
     assert torch.equal(lo[1], alone)
+
+
+def _activation_like(n, rows, seed, k=3):
+    """Statistics of well-conditioned rows (unit noise plus a shared mean direction), as the benchmark's."""
+    from toner_b200.synthetic import fill_rows
+    from toner_b200 import ops as _ops
+    buf = torch.empty(k, rows, n, device="cuda", dtype=torch.bfloat16)
+    fill_rows(buf, seed=seed)
+    ema = torch.zeros(k, n, n, device="cuda")
+    _ops.syrk_upper(buf, ema, _ops.EMA_FULL, 0.0, 1.0 / rows)
+    return ema
+
+
+def _extremes(c, damping=DAMPING):
+    """Smallest eigenvalue of A = sym(C) / mean diag + damping I, and the largest once the top one is set aside."""
+    c = c.double().cpu()
+    lam = torch.linalg.eigvalsh(0.5 * (c + c.T)).clamp_min(0)
+    lam = lam / lam.mean() + damping
+    return float(lam[0]), float(lam[-2])
+
+
+def test_tracked_spectrum_estimate_saves_steps(ops):
+    """toner_inv_roots_tracked on well-conditioned statistics: the first call reports an estimate of lambda_min(A)
+    (a little high, as a Rayleigh quotient is) and a certified bound of lambda_max(A'); the second call, scheduled for
+    half the ratio of the two, takes fewer than half the plane passes and returns the same roots, verified."""
+    n = 512
+    ema = _activation_like(n, 8192, seed=3)
+    k = ema.shape[0]
+    norms, lmin, track = torch.zeros(k, device="cuda"), torch.zeros(k, device="cuda"), torch.zeros(k, n, device="cuda")
+    lo0, hi0, _, st0 = ops.inv_roots(ema, DAMPING, 8, 4, norms=norms, track=track, lmin=lmin, track_sweeps=12,
+                                     track_restart=True)
+    ops.assert_healthy()
+    assert st0.tolist() == [0] * k
+    for b in range(k):
+        true_min, true_max = _extremes(ema[b])
+        assert 0.98 * true_min < lmin[b].item() < 1.4 * true_min, (lmin[b].item(), true_min)
+        assert true_max < norms[b].item() < 2.5 * true_max, (norms[b].item(), true_max)   # certified, and tight
+    assert abs(track.norm(dim=1) - 1).max().item() < 1e-4
+    lower = 0.5 * float((lmin / norms).min())
+    cold, warm = ops.inv_roots_iterations(n, DAMPING, 8), ops.inv_roots_iterations_for(lower, 8)
+    assert warm <= 3 < cold, (warm, cold)
+    resid = torch.zeros(k, device="cuda")
+    lo1, hi1, _, st1 = ops.inv_roots(ema, DAMPING, 8, 4, lower=lower, lower_is_estimate=True, track=track, lmin=lmin,
+                                     resid=resid, track_sweeps=4)
+    ops.assert_healthy()
+    assert st1.tolist() == [0] * k
+    e_assumed = 1.0    # the verified distance of the last M from the identity stays inside what the schedule assumed
+    assert 0 <= resid.min().item() and resid.max().item() < e_assumed
+    for b in range(k):
+        c = ema[b].cpu()
+        assert orc.rel_fro(lo1[b].cpu(), orc.inverse_root_truth(c, 0.125, DAMPING)) < 5e-5
+        assert orc.rel_fro(hi1[b].cpu(), orc.inverse_root_truth(c, 0.5, DAMPING)) < 2e-4
+        assert orc.rel_fro(lo1[b].cpu(), lo0[b].cpu()) < 5e-5
+
+
+def test_an_estimate_that_is_too_high_is_caught_after_the_chain(ops):
+    """A caller's estimate above the true lower end of the spectrum cannot be checked before the chain has run; the
+    verification afterwards (power iteration on I - M) must flag it: status 4, and only where it does not hold."""
+    n = 512
+    benign = _activation_like(n, 8192, seed=4, k=2)
+    harder = spd(n, 300.0, 9).cuda().unsqueeze(0)          # smallest eigenvalue 300 times below the largest
+    ema = torch.cat([benign, harder])
+    k = ema.shape[0]
+    norms, lmin, track = torch.zeros(k, device="cuda"), torch.zeros(k, device="cuda"), torch.zeros(k, n, device="cuda")
+    ops.inv_roots(ema, DAMPING, 8, 4, norms=norms, track=track, lmin=lmin, track_sweeps=12, track_restart=True)
+    ratio = (lmin / norms).tolist()
+    assert ratio[2] < 0.1 * min(ratio[:2])
+    lower = 0.5 * min(ratio[:2])                            # right for the first two statistics, far too high for the third
+    _, _, _, st = ops.inv_roots(ema, DAMPING, 8, 4, lower=lower, lower_is_estimate=True, track=track, lmin=lmin,
+                                track_sweeps=4)
+    ops.assert_healthy()
+    # (4: caught by the verification; 1: so far off that the last M already fails the convergence test)
+    assert st.tolist()[:2] == [0, 0] and st.tolist()[2] in (1, 4)
+    milder = 3.0 * ratio[2]                                 # three times too high for the third statistic only
+    _, _, _, st = ops.inv_roots(ema, DAMPING, 8, 4, lower=milder, lower_is_estimate=True, track=track, lmin=lmin,
+                                track_sweeps=4)
+    assert st.tolist()[:2] == [0, 0] and st.tolist()[2] in (1, 4)
+    with pytest.raises(Exception):                          # an estimate needs the tracked vectors to be verified
+        ops.inv_roots(ema, DAMPING, 8, 4, lower=lower, lower_is_estimate=True)
+
+
+def test_fifty_steps_on_a_drifting_statistic(ops):
+    """FactorSet on an EMA (decay 0.95) fed fresh rows every step: after the first step the schedule follows the tracked
+    spectrum (fewer Newton steps than the bound that always holds needs), no statistic is ever flagged, and the factors
+    stay as close to the exact ones as those of a cold factorisation of the same statistic."""
+    from toner_b200 import core
+    from toner_b200.synthetic import fill_rows
+    n, rows, k = 512, 4096, 2
+    dev = torch.device("cuda")
+    warm = core.FactorSet(k, n, dev, (0.5, 0.125), DAMPING)
+    buf = torch.empty(k, rows, n, device="cuda", dtype=torch.bfloat16)
+    counts, worst_ratio = [], 0.0
+    for step in range(50):
+        fill_rows(buf, seed=100 + step, mean_seed=7)
+        ops.syrk_upper(buf, warm.ema, ops.EMA_FULL, 0.95 if step else 0.0, (0.05 if step else 1.0) / rows)
+        warm.compute()
+        counts.append(warm.iterations)
+        assert warm.finish() == 0
+        if step % 7 == 0 or step == 49:
+            cold_lo, cold_hi, _, st = ops.inv_roots(warm.ema, DAMPING, 8, 4)
+            assert st.tolist() == [0] * k
+            for b in range(k):
+                c = warm.ema[b].cpu()
+                for got, ref, s in ((warm.root_lo[b], cold_lo[b], 0.125), (warm.root_hi[b], cold_hi[b], 0.5)):
+                    truth = orc.inverse_root_truth(c, s, DAMPING)
+                    e_warm, e_cold = orc.rel_fro(got.cpu(), truth), orc.rel_fro(ref.cpu(), truth)
+                    worst_ratio = max(worst_ratio, e_warm / max(e_cold, 2e-5))
+                    assert e_warm < 2e-4, (step, b, s, e_warm)
+    assert warm.repairs == 0 and warm.fallbacks == 0 and warm.bound_failures == 0
+    assert counts[0] == ops.inv_roots_iterations(n, DAMPING, 8) and max(counts[2:]) <= 3, counts
+    assert worst_ratio < 2.0, worst_ratio
+    print(f"Newton steps per factorisation over 50 steps: first {counts[0]}, then {sorted(set(counts[1:]))}; "
+          f"warm / cold error ratio at most {worst_ratio:.2f}")

@@ -78,6 +78,8 @@ SIGNATURES = {
     "toner_inv_roots_iterations_for": (C.c_int, [_f32, _i32]),
     "toner_inv_roots_finish_order_for": (C.c_int, [_f32, _i32, _i32]),
     "toner_inv_roots_ex": (C.c_int, [_vp, _i32, _i32, _f32, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "toner_inv_roots_tracked": (C.c_int, [_vp, _i32, _i32, _f32, _i32, _i32, _i32, _f32, _i32, _vp, _vp, _vp, _vp, _vp, _vp,
+                                          _vp, _vp, _i32, _vp, _sz, _vp]),
     "toner_ns_polar_workspace_bytes": (C.c_size_t, [_i32, _i32, _i32]),
     "toner_ns_polar": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _sz, _vp]),
     "toner_sumsq_scratch_bytes": (C.c_size_t, [_i32]),

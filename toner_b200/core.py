@@ -94,6 +94,17 @@ class FactorSet:
         self.norms = torch.zeros(k, device=device, dtype=torch.float32)
         self.norms_host = torch.zeros(k, dtype=torch.float32).pin_memory()
         self.lower = 0.0
+        # Tracking of each statistic's smallest eigenvalue (toner_inv_roots_tracked): with it the next step's Newton
+        # schedule starts from an estimate of the actual spectrum (verified after the chain) instead of the bound
+        # damping / norm, which is far too pessimistic for well-conditioned statistics.
+        self.tracking = True
+        self.track = torch.zeros(k, n, device=device, dtype=torch.float32)
+        self.lmin = torch.zeros(k, device=device, dtype=torch.float32)
+        self.lmin_host = torch.zeros(k, dtype=torch.float32).pin_memory()
+        self.track_restart = True        # the vectors hold nothing yet (or the statistics were replaced)
+        self.lower_is_estimate = False
+        self.estimate_backoff = 0        # steps left during which only certified bounds are used (after a bound failed)
+        self.bound_failures = 0
         self.status_event: Optional[torch.cuda.Event] = None
         self.health = ops.Health()
         self.lo_planes = torch.empty(2, k, n, n, device=device, dtype=torch.float16)
@@ -143,16 +154,26 @@ class FactorSet:
             return
         ops.inv_roots(self.ema, self.damping, self.p, self.q, root_lo=self.root_lo, root_hi=self.root_hi,
                       fro2_lo=self.fro2_lo, status=self.status, workspace=self.workspace, lower=self.lower,
-                      norms=self.norms)
+                      norms=self.norms, lower_is_estimate=self.lower_is_estimate,
+                      track=self.track if self.tracking else None, lmin=self.lmin if self.tracking else None,
+                      track_sweeps=(12 if self.track_restart else 4) if self.tracking else 0,
+                      track_restart=self.track_restart)
+        self.track_restart = False
+        self._estimate_in_flight = self.lower_is_estimate
         self.iterations = (ops.inv_roots_iterations_for(self.lower, self.p) if self.lower > 0
                            else ops.inv_roots_iterations(self.n, self.damping, self.p))
         self.finish_order = ops.inv_roots_finish_order(self.n, self.damping, self.p, self.lower)
         self._split()
         self.status_host.copy_(self.status, non_blocking=True)
         self.norms_host.copy_(self.norms, non_blocking=True)
+        self.lmin_host.copy_(self.lmin, non_blocking=True)
         self.health.arm("the factor computation")
         self.status_event = torch.cuda.Event()
         self.status_event.record(torch.cuda.current_stream())
+
+    def statistics_replaced(self) -> None:
+        """The EMAs were overwritten from outside (a checkpoint): nothing learnt from earlier factorisations applies."""
+        self.lower, self.lower_is_estimate, self.track_restart, self.estimate_backoff = 0.0, False, True, 0
 
     def _split(self) -> None:
         tmp = self.scratch.get("split_max", (self.k,), torch.int32, self.device)
@@ -170,17 +191,31 @@ class FactorSet:
         self.status_event.synchronize()
         self.status_event = None
         self.health.check()   # a product of the factor engine that gave up a wait: raise before the factors are used
-        bad = [i for i, s in enumerate(self.status_host.tolist()) if s != 0]
-        # Next step's bound: damping / ||A'||_F of the widest statistic, with room for one step of EMA drift.
-        # A flagged statistic (not converged, or below the bound used) sends the next step back to the bound
-        # that always holds.
+        codes = self.status_host.tolist()
+        bad = [i for i, s in enumerate(codes) if s != 0]
+        # Next step's bound.  Certified: damping / norm of the widest statistic, with room for one step of EMA drift.
+        # Estimated (tracking): the smallest eigenvalue found in this step's roots over the norm, halved -- the
+        # estimate errs high by up to a quarter, the statistic moves by a few percent per step -- and used only where it
+        # buys a step.  A flagged statistic (not converged, or below the bound used) sends the next step back to the
+        # bound that always holds; an estimate that failed its verification is not tried again for eight steps.
         top = float(self.norms_host.max())
         worst = self.damping / (self.n * (1.0 + self.damping))
-        self.lower = 0.0
-        if not bad and math.isfinite(top) and top > 0:
+        self.lower, self.lower_is_estimate = 0.0, False
+        if getattr(self, "_estimate_in_flight", False) and any(c in (1, 4) for c in codes):
+            self.estimate_backoff = 8     # (a gross overestimate already fails the convergence test, status 1)
+            self.bound_failures += 1
+        elif self.estimate_backoff:
+            self.estimate_backoff -= 1
+        if all(c in (0, 4) or (c == 1 and getattr(self, "_estimate_in_flight", False)) for c in codes) \
+                and math.isfinite(top) and top > 0:
             hint = 0.6 * self.damping / top
             if worst < hint < 1.0:
                 self.lower = hint
+            if self.tracking and not self.estimate_backoff and not bad:
+                ratio = float((self.lmin_host / self.norms_host).min())
+                guess = min(0.5 * ratio, 0.8)
+                if math.isfinite(guess) and guess > 1.5 * max(self.lower, worst):
+                    self.lower, self.lower_is_estimate = guess, True
         if not bad:
             return 0
         # Repair round (the reference's engine repairs flagged roots before it falls back,

@@ -353,13 +353,84 @@ __global__ void __launch_bounds__(256) rank1_update_kernel(float* __restrict__ a
   }
 }
 
-// bound^2 <- bound^2 * min(1, 1.04 * sqrt(||P^2||_F^2)): the normalisation moves from ||A'||_F to the tighter
-// ||A'||_F ||P^2||_F^(1/2) (2 % above it, for the single-pass product's rounding).
-__global__ void tighten_bound_kernel(float* __restrict__ bound2, const float* __restrict__ ss2, int k) {
+// With P = A' / ||A'||_F:  lambda_max(P) <= ||P^(2^j)||_F^(1 / 2^j) = (sum lambda^(2^(j+1)))^(1 / 2^(j+1))  for every j, and
+// the bound tightens with j (for a flat spectrum it is n^(-1/2) times n^(1/4), n^(1/8), n^(1/16) for j = 1, 2, 3).
+// bound^2 <- bound^2 * t^2 with t the smallest of the three, 3 % above it for the single-pass products' rounding.
+__global__ void tighten_bound_kernel(float* __restrict__ bound2, const float* __restrict__ ss2, const float* __restrict__ ss4,
+                                     const float* __restrict__ ss8, int k) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= k) return;
-  const float t = 1.04f * sqrtf(fmaxf(ss2[b], 0.f));
-  if (isfinite(t) && t > 0.f && t < 1.f) bound2[b] *= t;
+  float t = 1.f;
+  const float t2 = powf(fmaxf(ss2[b], 0.f), 0.25f);
+  if (isfinite(t2) && t2 > 0.f) t = fminf(t, 1.03f * t2);
+  if (ss4) {
+    const float t4 = powf(fmaxf(ss4[b], 0.f), 0.125f);
+    if (isfinite(t4) && t4 > 0.f) t = fminf(t, 1.03f * t4);
+  }
+  if (ss8) {
+    const float t8 = powf(fmaxf(ss8[b], 0.f), 0.0625f);
+    if (isfinite(t8) && t8 > 0.f) t = fminf(t, 1.03f * t8);
+  }
+  if (t < 1.f) bound2[b] *= t * t;
+}
+
+// v <- (v - y) / ||v - y||  with y = M v:  one power-iteration step on R = I - M;  e[b] = the Rayleigh quotient of R at
+// the incoming v, 1 - v.y / v.v (0 where v is zero: nothing is known).
+__global__ void __launch_bounds__(256) power_shift_kernel(float* __restrict__ v, const float* __restrict__ y, int n,
+                                                          float* __restrict__ e) {
+  const int b = blockIdx.x;
+  float* V = v + (long long)b * n;
+  const float* Y = y + (long long)b * n;
+  __shared__ double red[3][8];
+  __shared__ double tot[3];
+  double vy = 0.0, vv = 0.0, tt = 0.0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const double yi = Y[i], vi = V[i], d = vi - yi;
+    vy += vi * yi;
+    vv += vi * vi;
+    tt += d * d;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    vy += __shfl_xor_sync(0xffffffffu, vy, o);
+    vv += __shfl_xor_sync(0xffffffffu, vv, o);
+    tt += __shfl_xor_sync(0xffffffffu, tt, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    red[0][threadIdx.x >> 5] = vy;
+    red[1][threadIdx.x >> 5] = vv;
+    red[2][threadIdx.x >> 5] = tt;
+  }
+  __syncthreads();
+  if (threadIdx.x < 3) {
+    double t = 0.0;
+    for (int w = 0; w < 8; ++w) t += red[threadIdx.x][w];
+    tot[threadIdx.x] = t;
+  }
+  __syncthreads();
+  const double inv = tot[2] > 0.0 ? 1.0 / sqrt(tot[2]) : 0.0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) V[i] = (float)(((double)V[i] - (double)Y[i]) * inv);
+  if (threadIdx.x == 0) e[b] = tot[1] > 0.0 ? (float)(1.0 - tot[0] / tot[1]) : 0.f;
+}
+
+// status 4 where the distance of the last M from the identity, estimated by power iteration on I - M, exceeds what the
+// schedule was built for: the caller's estimate of the spectrum's lower end was too high for this statistic.
+__global__ void verify_kernel(const float* __restrict__ e_est, float e_allowed, int* __restrict__ status, float* __restrict__ e_out,
+                              int k) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= k) return;
+  const float e = e_est[b];
+  if (e_out) e_out[b] = e;
+  if (status && status[b] == 0 && (!isfinite(e) || e > e_allowed)) status[b] = 4;
+}
+
+// lmin[b] = theta^(-power): the smallest eigenvalue of A from the largest eigenvalue theta (a Rayleigh quotient, so a
+// lower estimate) of its computed inverse root A^(-1/power).
+__global__ void lmin_from_root_kernel(const float* __restrict__ theta, float power, float* __restrict__ lmin, int k) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= k) return;
+  const float t = theta[b];
+  lmin[b] = (isfinite(t) && t > 0.f) ? powf(t, -power) : 0.f;
 }
 
 // Per statistic: the scale that turns M_0^{-1/p} into A^{-1/p}, and the convergence status from the
@@ -375,7 +446,8 @@ __global__ void finish_kernel(const unsigned int* __restrict__ resid, const floa
   if (norm_out) norm_out[b] = ub;
   const float r = __uint_as_float(resid[b]);
   int st = !isfinite(r) ? 2 : (r > tol ? 1 : 0);
-  if (st == 0 && damping / ub < lower_used * 0.999f) st = 3;
+  // lower_used < 0: the bound is an estimate, verified after the chain instead (verify_kernel)
+  if (st == 0 && lower_used > 0.f && damping / ub < lower_used * 0.999f) st = 3;
   if (status) status[b] = st;
 }
 
@@ -434,6 +506,14 @@ int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32
 int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
                        float lower, float* root_lo, float* root_hi, float* fro2_lo, int32_t* status, float* norm_out,
                        void* workspace, size_t workspace_bytes, void* stream_) {
+  return toner_inv_roots_tracked(ema, k, n, damping, p, q, iters, lower, 0, root_lo, root_hi, fro2_lo, status, norm_out,
+                                 nullptr, nullptr, nullptr, 0, workspace, workspace_bytes, stream_);
+}
+
+int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
+                            float lower, int32_t lower_is_estimate, float* root_lo, float* root_hi, float* fro2_lo,
+                            int32_t* status, float* norm_out, float* track, float* lmin_out, float* resid_out,
+                            int32_t track_sweeps, void* workspace, size_t workspace_bytes, void* stream_) {
   using namespace toner;
   Context* ctx = context();
   if (!ctx) return kErrCuda;
@@ -450,7 +530,11 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
   const double l_worst = (double)damping / ((double)n * (1.0 + damping));
   if (lower != 0.f && !(lower > 0.f && lower < 1.f)) return fail(kErrArg, "inv_roots: lower must be 0 or inside (0, 1)");
   const double l0 = (lower > 0.f && (double)lower > l_worst) ? (double)lower : l_worst;
-  const float lower_used = l0 > l_worst ? (float)l0 : 0.f;
+  const bool estimated = lower_is_estimate != 0 && l0 > l_worst;
+  if (estimated && !track) return fail(kErrArg, "inv_roots: an estimated bound needs the tracking vectors to verify it");
+  if (track_sweeps < 0 || (track_sweeps & ~(63 | 256))) return fail(kErrArg, "inv_roots: track_sweeps is 0..63, plus 256 to start afresh");
+  // > 0: certified bound, checked against damping / norm per statistic; < 0: estimate, verified after the chain
+  const float lower_used = l0 > l_worst ? (estimated ? -(float)l0 : (float)l0) : 0.f;
   if (iters <= 0) iters = default_iterations(l0, p);
   if (iters < 2) return fail(kErrArg, "inv_roots: at least two iterations are required");
   const std::vector<NewtonStep> sched = newton_schedule(l0, p, iters, nullptr);
@@ -510,6 +594,10 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
     float* inv_r = small(9);
     unsigned int* max_r = reinterpret_cast<unsigned int*>(small(10));
     float* ss2 = small(11);
+    float* ss4 = small(12);
+    float* ss8 = small(13);
+    float* e_est = small(14);
+    float* theta = small(15);
     float* partials = small(16);
     const size_t vec = align_up((size_t)kc * n * 4, 256);
     float* pv = reinterpret_cast<float*>(w + sm * 16 + align_up(sumsq_scratch_bytes(kc), 256));
@@ -547,10 +635,13 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
     TONER_CUDA(cudaGetLastError());
     {
       // A tighter bound of the largest eigenvalue than ||A'||_F: with P = A' / ||A'||_F, lambda_max(P) <= ||P^2||_F^(1/2)
-      // = (sum lambda^4)^(1/4).  For a flat spectrum that is n^(-1/4) instead of 1, which raises the spectrum's lower
-      // bound after normalisation by the same factor and saves a Newton step.  One single-pass product of the hi
-      // planes is accurate enough for a bound (2 % is added); its FP32 result goes to a buffer that is free here.
+      // = (sum lambda^4)^(1/4), and likewise ||P^4||_F^(1/4), ||P^8||_F^(1/8).  For a flat spectrum these are n^(-1/4),
+      // n^(-3/8), n^(-7/16) instead of 1, which raises the spectrum's lower bound after normalisation by the same factor
+      // and saves Newton steps (each costs fifteen plane passes; these three squarings cost one pass each).  Single-pass
+      // products of hi planes are accurate enough for a bound (3 % is added); the FP32 results and the planes of P^2
+      // and P^4 (written by the epilogues, entries at most 1) go to buffers that are free here.
       float* P2 = reinterpret_cast<float*>(Pb[0]);
+      const float s_w = plane_scale(1.0);
       toner_gemm_desc g = {};
       toner_operand op = {};
       op.base = Mb[0];
@@ -560,11 +651,28 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
       g.tri = 1; g.mirror = 1;
       g.alpha = (float)(1.0 / ((double)s_m * (double)s_m));
       g.d = P2; g.ldd = n; g.d_bs = nn;
+      g.split0 = Pb[1]; g.split0_scale = s_w; g.split_ld = n; g.split_bs = nn; g.split_plane = (long long)kc * nn;
       int rc1 = launch_gemm(g, stream);
       if (rc1) return rc1;
       rc1 = sumsq_det(P2, kc, n, n, n, nn, partials, ss2, stream);
       if (rc1) return rc1;
-      tighten_bound_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(sumsq_a, ss2, kc);
+      float* P4 = reinterpret_cast<float*>(Xb[0]);
+      toner_gemm_desc g4 = g;
+      g4.a.base = Pb[1]; g4.b.base = Pb[1];
+      g4.alpha = (float)(1.0 / ((double)s_w * (double)s_w));
+      g4.d = P4; g4.split0 = Mb[1];
+      rc1 = launch_gemm(g4, stream);
+      if (rc1) return rc1;
+      rc1 = sumsq_det(P4, kc, n, n, n, nn, partials, ss4, stream);
+      if (rc1) return rc1;
+      toner_gemm_desc g8 = g4;
+      g8.a.base = Mb[1]; g8.b.base = Mb[1];
+      g8.d = P2; g8.split0 = nullptr;
+      rc1 = launch_gemm(g8, stream);
+      if (rc1) return rc1;
+      rc1 = sumsq_det(P2, kc, n, n, n, nn, partials, ss8, stream);
+      if (rc1) return rc1;
+      tighten_bound_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(sumsq_a, ss2, ss4, ss8, kc);
       count_launch();
       init_planes_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(A32, n, kc, sumsq_a, (float)sched[0].a, (float)sched[0].b,
                                                                   s_m, s_t, Mb[0], Tb[0], Xb[1]);
@@ -746,6 +854,50 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
         Xcur = Pb[pi];
         s_x = o.s0_scale;
         pi ^= 1;
+      }
+    }
+
+    if (track) {
+      float* vt = track + (long long)k0 * n;
+      if (lower_used < 0.f) {
+        // The schedule was built for an ESTIMATE of the spectrum's lower end.  If the estimate was too high for a
+        // statistic, its smallest eigenvalues have not reached the distance from 1 the finishing series was cut for,
+        // and they are the dominant eigenvalues of R = I - M of the last M (kept in FP32): four power-iteration steps
+        // on R from the tracked direction (the eigenvector of the smallest eigenvalue, as of the previous call) find
+        // them.  The allowance: the assumed distance with 15 % and the noise floor of the estimate.
+        TONER_CUDA(cudaMemcpyAsync(pv, vt, sizeof(float) * (size_t)kc * n, cudaMemcpyDeviceToDevice, stream));
+        for (int sw = 0; sw < 4; ++sw) {
+          gemv_kernel<<<dim3((n + 7) / 8, kc), 256, 0, stream>>>(A32, pv, py, n);
+          count_launch();
+          power_shift_kernel<<<kc, 256, 0, stream>>>(pv, py, n, e_est);
+          count_launch();
+        }
+        verify_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(e_est, (float)(1.15 * (1.0 - l_last) + 1e-3),
+                                                          status ? status + k0 : nullptr,
+                                                          resid_out ? resid_out + k0 : nullptr, kc);
+        count_launch();
+        TONER_CUDA(cudaGetLastError());
+      }
+      const int sweeps = track_sweeps & 63;
+      if (sweeps > 0) {
+        // Track the direction of the smallest eigenvalue of A for the next call: it is the dominant eigenvector of the
+        // highest inverse power just computed, where it stands out however small it is next to lambda_max(A).
+        const float* top = (q > 1 ? root_hi : root_lo) + (long long)k0 * nn;
+        if (track_sweeps & 256) {
+          power_start_kernel<<<dim3(8, kc), 256, 0, stream>>>(vt, n);
+          count_launch();
+        }
+        for (int sw = 0; sw < sweeps; ++sw) {
+          gemv_kernel<<<dim3((n + 7) / 8, kc), 256, 0, stream>>>(top, vt, py, n);
+          count_launch();
+          power_norm_kernel<<<kc, 256, 0, stream>>>(vt, py, n, theta, pres);
+          count_launch();
+        }
+        if (lmin_out) {
+          lmin_from_root_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(theta, (float)p / (float)q, lmin_out + k0, kc);
+          count_launch();
+        }
+        TONER_CUDA(cudaGetLastError());
       }
     }
   }

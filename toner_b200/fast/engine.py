@@ -285,6 +285,11 @@ class FastTonerCore:
         return sum(g.factors.fallbacks for g in self.groups.values())
 
     @property
+    def bound_failures(self) -> int:
+        """Steps in which an estimated spectrum bound failed its verification (those statistics were repaired)."""
+        return sum(g.factors.bound_failures for g in self.groups.values())
+
+    @property
     def extra(self) -> int:
         """Statistics that needed a repair round (factored again with the bound that always holds)."""
         return sum(g.factors.repairs for g in self.groups.values())
@@ -534,6 +539,7 @@ class FastTonerCore:
         for g in self.groups.values():
             for j, (i, k) in enumerate(g.own):
                 g.factors.ema[j].copy_(sd["ema"][f"{i}.{k}"])
+            g.factors.statistics_replaced()
         self.weight = sd["weight"]
         self.t = sd["t"]
         lo_layer = sum(self.layer_counts[:self.rank])

@@ -144,6 +144,8 @@ class _TonerGeneral(Optimizer):
             held, row = state[key], stack[i]
             if held.data_ptr() != row.data_ptr():
                 row.copy_(held.to(device=row.device, dtype=row.dtype))
+                if key == "input_ema":
+                    bucket.factors.statistics_replaced()
             state[key] = row
 
     def load_state_dict(self, state_dict) -> None:

@@ -306,12 +306,16 @@ def inv_roots(ema: torch.Tensor, damping: float, p: int, q: int = 1, *, iters: i
               root_lo: Optional[torch.Tensor] = None, root_hi: Optional[torch.Tensor] = None,
               fro2_lo: Optional[torch.Tensor] = None, status: Optional[torch.Tensor] = None,
               workspace: Optional[torch.Tensor] = None, chunk: Optional[int] = None, lower: float = 0.0,
-              norms: Optional[torch.Tensor] = None):
-    """A^(-1/p) and A^(-q/p) of the damped, trace-normalised statistics (toner_inv_roots).
+              norms: Optional[torch.Tensor] = None, lower_is_estimate: bool = False,
+              track: Optional[torch.Tensor] = None, lmin: Optional[torch.Tensor] = None,
+              resid: Optional[torch.Tensor] = None, track_sweeps: int = 0, track_restart: bool = False):
+    """A^(-1/p) and A^(-q/p) of the damped, trace-normalised statistics (toner_inv_roots_tracked).
 
     ``lower``: a lower bound of the normalised spectrum valid for every statistic (0: the bound that always
-    holds); ``norms`` (k,) receives ||A'_b||_F, from which the next call's bound can be derived.
-    Returns (root_lo, root_hi or None, fro2_lo, status); nothing is synchronised."""
+    holds); ``norms`` (k,) receives the bound of lambda_max(A'_b) the engine normalised by, from which the next call's
+    bound can be derived.  ``track`` (k, n), ``lmin`` (k,), ``track_sweeps``, ``track_restart``, ``lower_is_estimate``,
+    ``resid`` (k,): tracking of the smallest eigenvalue between calls and a bound that is an estimate, verified after
+    the chain (see the header).  Returns (root_lo, root_hi or None, fro2_lo, status); nothing is synchronised."""
     _need_cuda(ema)
     if ema.ndim == 2:
         ema = ema.unsqueeze(0)
@@ -332,9 +336,14 @@ def inv_roots(ema: torch.Tensor, damping: float, p: int, q: int = 1, *, iters: i
             per = inv_roots_workspace_bytes(1, n)
             chunk = max(1, min(k, (4 << 30) // per))
         workspace = torch.empty(inv_roots_workspace_bytes(chunk, n), device=dev, dtype=torch.uint8)
-    check(_lib.load().toner_inv_roots_ex(ema.data_ptr(), k, n, damping, p, q, iters, lower, root_lo.data_ptr(),
-                                         _ptr(root_hi), fro2_lo.data_ptr(), status.data_ptr(), _ptr(norms),
-                                         workspace.data_ptr(), workspace.numel(), _stream()), "toner_inv_roots_ex")
+    if track is not None and (track.shape != (k, n) or track.dtype != torch.float32 or not track.is_contiguous()):
+        raise ValueError("the tracking vectors are a contiguous FP32 (k, n) tensor")
+    sweeps = (int(track_sweeps) & 63) | (256 if track_restart else 0)
+    check(_lib.load().toner_inv_roots_tracked(ema.data_ptr(), k, n, damping, p, q, iters, lower, int(lower_is_estimate),
+                                              root_lo.data_ptr(), _ptr(root_hi), fro2_lo.data_ptr(), status.data_ptr(),
+                                              _ptr(norms), _ptr(track), _ptr(lmin), _ptr(resid), sweeps,
+                                              workspace.data_ptr(), workspace.numel(), _stream()),
+          "toner_inv_roots_tracked")
     return root_lo, root_hi, fro2_lo, status
 
 
