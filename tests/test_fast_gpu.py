@@ -64,6 +64,37 @@ def test_nanogpt_stack_at_full_size(fast):
     steps_against_oracle(fast, "nanogpt", "muont", (768, 3072, 1024, 16, 4, 12, 32, 16), 1)
 
 
+def test_snapshot_and_cross_check(fast):
+    """Engine extras of the reference: snapshot(layers) returns the bias-corrected statistics of the chosen layers
+    (src/toner/fast/engine.py:929-941); check_every compares the factors with an eigendecomposition of the same
+    statistics and reports (largest, median, statistic-weighted) relative errors per group and power (:743-770)."""
+    stack, opt = make(fast, "llama", "muont", ns_steps=2, check_every=1)
+    try:
+        gen = torch.Generator().manual_seed(2)
+        for _ in range(2):
+            for _ in range(ACC):
+                with opt.capture_microbatch():
+                    forward(stack, torch.randn(MB, SEQ, HID, generator=gen).cuda())
+            opt.begin()
+            for b in stack:
+                for p in b.parameters():
+                    p.grad = (torch.randn(p.shape, generator=gen) * 1e-3).cuda()
+            opt.step()
+        core_ = opt._core
+        snap = core_.snapshot([1])
+        assert set(snap) == {"1.attn", "1.o", "1.mlp", "1.down"}
+        d = core_.groups["d"]
+        want = d.factors.ema[d.keys.index((1, "o"))] / core_.weight
+        assert torch.equal(snap["1.o"], want.cpu())
+        assert abs(core_.weight - (1 - 0.95 ** 2)) < 1e-12
+        check = opt.diagnostics["check"]
+        assert set(check) == {"d", "d_out", "f", "f_out"}
+        for key, (worst, median, weighted) in check.items():
+            assert 0 <= median <= worst < 2e-3 and weighted < 2e-3, (key, worst, median, weighted)
+    finally:
+        opt.close()
+
+
 def test_llama_layer_at_full_width(fast):
     """One layer of the benchmark's Llama shape -- hidden 2048, MLP 5632, sequences of 4096 tokens sampled with head
     32 / stride 16 -- with 5 x 4 sequences per update: 5720 rows per statistic, so the 5632-wide statistic has full

@@ -124,3 +124,34 @@ def test_newton_schedule_is_restated_consistently():
         xk = xk @ t
         m = torch.linalg.matrix_power(t, p) @ m
     assert orc.rel_fro(xk * ub ** (-1.0 / p), truth) < 1e-5
+
+
+def test_flat_exchange_layout_with_uneven_ownership():
+    """Ranks that own different numbers of layers: every rank's flat buffer is its roles' stacks back to back, and the
+    stack of a role is found from the per-layer offset alone, whatever the rank owns (also nothing)."""
+    from toner_b200.fast.engine import flat_layout, layer_counts, owner_block
+    layers, world = 6, 3
+    counts = layer_counts(layers, world, [1.0, 0.0, 2.0])
+    assert counts == [2, 0, 4]
+    shapes = {"down": (3, 4), "q": (2, 3)}
+    numels = [a * b for a, b in shapes.values()]
+    offsets = flat_layout(numels)
+    lo = 0
+    seen = {}
+    for r, owned in enumerate(counts):
+        flat = torch.empty(owned * sum(numels))
+        for (role, shape), off, numel in zip(shapes.items(), offsets, numels):
+            block = owner_block(flat, owned, off, numel, shape)
+            assert block.shape == (owned,) + shape
+            for j in range(owned):
+                block[j] = 100.0 * list(shapes).index(role) + lo + j     # (role, global layer)
+        # a reader that knows only counts[r] recovers every (role, layer)
+        for (role, shape), off, numel in zip(shapes.items(), offsets, numels):
+            got = owner_block(flat, owned, off, numel, shape)
+            for j in range(owned):
+                seen[(role, lo + j)] = got[j].unique().tolist()
+        assert flat.numel() == 0 or torch.isfinite(flat).all()
+        lo += owned
+    assert len(seen) == layers * len(shapes)
+    for (role, layer), vals in seen.items():
+        assert vals == [100.0 * list(shapes).index(role) + layer]

@@ -28,17 +28,18 @@ def _microbatch(rank, mb_index):
     return torch.randn(MB, SEQ, HID, generator=g)
 
 
-def _run(kind, world, rank, device, microbatches, steps=2, first_step=0, resume=None, save_to=None, streamed=False):
+def _run(kind, world, rank, device, microbatches, steps=2, first_step=0, resume=None, save_to=None, streamed=False,
+         layers=LAYERS, owner_weights=None, snapshot_to=None):
     """One process's part of optimizer steps first_step .. steps-1; returns its weights.  `resume` = (weights,
     checkpoint) continues a run saved after `first_step` steps; `save_to` writes rank zero's checkpoint at the end."""
     import toner_b200.fast as fast
     from toner_b200.synthetic import make_stack
-    stack = make_stack("llama", LAYERS, HID, MLP, device, seed=0)
+    stack = make_stack("llama", layers, HID, MLP, device, seed=0)
     cls = fast.FastMuonT if kind == "muont" else fast.FastAdamT
     extra = dict(ns_steps=2) if kind == "muont" else dict(betas=(0.9, 0.95), eps=1e-4)
     opt = cls([fast.ProjectionBlock.from_module(b) for b in stack], 0.02 if kind == "muont" else 2e-3, weight_decay=0.1,
               micro_batch_size=MB, sequence_length=SEQ, accumulation_steps=len(microbatches), statistic_head=32,
-              statistic_stride=4, **extra)
+              statistic_stride=4, owner_weights=owner_weights, **extra)
     try:
         if resume is not None:
             weights, ckpt = resume
@@ -56,7 +57,7 @@ def _run(kind, world, rank, device, microbatches, steps=2, first_step=0, resume=
             if streamed:    # rows "arrive" group by group: wide statistics first, then the hidden-width ones in two slices
                 ev = torch.cuda.Event()
                 ev.record()
-                opt._core.begin(ready=[("f", 0, LAYERS, ev), ("d", 0, 2, ev), ("d", 2, 3 * LAYERS, ev)])
+                opt._core.begin(ready=[("f", 0, layers, ev), ("d", 0, 2, ev), ("d", 2, 3 * layers, ev)])
             else:
                 opt.begin()
             g = torch.Generator().manual_seed(77 + step)     # gradients arrive already synchronised
@@ -68,6 +69,10 @@ def _run(kind, world, rank, device, microbatches, steps=2, first_step=0, resume=
         torch.cuda.synchronize(device)
         from toner_b200 import ops
         ops.assert_healthy()
+        if snapshot_to is not None:
+            snap = opt._core.snapshot([0, layers - 1])       # collective; the statistics come back on rank zero
+            if rank == 0:
+                torch.save({"snapshot": snap, "counts": opt._core.layer_counts}, snapshot_to)
         if save_to is not None:
             ckpt = opt.state_dict()                          # collective; the checkpoint comes back on rank zero
             if rank == 0:
@@ -149,3 +154,49 @@ def test_streamed_rows_on_two_ranks_change_nothing(tmp_path):
         plain = torch.load(os.path.join(tmp_path, f"w{r}_2.pt"))
         streamed = torch.load(os.path.join(tmp_path, f"w{r}_2s.pt"))
         assert all(torch.equal(a, b) for a, b in zip(plain, streamed))
+
+
+def _uneven_worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        weights = _run("muont", world, rank, device, [_microbatch(rank, i) for i in range(ACC)], layers=4,
+                       owner_weights=[1.0, 3.0], save_to=os.path.join(out_dir, "ckpt_uneven.pt"),
+                       snapshot_to=os.path.join(out_dir, "snap.pt"))
+        torch.save(weights, os.path.join(out_dir, f"u{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_uneven_layer_ownership_matches_one_process(tmp_path):
+    """owner_weights (1, 3) on four layers: rank 0 owns one layer, rank 1 three.  The statistics reach their owners
+    through the uneven form of reduce-scatter, the changes come back through the uneven all-gather, and every rank
+    ends with the weights one process computes from all microbatches; the gathered checkpoint and the statistics
+    snapshot name every layer."""
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_uneven_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    torch.cuda.set_device(0)
+    single = _run("muont", 1, 0, torch.device("cuda", 0), [_microbatch(r, i) for r in range(world) for i in range(ACC)],
+                  layers=4)
+    for r in range(world):
+        got = torch.load(os.path.join(tmp_path, f"u{r}.pt"))
+        for a, b in zip(got, single):
+            rel = (a - b).norm().item() / b.norm().item()
+            assert rel < 3e-4, (r, rel)
+    snap = torch.load(os.path.join(tmp_path, "snap.pt"), weights_only=False)
+    assert snap["counts"] == [1, 3]
+    assert set(snap["snapshot"]) == {f"{i}.{k}" for i in (0, 3) for k in ("attn", "o", "mlp", "down")}
+    ckpt = torch.load(os.path.join(tmp_path, "ckpt_uneven.pt"), weights_only=False)
+    assert len(ckpt["core"]["ema"]) == 16 and len(ckpt["core"]["moments"]) == 28
+    # the snapshot is the bias-corrected statistic: EMA / weight
+    for key, value in snap["snapshot"].items():
+        assert torch.allclose(value, ckpt["core"]["ema"][key] / ckpt["core"]["weight"], rtol=1e-6, atol=0)

@@ -115,6 +115,11 @@ class FactorSet:
         else:
             self.hi_planes, self.hi_inv = self.lo_planes, self.lo_inv
         per = ops.inv_roots_workspace_bytes(1, n)
+        if k == 0:            # a rank that owns no statistic of this width (weighted ownership): nothing to factor
+            self.workspace = None
+            self.iterations = self.finish_order = 0
+            self.fallbacks = self.repairs = 0
+            return
         if chunk is None:
             # One launch over all statistics keeps the persistent kernel's last wave full (24 statistics of width
             # 5632 are 83 waves of pair tiles; five at a time would be 18 waves per launch with a ragged tail each).
@@ -150,7 +155,7 @@ class FactorSet:
 
     def compute(self) -> None:
         """Enqueue the Newton factor computation and the operand split of the results."""
-        if self.inner_strength == 0 and self.outer_strength == 0:
+        if self.k == 0 or (self.inner_strength == 0 and self.outer_strength == 0):
             return
         ops.inv_roots(self.ema, self.damping, self.p, self.q, root_lo=self.root_lo, root_hi=self.root_hi,
                       fro2_lo=self.fro2_lo, status=self.status, workspace=self.workspace, lower=self.lower,
@@ -298,11 +303,15 @@ def _product(a_planes, a_inv, group: MatrixGroup, which: str, d, coarse: bool = 
              alpha_b=r_inv[group.first:], alpha_b_step=group.step, promote=0, **kw)
 
 
-def _muont_buffers(group: MatrixGroup, scratch: Scratch):
+def _muont_buffers(group: MatrixGroup, scratch: Scratch, work: Optional[torch.Tensor] = None):
+    """Scratch of one matrix group's update.  `work` (count, out, in) replaces the shared FP32 work stack: several groups
+    of one shape can then keep their stacks side by side and go through Newton-Schulz as one batch."""
     dev = group.device
     count, m, n = group.count, group.out_features, group.in_features
     shape = (count, m, n)
-    return dict(work=scratch.get("work", shape, torch.float32, dev),
+    if work is not None and (tuple(work.shape) != shape or work.dtype != torch.float32 or not work.is_contiguous()):
+        raise ValueError("the work stack of a matrix group is a contiguous FP32 (count, out, in) tensor")
+    return dict(work=work if work is not None else scratch.get("work", shape, torch.float32, dev),
                 planes=scratch.get("planes", (2,) + shape, torch.float16, dev),
                 inv=scratch.get("inv", (count,), torch.float32, dev),
                 maxabs=scratch.get("maxabs", (count,), torch.int32, dev),
@@ -311,11 +320,11 @@ def _muont_buffers(group: MatrixGroup, scratch: Scratch):
 
 
 def muont_ns_input(group: MatrixGroup, grads: Sequence[torch.Tensor], scratch: Scratch, *, momentum: float,
-                   nesterov: bool) -> torch.Tensor:
+                   nesterov: bool, work: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Stage 1 of the MuonT update: momentum, Nesterov direction and the inner preconditioning d R_in
     (src/toner/reference.py:197-204).  Returns the (count, out, in) stack the polar iteration starts from."""
     f = group.factors
-    buf = _muont_buffers(group, scratch)
+    buf = _muont_buffers(group, scratch, work)
     work, planes, inv, maxabs = buf["work"], buf["planes"], buf["inv"], buf["maxabs"]
     ops.muont_momentum(group.grad_ptrs(grads), group.m, work, momentum, nesterov, maxabs)
     if f.inner_strength != 0:
@@ -325,13 +334,14 @@ def muont_ns_input(group: MatrixGroup, grads: Sequence[torch.Tensor], scratch: S
 
 
 def muont_delta_from_polar(group: MatrixGroup, polar: torch.Tensor, delta: torch.Tensor, scratch: Scratch, *, lr: float,
-                           weight_decay: float, polar_maxabs: Optional[torch.Tensor] = None) -> None:
+                           weight_decay: float, polar_maxabs: Optional[torch.Tensor] = None,
+                           work: Optional[torch.Tensor] = None) -> None:
     """Stage 3: outer map, shape scale and shaped weight decay (src/toner/reference.py:206-215), fused as the
     reference's engine fuses them (src/toner/fast/engine.py:42-51):
     delta = -((lr wd n / ||R||^2) W R + (lr s sqrt(n) / ||R||) P) R.  `polar` may be the work stack itself."""
     f = group.factors
     count, m, n = group.count, group.out_features, group.in_features
-    buf = _muont_buffers(group, scratch)
+    buf = _muont_buffers(group, scratch, work)
     work, planes, inv, maxabs, c1, c2 = (buf[k] for k in ("work", "planes", "inv", "maxabs", "c1", "c2"))
     if polar.data_ptr() != work.data_ptr():
         work.copy_(polar)
@@ -367,6 +377,32 @@ def muont_group_delta(group: MatrixGroup, grads: Sequence[torch.Tensor], delta: 
     ns_ws = scratch.bytes_like("ns", ops.ns_polar_workspace_bytes(count, m, n), dev)
     ops.ns_polar(work, ns_steps, ns_eps, out=work, maxabs=maxabs, workspace=ns_ws)
     muont_delta_from_polar(group, work, delta, scratch, lr=lr, weight_decay=weight_decay, polar_maxabs=maxabs)
+
+
+def muont_groups_delta(groups: Sequence[MatrixGroup], grads: Sequence[Sequence[torch.Tensor]],
+                       deltas: Sequence[torch.Tensor], scratch: Scratch, *, lr: float, weight_decay: float,
+                       momentum: float, nesterov: bool, ns_steps: int, ns_eps: float) -> None:
+    """muont_group_delta for several groups of ONE matrix shape (for instance the q, k, v and o projections of the owned
+    layers): momentum and inner preconditioning per group, then ONE Newton-Schulz call over all their matrices, then the
+    outer map per group.  The arithmetic per matrix is unchanged; the polar iteration's thirty products run on a batch
+    several times larger, which matters when a rank owns few layers (three layers are 108 symmetric tiles on 74 SM
+    pairs: a wave and a half)."""
+    first = groups[0]
+    count, m, n = first.count, first.out_features, first.in_features
+    if any((g.count, g.out_features, g.in_features) != (count, m, n) for g in groups):
+        raise ValueError("groups that share a Newton-Schulz batch need one matrix shape and one count")
+    dev = first.device
+    total = count * len(groups)
+    merged = scratch.get("work_merged", (total, m, n), torch.float32, dev)
+    maxabs = scratch.get("maxabs_merged", (total,), torch.int32, dev)
+    slices = [merged[j * count:(j + 1) * count] for j in range(len(groups))]
+    for g, gr, w in zip(groups, grads, slices):
+        muont_ns_input(g, gr, scratch, momentum=momentum, nesterov=nesterov, work=w)
+    ns_ws = scratch.bytes_like("ns", ops.ns_polar_workspace_bytes(total, m, n), dev)
+    ops.ns_polar(merged, ns_steps, ns_eps, out=merged, maxabs=maxabs, workspace=ns_ws)
+    for j, (g, w, d) in enumerate(zip(groups, slices, deltas)):
+        muont_delta_from_polar(g, w, d, scratch, lr=lr, weight_decay=weight_decay,
+                               polar_maxabs=maxabs[j * count:(j + 1) * count], work=w)
 
 
 def adamt_group_delta(group: MatrixGroup, grads: Sequence[torch.Tensor], delta: torch.Tensor, scratch: Scratch, *,

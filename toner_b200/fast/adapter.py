@@ -123,7 +123,7 @@ class _FastToner(torch.optim.Optimizer):
                  inner_strength=0.5, outer_strength=0.125, statistic_momentum=0.938, statistic_head=32,
                  statistic_stride=16, ns_steps=10, ns_eps=1e-5, root_refresh=4, root_iterations=2,
                  root_inline_steps=20, root_repair_rounds=3, root_graphs=True, host_workers=2, host_threads=4,
-                 statistic_chunks=4, row_pieces=1):
+                 statistic_chunks=4, row_pieces=1, owner_weights=None, check_every=0):
         if len(_LIVE):
             raise RuntimeError("another fast Toner optimizer is alive in this process; close() it first")
         strengths = (float(inner_strength), float(outer_strength))
@@ -191,8 +191,17 @@ class _FastToner(torch.optim.Optimizer):
         rank = dist.get_rank() if in_group else 0
         if world > 1 and dist.get_backend() != "nccl":
             raise ValueError("more than one rank needs the NCCL backend (and replicated, synchronised gradients)")
-        if len(self.blocks) % world != 0:
-            raise ValueError("the number of blocks must be a multiple of the number of ranks")
+        # Optional (the reference's engine has both, its adapter does not pass them: --toner-owner-weights and
+        # toner_check_every, src/toner/fast/engine.py:215-219,743-770): layers per rank in proportion to `owner_weights`
+        # instead of equal blocks, and a cross-check of the factors against an eigendecomposition every `check_every` steps.
+        if owner_weights is not None:
+            owner_weights = [float(x) for x in owner_weights]
+            if len(owner_weights) != world or min(owner_weights) < 0 or sum(owner_weights) <= 0:
+                raise ValueError("owner_weights needs one non-negative weight per rank, not all zero")
+        elif len(self.blocks) % world != 0:
+            raise ValueError("the number of blocks must be a multiple of the number of ranks (or give owner_weights)")
+        if isinstance(check_every, bool) or not isinstance(check_every, int) or check_every < 0:
+            raise ValueError("check_every must be a nonnegative integer")
         super().__init__(list(named.values()), {"lr": float(lr), "weight_decay": float(weight_decay)})
         self._closed = self._capturing = False
         self._microbatches = 0
@@ -212,7 +221,8 @@ class _FastToner(torch.optim.Optimizer):
             statistic_momentum=float(statistic_momentum), inner_strength=strengths[0], outer_strength=strengths[1],
             damping=1e-3, weight_decay=float(weight_decay), beta1=float(betas[0]), beta2=float(betas[1]),
             eps=float(eps), momentum=float(momentum), nesterov=bool(nesterov), ns_steps=ns_steps,
-            ns_eps=float(ns_eps), stat_chunks=int(statistic_chunks))
+            ns_eps=float(ns_eps), stat_chunks=int(statistic_chunks), owner_weights=owner_weights,
+            check_every=int(check_every))
         # the checkpoint's "config" block: same keys as the reference writes (src/toner/fast/adapter.py:321-340)
         self._config = dict(
             layout=self._layout, kind=kind, inner_strength=strengths[0], outer_strength=strengths[1],
@@ -402,8 +412,11 @@ class _FastToner(torch.optim.Optimizer):
     def diagnostics(self):
         """Fallback counts and recent timings of the engine."""
         self._assert_open()
-        return {"fallbacks": self._core.fallbacks, "extra_iterations": self._core.extra,
-                "timing": dict(self._core.timing), "gpu_ms": dict(self._core.gpu_ms)}
+        out = {"fallbacks": self._core.fallbacks, "extra_iterations": self._core.extra,
+               "timing": dict(self._core.timing), "gpu_ms": dict(self._core.gpu_ms)}
+        if self._core.check:
+            out["check"] = dict(self._core.check)
+        return out
 
     def close(self):
         """Finish outstanding work, detach hooks and release the engine's NCCL group (call on every rank)."""

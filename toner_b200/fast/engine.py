@@ -82,14 +82,27 @@ def gathered_block(gathered: torch.Tensor, rank: int, offset: int, size: int, sh
     return gathered[rank, offset: offset + size].view(tuple(shape))
 
 
+def owner_block(flat: torch.Tensor, owned: int, unit_offset: int, numel: int, shape) -> torch.Tensor:
+    """One role's stack inside the flat exchange buffer of a rank that owns `owned` layers.  The buffer is the roles'
+    stacks back to back, each (owned, out, in); `unit_offset` is the sum of the earlier roles' matrix sizes, so the
+    stack starts at owned * unit_offset whatever the rank owns (ranks may own different numbers of layers)."""
+    return flat[owned * unit_offset: owned * (unit_offset + numel)].view((owned,) + tuple(shape))
+
+
 class StatGroup:
     """All statistics of one width: row buffers for every layer, EMAs and factors for the owned ones."""
 
-    def __init__(self, name: str, keys: List[Tuple[int, str]], n: int, rows: int, per_rank: int, rank: int, world: int,
-                 device: torch.device, strengths: Tuple[float, float], damping: float, scratch: core.Scratch) -> None:
+    def __init__(self, name: str, keys: List[Tuple[int, str]], n: int, rows: int, counts: Sequence[int], rank: int,
+                 world: int, device: torch.device, strengths: Tuple[float, float], damping: float,
+                 scratch: core.Scratch) -> None:
+        """`counts[r]` statistics are owned by rank r, in key order (contiguous layer blocks; ranks may own different
+        numbers of layers, a rank may own none)."""
         self.name, self.keys, self.n, self.rows = name, keys, n, rows
+        self.counts = [int(c) for c in counts]
+        per_rank = self.counts[rank]
+        self.uneven = len(set(self.counts)) > 1
         self.k_all, self.per, self.rank, self.world = len(keys), per_rank, rank, world
-        self.lo = rank * per_rank
+        self.lo = sum(self.counts[:rank])
         self.own = keys[self.lo: self.lo + per_rank]
         self.tri = n * (n + 1) // 2
         # one stacked row buffer: statistic s of this rank's tokens is rows_buf[s]
@@ -101,10 +114,18 @@ class StatGroup:
 
     def plan_chunks(self, chunks: int) -> None:
         """Split the owned block into `chunks` pieces; chunk c of every rank is reduced together."""
+        dev = self.rows_buf.device
+        if self.uneven:
+            # Ranks own different numbers of statistics: one piece, the partial Grams in key order (rank blocks are
+            # contiguous), summed at the owners by the uneven (list) form of reduce-scatter.
+            self.chunks, self.chunk_stats = 1, self.per
+            self.partial = torch.empty(1, self.k_all, self.tri, device=dev, dtype=torch.float32)
+            self.summed = torch.empty(1, self.per, self.tri, device=dev, dtype=torch.float32)
+            self.chunk_lists = [[self.rows_buf[s] for s in range(self.k_all)]]
+            return
         chunks = chunk_plan(self.per, chunks)
         self.chunks = chunks
         self.chunk_stats = self.per // chunks
-        dev = self.rows_buf.device
         self.partial = torch.empty(chunks, self.world, self.chunk_stats, self.tri, device=dev, dtype=torch.float32)
         self.summed = (torch.empty(chunks, self.chunk_stats, self.tri, device=dev, dtype=torch.float32)
                        if self.world > 1 else None)
@@ -133,17 +154,26 @@ class FastTonerCore:
         self.L = layers
         self.rows_total = local_rows * world
         self.decay = float(args.statistic_momentum)
-        self.layer_counts = layer_counts(layers, world)
+        # Layers per rank: equal blocks, or in proportion to `owner_weights` (a slower GPU can be given fewer layers to
+        # factor and update, a zero weight none; every rank still computes its rows' partial Grams of every statistic),
+        # as --toner-owner-weights does in the reference (src/toner/fast/engine.py:66-83,215-239).
+        weights = getattr(args, "owner_weights", None)
+        self.layer_counts = layer_counts(layers, world, list(weights) if weights else None)
+        self.uneven = len(set(self.layer_counts)) > 1
         self.per_layers = self.layer_counts[rank]
+        self.lo_layer = sum(self.layer_counts[:rank])
+        self.check_every = int(getattr(args, "check_every", 0) or 0)
+        self.check: Dict[str, Tuple[float, float, float]] = {}
         self.owner_of_layer = [r for r, c in enumerate(self.layer_counts) for _ in range(c)]
         self.scratch = core.Scratch()
         strengths = (float(args.inner_strength), float(args.outer_strength))
         damping = float(getattr(args, "damping", 1e-3))
         self.groups = {
             "d": StatGroup("d", [(i, k) for i in range(layers) for k in KINDS_D], hid, row_capacity,
-                           len(KINDS_D) * self.per_layers, rank, world, device, strengths, damping, self.scratch),
-            "f": StatGroup("f", [(i, "down") for i in range(layers)], mlp, row_capacity, self.per_layers, rank, world,
-                           device, strengths, damping, self.scratch),
+                           [len(KINDS_D) * c for c in self.layer_counts], rank, world, device, strengths, damping,
+                           self.scratch),
+            "f": StatGroup("f", [(i, "down") for i in range(layers)], mlp, row_capacity, list(self.layer_counts), rank,
+                           world, device, strengths, damping, self.scratch),
         }
         self.weight = 0.0
         # matrices by role; the owned layers of a role form one MatrixGroup
@@ -157,7 +187,7 @@ class FastTonerCore:
                 raise ValueError(f"Invalid input-statistic binding for matrix {name}")
             roles.setdefault(role, []).append((layer, name, p))
         self.roles = {}
-        lo_layer = sum(self.layer_counts[:rank])
+        lo_layer = self.lo_layer
         plan = []
         for role, items in roles.items():
             items.sort(key=lambda it: it[0])
@@ -168,7 +198,7 @@ class FastTonerCore:
         # buffers: the first is all-gathered (one large NCCL transfer) while the roles of the second are still being
         # computed, the second right after them.  One buffer when there is nothing to exchange.
         plan.sort(key=lambda pr: -pr[1][0][2].numel())
-        sizes = [self.per_layers * items[0][2].numel() for _, items in plan]
+        sizes = [items[0][2].numel() for _, items in plan]   # per layer: the split must not depend on what a rank owns
         cut = len(plan)
         if world > 1 and len(plan) > 1:
             acc = 0
@@ -181,11 +211,17 @@ class FastTonerCore:
         for lo_i, hi_i in ((0, cut), (cut, len(plan))):
             if lo_i == hi_i:
                 continue
-            total = sum(sizes[lo_i:hi_i])
-            part = dict(delta=torch.empty(total, device=device, dtype=torch.float32),
-                        gathered=(torch.empty(world, total, device=device, dtype=torch.float32) if world > 1 else None),
-                        roles=[])
-            for (role, items), size, offset in zip(plan[lo_i:hi_i], sizes[lo_i:hi_i], flat_layout(sizes[lo_i:hi_i])):
+            numels = [items[0][2].numel() for _, items in plan[lo_i:hi_i]]
+            unit = sum(numels)                                   # elements one layer contributes to this part
+            total = self.per_layers * unit
+            if world == 1:
+                gathered = None
+            elif self.uneven:   # one flat buffer per rank, sized by what that rank owns
+                gathered = [torch.empty(c * unit, device=device, dtype=torch.float32) for c in self.layer_counts]
+            else:
+                gathered = torch.empty(world, total, device=device, dtype=torch.float32)
+            part = dict(delta=torch.empty(total, device=device, dtype=torch.float32), gathered=gathered, roles=[])
+            for (role, items), numel, unit_offset in zip(plan[lo_i:hi_i], numels, flat_layout(numels)):
                 all_w = [it[2] for it in items]
                 own_w = all_w[lo_layer: lo_layer + self.per_layers]
                 stat_kind = ROLE_KIND[role]
@@ -193,11 +229,12 @@ class FastTonerCore:
                     g, first, step = self.groups["f"], 0, 1
                 else:
                     g, first, step = self.groups["d"], KINDS_D.index(stat_kind), len(KINDS_D)
-                group = core.MatrixGroup(own_w, g.factors, first, step, kind)
-                shape = (self.per_layers,) + tuple(all_w[0].shape)
-                delta = part["delta"][offset: offset + size].view(shape)
-                self.roles[role] = dict(group=group, all=all_w, names=[it[1] for it in items], delta=delta, offset=offset,
-                                        size=size, all_ptrs=ops.pointer_table(all_w))
+                group = core.MatrixGroup(own_w, g.factors, first, step, kind) if own_w else None
+                matrix = tuple(all_w[0].shape)
+                delta = owner_block(part["delta"], self.per_layers, unit_offset, numel, matrix)
+                self.roles[role] = dict(group=group, all=all_w, names=[it[1] for it in items], delta=delta,
+                                        unit_offset=unit_offset, numel=numel, matrix=matrix,
+                                        all_ptrs=ops.pointer_table(all_w))
                 part["roles"].append(role)
             self.parts.append(part)
         self.t = 0
@@ -256,7 +293,10 @@ class FastTonerCore:
             weight_decay=float(args.wd), beta1=float(getattr(args, "beta1", 0.9)), beta2=float(getattr(args, "beta2", 0.98)),
             eps=float(getattr(args, "eps", 1e-15)), momentum=float(getattr(args, "muon_momentum", 0.95)),
             nesterov=bool(getattr(args, "muon_nesterov", True)), ns_steps=int(getattr(args, "muon_ns_steps", 10)),
-            ns_eps=float(getattr(args, "muon_eps", 1e-5)), stat_chunks=4)
+            ns_eps=float(getattr(args, "muon_eps", 1e-5)), stat_chunks=4,
+            owner_weights=([float(x) for x in str(args.toner_owner_weights).split(",")]
+                           if getattr(args, "toner_owner_weights", "") else None),
+            check_every=int(getattr(args, "toner_check_every", 0) or 0))
         if rows_total % world:
             raise ValueError("rows_total must be a multiple of the number of ranks")
         capacity = int(blocks[0].input_rows_attn.size(0))
@@ -308,6 +348,12 @@ class FastTonerCore:
         mode = ops.PACKED_ACC if self.pieces_done else ops.PACKED
         ops.syrk_upper(g.chunk_lists[c], g.partial[c].view(-1, g.tri), mode)
 
+    def _reduce_to_owners(self, g: "StatGroup", c: int):
+        """Sum chunk c's partial Grams over the ranks at the owners (asynchronous; returns the NCCL work)."""
+        if g.uneven:
+            return dist.reduce_scatter(g.summed[0], list(g.partial[0].split(g.counts)), group=self.pg, async_op=True)
+        return dist.reduce_scatter_tensor(g.summed[c], g.partial[c], group=self.pg, async_op=True)
+
     def chunk_stats(self) -> None:
         """Fold the rows now in the buffers into the step's partial Grams (side stream); the buffers then take the
         next piece of the step.  Call after the forward of a piece's last microbatch, except for the step's last
@@ -356,14 +402,14 @@ class FastTonerCore:
                 for c in range(g.chunks):
                     self._partial_grams(g, c)
                     # NCCL waits for the SYRK just enqueued and runs on its own stream: the next chunk's SYRK overlaps it
-                    work = dist.reduce_scatter_tensor(g.summed[c], g.partial[c], group=self.pg, async_op=True)
-                    pending.append((g, c, work))
+                    pending.append((g, c, self._reduce_to_owners(g, c)))
                     self._beside_collective(True)
             self._beside_collective(False)
             for g, c, work in pending:
                 work.wait()
                 cs = g.chunk_stats
-                ops.unpack_ema(g.summed[c], g.factors.ema[c * cs:(c + 1) * cs], b, gamma)
+                if cs:
+                    ops.unpack_ema(g.summed[c], g.factors.ema[c * cs:(c + 1) * cs], b, gamma)
         self.pieces_done = 0
         self.weight = b * self.weight + (1 - b)
 
@@ -396,13 +442,14 @@ class FastTonerCore:
                 pending = []
                 for c in range(g.chunks):
                     self._partial_grams(g, c)
-                    pending.append((c, dist.reduce_scatter_tensor(g.summed[c], g.partial[c], group=self.pg, async_op=True)))
+                    pending.append((c, self._reduce_to_owners(g, c)))
                     self._beside_collective(True)
                 self._beside_collective(False)
                 cs = g.chunk_stats
                 for c, work in pending:
                     work.wait()
-                    ops.unpack_ema(g.summed[c], g.factors.ema[c * cs:(c + 1) * cs], b, gamma)
+                    if cs:
+                        ops.unpack_ema(g.summed[c], g.factors.ema[c * cs:(c + 1) * cs], b, gamma)
             g.factors.compute()
         self.weight = b * self.weight + (1 - b)
 
@@ -460,36 +507,49 @@ class FastTonerCore:
         self.t += 1
         works = []
         for part in self.parts:
+            # roles of one matrix shape (q, k, v, o; gate, up) go through Newton-Schulz together
+            by_shape: Dict[Tuple[int, ...], List[str]] = {}
             for role in part["roles"]:
-                info = self.roles[role]
-                group: core.MatrixGroup = info["group"]
-                if group.count:
-                    grads = [p.grad for p in group.weights]
+                by_shape.setdefault(self.roles[role]["matrix"], []).append(role)
+            for shape, names in by_shape.items():
+                infos = [self.roles[r] for r in names]
+                if infos[0]["group"] is not None:
+                    grads = [[p.grad for p in info["group"].weights] for info in infos]
                     if self.kind == "muont":
-                        core.muont_group_delta(group, grads, info["delta"], self.scratch, lr=lr, weight_decay=wd,
-                                               momentum=float(a.momentum), nesterov=bool(a.nesterov),
-                                               ns_steps=int(a.ns_steps), ns_eps=float(a.ns_eps))
+                        core.muont_groups_delta([info["group"] for info in infos], grads, [info["delta"] for info in infos],
+                                                self.scratch, lr=lr, weight_decay=wd, momentum=float(a.momentum),
+                                                nesterov=bool(a.nesterov), ns_steps=int(a.ns_steps),
+                                                ns_eps=float(a.ns_eps))
                     else:
-                        core.adamt_group_delta(group, grads, info["delta"], self.scratch, lr=lr, weight_decay=wd,
-                                               betas=(float(a.beta1), float(a.beta2)), eps=float(a.eps), t=self.t)
+                        for info, gr in zip(infos, grads):
+                            core.adamt_group_delta(info["group"], gr, info["delta"], self.scratch, lr=lr, weight_decay=wd,
+                                                   betas=(float(a.beta1), float(a.beta2)), eps=float(a.eps), t=self.t)
                 if self.world == 1:
-                    ops.apply_delta(info["all_ptrs"], info["delta"])
+                    for info in infos:
+                        ops.apply_delta(info["all_ptrs"], info["delta"])
             if self.world > 1:   # this part's changes travel while the next part is computed
-                works.append(dist.all_gather_into_tensor(part["gathered"], part["delta"], group=self.pg, async_op=True))
+                if self.uneven:
+                    works.append(dist.all_gather(part["gathered"], part["delta"], group=self.pg, async_op=True))
+                else:
+                    works.append(dist.all_gather_into_tensor(part["gathered"], part["delta"], group=self.pg, async_op=True))
                 self._beside_collective(True)
         self._beside_collective(False)
         self._ev[4].record(self.main_stream)
-        per = self.per_layers
         for part, work in zip(self.parts, works):
             work.wait()
             for role in part["roles"]:
                 info = self.roles[role]
-                shape = tuple(info["delta"].shape)
-                for r in range(self.world):   # rank r's block holds layers r*per .. (r+1)*per - 1 of this role
-                    block = gathered_block(part["gathered"], r, info["offset"], info["size"], shape)
-                    ops.apply_delta(info["all_ptrs"][r * per:(r + 1) * per], block)
+                lo = 0
+                for r, owned in enumerate(self.layer_counts):   # rank r's block holds layers lo .. lo + owned - 1
+                    if owned:
+                        flat = part["gathered"][r]
+                        block = owner_block(flat, owned, info["unit_offset"], info["numel"], info["matrix"])
+                        ops.apply_delta(info["all_ptrs"][lo: lo + owned], block)
+                    lo += owned
         self._ev[5].record(self.main_stream)
         self._ev[3].record(self.main_stream)
+        if self.check_every and self.steps % self.check_every == 0:
+            self._cross_check()
         self.health.arm("the previous step's update")
         self._ev_last = self._ev
         self.steps += 1
@@ -500,12 +560,62 @@ class FastTonerCore:
             p.grad = None
 
     # ------------------------------------------------------------------ checkpoint state
-    def _gather(self, t: torch.Tensor) -> torch.Tensor:
+    def _gather(self, t: torch.Tensor, counts: Sequence[int]) -> torch.Tensor:
+        """Stacks (counts[r], ...) of all ranks, concatenated in rank order (= layer order)."""
         if self.world == 1:
             return t
-        full = torch.empty((self.world,) + tuple(t.shape), device=t.device, dtype=t.dtype)
-        dist.all_gather_into_tensor(full, t.contiguous(), group=self.pg)
-        return full.view((-1,) + tuple(t.shape[1:]))
+        if len(set(counts)) == 1:
+            full = torch.empty((self.world,) + tuple(t.shape), device=t.device, dtype=t.dtype)
+            dist.all_gather_into_tensor(full, t.contiguous(), group=self.pg)
+            return full.view((-1,) + tuple(t.shape[1:]))
+        outs = [torch.empty((c,) + tuple(t.shape[1:]), device=t.device, dtype=t.dtype) for c in counts]
+        dist.all_gather(outs, t.contiguous(), group=self.pg)
+        return torch.cat(outs)
+
+    @torch.no_grad()
+    def snapshot(self, layers):
+        """Collective: the bias-corrected statistics (EMA / weight) of the chosen layers on rank zero, None elsewhere
+        (snapshot, src/toner/fast/engine.py:929-941); keys "<layer>.<kind>"."""
+        self.main_stream.wait_stream(self.side)
+        wanted = set(int(i) for i in layers)
+        out = {}
+        for g in self.groups.values():
+            full = self._gather(g.factors.ema, g.counts)
+            if self.rank == 0:
+                for (i, k), c in zip(g.keys, full.unbind(0)):
+                    if i in wanted:
+                        out[f"{i}.{k}"] = (c / self.weight).cpu()
+            del full
+        return out if self.rank == 0 else None
+
+    @torch.no_grad()
+    def _cross_check(self) -> None:
+        """Validation only (toner_check_every, src/toner/fast/engine.py:743-770): the factors of this rank's
+        statistics against an eigendecomposition of the same EMAs.  For every group and power, check[key] = (largest and
+        median relative Frobenius error, largest error weighted by the statistic itself -- the norm the gradient sees)."""
+        for name, g in self.groups.items():
+            f = g.factors
+            if not f.k:
+                continue
+            c = f.ema.double()
+            c = 0.5 * (c + c.transpose(-1, -2))
+            lam, vec = torch.linalg.eigh(c)
+            lam = lam.clamp_min(0)
+            unit = lam / lam.mean(-1, keepdim=True).clamp_min(1e-30) + f.damping
+            cn = c / c.diagonal(dim1=-2, dim2=-1).sum(-1)[:, None, None]
+            pairs = [(name, f.root("inner"), f.inner_strength)]
+            if f.outer_strength != f.inner_strength:
+                pairs.append((name + "_out", f.root("outer"), f.outer_strength))
+            for key, got, strength in pairs:
+                if got is None:
+                    continue
+                exact = (vec * unit.pow(-strength).unsqueeze(-2)) @ vec.transpose(-1, -2)
+                d = got.double() - exact
+                rel = d.norm(dim=(-2, -1)) / exact.norm(dim=(-2, -1))
+                num = (d @ cn @ d.transpose(-1, -2)).diagonal(dim1=-2, dim2=-1).sum(-1)
+                den = (exact @ cn @ exact.transpose(-1, -2)).diagonal(dim1=-2, dim2=-1).sum(-1)
+                ec = (num / den).clamp_min(0).sqrt()
+                self.check[key] = (rel.max().item(), rel.median().item(), ec.max().item())
 
     @torch.no_grad()
     def full_state(self):
@@ -513,7 +623,7 @@ class FastTonerCore:
         self.main_stream.wait_stream(self.side)
         ema = {}
         for g in self.groups.values():
-            full = self._gather(g.factors.ema)
+            full = self._gather(g.factors.ema, g.counts)
             if self.rank == 0:
                 for (i, k), c in zip(g.keys, full.unbind(0)):
                     ema[f"{i}.{k}"] = c.cpu()
@@ -521,10 +631,10 @@ class FastTonerCore:
         moments: Dict[str, Dict[str, torch.Tensor]] = {}
         for role, info in self.roles.items():
             group = info["group"]
-            for key, stack in (("m", group.m), ("v", group.v)):
-                if stack is None:
-                    continue
-                full = self._gather(stack)
+            for key in (("m",) if self.kind == "muont" else ("m", "v")):
+                # a rank that owns no layer still joins the gather, with an empty stack
+                stack = getattr(group, key) if group is not None else torch.empty((0,) + info["matrix"], device=self.device)
+                full = self._gather(stack, self.layer_counts)
                 if self.rank == 0:
                     for name, val in zip(info["names"], full.unbind(0)):
                         moments.setdefault(name, {})[key] = val.cpu()
@@ -542,9 +652,11 @@ class FastTonerCore:
             g.factors.statistics_replaced()
         self.weight = sd["weight"]
         self.t = sd["t"]
-        lo_layer = sum(self.layer_counts[:self.rank])
+        lo_layer = self.lo_layer
         for role, info in self.roles.items():
             group = info["group"]
+            if group is None:
+                continue
             names = info["names"][lo_layer: lo_layer + self.per_layers]
             missing = [nm for nm in names if nm not in sd["moments"]]
             if missing:

@@ -82,3 +82,51 @@ def fill_rows(buf: torch.Tensor, seed: int, mean_seed: int = None) -> None:
     for s in range(0, k, step):
         e = min(k, s + step)
         buf[s:e].copy_(torch.randn(e - s, rows, n, device=buf.device, generator=g) + mean)
+
+
+def fill_rows_spectrum(buf: torch.Tensor, seed: int, spectrum: str = "iid", mean_seed: int = None) -> None:
+    """Rows whose population covariance has a chosen spectrum, plus the shared mean direction of ``fill_rows``.
+
+    ``iid``            unit-variance noise: the sample covariance is Marchenko-Pastur around 1 (condition 2-3)
+    ``loguniform:C``   rows = Z diag(sqrt(lambda)) Q^T with Q Haar and lambda log-uniform on [1, C] (scaled to unit mean):
+                       the recipe of the inverse-root kernel sweep, condition C before damping
+    ``spiked:K``       unit noise plus K strong directions of standard deviation 3 .. 20 (eigenvalues 10 .. 400 times
+                       the bulk), as outlier features of a residual stream give
+    Every statistic of the stack shares the population covariance (drawn from ``mean_seed``); the samples differ."""
+    kind, _, arg = spectrum.partition(":")
+    if kind == "iid":
+        fill_rows(buf, seed, mean_seed)
+        return
+    dev = buf.device
+    k, rows, n = buf.shape
+    g = torch.Generator(device=dev).manual_seed(seed)
+    gp = torch.Generator(device=dev).manual_seed(seed if mean_seed is None else mean_seed)
+    mean = torch.randn(1, n, device=dev, generator=gp) * 0.5
+    chunk = max(1, min(rows, (1 << 27) // n))
+    if kind == "loguniform":
+        cond = float(arg)
+        q, _ = torch.linalg.qr(torch.randn(n, n, device=dev, generator=gp))
+        lam = torch.exp(torch.rand(n, device=dev, generator=gp) * torch.log(torch.tensor(cond)))
+        mix = (q * (lam / lam.mean()).sqrt()).T.contiguous()        # diag(sqrt(lambda)) Q^T
+        tf32 = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True                # input synthesis only
+        try:
+            for s in range(k):
+                for r0 in range(0, rows, chunk):
+                    r1 = min(rows, r0 + chunk)
+                    z = torch.randn(r1 - r0, n, device=dev, generator=g)
+                    buf[s, r0:r1].copy_(z @ mix + mean)
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = tf32
+    elif kind == "spiked":
+        spikes = int(arg)
+        d, _ = torch.linalg.qr(torch.randn(n, spikes, device=dev, generator=gp))
+        scale = torch.linspace(3.0, 20.0, spikes, device=dev)
+        for s in range(k):
+            for r0 in range(0, rows, chunk):
+                r1 = min(rows, r0 + chunk)
+                z = torch.randn(r1 - r0, n, device=dev, generator=g)
+                z += (torch.randn(r1 - r0, spikes, device=dev, generator=g) * scale) @ d.T
+                buf[s, r0:r1].copy_(z + mean)
+    else:
+        raise ValueError("spectrum is 'iid', 'loguniform:<condition>' or 'spiked:<directions>'")
