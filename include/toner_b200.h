@@ -114,6 +114,9 @@ typedef struct toner_gemm_desc {
   int64_t split_ld, split_bs, split_plane;
   float split0_scale, split1_scale, split1_aff_a, split1_aff_b;
   uint32_t* maxres;         /* optional per-batch accumulator: max |[r==c] - d| as FP32 bits */
+  int32_t upper_d;          /* with tri + mirror: write the FP32 result d on and above the diagonal only (the 16-bit copy
+                               and the operand planes are still mirrored) -- for a result whose FP32 form is read back
+                               as the upper-triangle `c` of another symmetric product and nowhere else */
 } toner_gemm_desc;
 
 int toner_gemm(const toner_gemm_desc* desc, void* stream);
@@ -155,13 +158,15 @@ int toner_gather_rows(const void* x, int32_t x_is_fp32, int32_t batch, int32_t s
  *   TONER_CAPTURE_RMSNORM   out = bf16(x * rsqrt(mean(x^2) + eps)); dst = bf16(float(bf16(w)) * float(out))
  *                           (a = x BF16, b = w FP32 of `width` elements: the model's BF16-residual RMSNorm)
  *   TONER_CAPTURE_SILU_MUL  dst = bf16(g * (1 / (1 + exp(-g))) * u) in FP32     (a = g, b = u, both BF16, same strides)
+ *   TONER_CAPTURE_COPY_F32  dst = bf16(a row)                                   (a FP32: the input of a projection that
+ *                           runs under BF16 autocast, rounded as autocast rounds it; strides in FP32 elements)
  * The job table is passed twice: `jobs_host` is validated, `jobs_device` (the same n_jobs entries in device memory)
  * is what the kernel reads; a caller keeps both for as long as the tensors' addresses repeat.  `at` and `idx` are
  * DEVICE int64 arrays of batch*positions and positions entries (not range-checked).  Widths and strides in
  * elements, multiples of 8; pointers 16-byte aligned; destination buffers are (capacity, width) BF16, contiguous.
  * Replaces capture_rows / capture_recomputed and their kernels _gather_rows, _norm_rows, _silu_mul_rows
  * (reproduce/marin/ops.py:10-27,30-54,63-100,107-163), four launches per micro-batch there. */
-enum { TONER_CAPTURE_COPY = 0, TONER_CAPTURE_RMSNORM = 1, TONER_CAPTURE_SILU_MUL = 2 };
+enum { TONER_CAPTURE_COPY = 0, TONER_CAPTURE_RMSNORM = 1, TONER_CAPTURE_SILU_MUL = 2, TONER_CAPTURE_COPY_F32 = 3 };
 typedef struct toner_capture_job {
   const void* a;
   const void* b;
@@ -253,12 +258,22 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
  *                  exceeds what the finishing series was cut for (by 15 % + 1e-3).  The caller recomputes such a
  *                  statistic with the bound that always holds.  resid_out (DEVICE, optional, k floats) receives the
  *                  estimate.  With lower_is_estimate = 0 the call is toner_inv_roots_ex (plus tracking).
+ *   deflate, deflate_rank, deflated_out
+ *                  `deflate` (DEVICE, k * 8 * n floats, kept by the caller between calls; optional): eight vector slots
+ *                  per statistic for the dominant eigen-directions.  With it the engine looks for deflate_rank (1..8)
+ *                  directions instead of one, by block power iteration with Rayleigh-Ritz (one pass over the statistic
+ *                  per sweep whatever the rank; three sweeps from the buffer's vectors, six from fixed ones when 256 is
+ *                  added to deflate_rank), and deflates those that converged (residual below 1e-5) and stand above 8x
+ *                  the mean of everything else, in descending order.  deflated_out (DEVICE, optional, k ints): how many.
+ *                  Outlier features of an activation statistic are such directions; each one deflated lowers
+ *                  lambda_max(A') and with it the number of Newton steps.
  * The upper end needs no estimate: norm_out is a certified bound, the smallest of ||A'||_F times ||P^2||_F^(1/2),
  * ||P^4||_F^(1/4), ||P^8||_F^(1/8) (three single-pass squarings). */
 int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
                             float lower, int32_t lower_is_estimate, float* root_lo, float* root_hi, float* fro2_lo,
                             int32_t* status, float* norm_out, float* track, float* lmin_out, float* resid_out,
-                            int32_t track_sweeps, void* workspace, size_t workspace_bytes, void* stream);
+                            int32_t track_sweeps, float* deflate, int32_t deflate_rank, int32_t* deflated_out,
+                            void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------ Newton-Schulz polar iteration
  * x = u / (||u||_F + eps); `steps` times  A = x x^T (on the short side),  x <- a x + (b A + c A A) x  with

@@ -133,6 +133,22 @@ def test_capture_rows_with_mixed_widths_and_strided_sources(capture):
         assert torch.equal(got.cpu(), ref)
 
 
+def test_fp32_sources_are_rounded_like_autocast(capture):
+    """Copied rows may come from FP32 tensors (a projection's input as the fast optimizers' hooks see it, before
+    autocast casts it): the rows are rounded to BF16 on the way, bit for bit what .to(bfloat16) gives."""
+    g = torch.Generator().manual_seed(8)
+    x32 = torch.randn(3, 40, 64, generator=g).cuda()
+    x16 = torch.randn(3, 40, 128, generator=g).to(torch.bfloat16).cuda()
+    idx = torch.tensor([0, 3, 4, 17, 39], device="cuda")
+    rows = 3 * idx.numel()
+    at = (torch.arange(rows, device="cuda") + 2)
+    bufs = [torch.zeros(rows + 4, 64, dtype=torch.bfloat16, device="cuda"), torch.zeros(rows + 4, 128, dtype=torch.bfloat16, device="cuda")]
+    capture.capture_rows([x32, x16], bufs, at, idx)
+    assert torch.equal(bufs[0][2:2 + rows], x32[:, idx].reshape(rows, 64).to(torch.bfloat16))
+    assert torch.equal(bufs[1][2:2 + rows], x16[:, idx].reshape(rows, 128))
+    assert float(bufs[0][:2].abs().max()) == 0 and float(bufs[0][2 + rows:].abs().max()) == 0
+
+
 def test_bad_arguments_are_refused(capture):
     from toner_b200._lib import TonerError
     x = torch.zeros(1, 16, 12, dtype=torch.bfloat16, device="cuda")      # width not a multiple of 8
@@ -140,7 +156,7 @@ def test_bad_arguments_are_refused(capture):
     at, idx = torch.arange(4, device="cuda"), torch.arange(4, device="cuda")
     with pytest.raises(TonerError):
         capture.capture_rows([x], [buf], at, idx)
-    y = torch.zeros(1, 16, 16, dtype=torch.float32, device="cuda")
+    y = torch.zeros(1, 16, 16, dtype=torch.float16, device="cuda")        # neither BF16 nor FP32
     with pytest.raises(ValueError):
         capture.capture_rows([y], [torch.zeros(4, 16, dtype=torch.bfloat16, device="cuda")], at, idx)
     z = torch.zeros(1, 16, 16, dtype=torch.bfloat16, device="cuda")

@@ -183,22 +183,25 @@ def test_dominant_direction_is_deflated(ops):
 
 
 def test_repair_round_when_the_bound_no_longer_holds(ops):
-    """FactorSet: a statistic that grows a dominant direction between two steps breaks the bound derived from the
-    previous step; the device flags it, the repair round refactors it with the bound that always holds, and no
-    eigendecomposition fallback is needed."""
+    """FactorSet: between two steps one statistic is replaced by a far worse conditioned one, so the spectrum estimate
+    carried over from the previous step is two orders of magnitude too high for it; the verification after the chain
+    flags it, the repair round refactors it with the bound that always holds, and no eigendecomposition fallback is
+    needed.  Two strong directions appearing in the other statistic break nothing: they are found and deflated."""
     from toner_b200 import core
     n = 512
     f = core.FactorSet(2, n, torch.device("cuda"), (0.5, 0.125), DAMPING)
     f.ema.copy_(torch.stack([spd(n, 10.0, 1), spd(n, 10.0, 2)]))
     f.compute()
-    assert f.finish() == 0 and f.lower > 0
-    # two strong directions: only one can be deflated, so ||A'||_F jumps far above what the bound allows for
+    assert f.finish() == 0 and f.lower > 0 and f.lower_is_estimate
     g = torch.Generator().manual_seed(3)
     u, v = torch.randn(n, 1, generator=g), torch.randn(n, 1, generator=g)
-    f.ema[1] += ((u @ u.T) + (v @ v.T)).cuda() * 50.0
+    f.ema[0] += ((u @ u.T) + (v @ v.T)).cuda() * 50.0
+    f.ema[1].copy_(spd(n, 3e3, 5))
     f.compute()
     assert f.finish() == 0
-    assert f.repairs == 1 and f.fallbacks == 0
+    assert f.repairs == 1 and f.fallbacks == 0 and f.bound_failures == 1
+    assert f.deflated_host.tolist()[0] == 2
+    assert not f.lower_is_estimate and f.estimate_backoff == 8     # estimates are suspended for a while
     for b in range(2):
         c = f.ema[b].cpu()
         assert orc.rel_fro(f.root_lo[b].cpu(), orc.inverse_root_truth(c, 0.125, DAMPING)) < 5e-4
@@ -330,3 +333,41 @@ def test_fifty_steps_on_a_drifting_statistic(ops):
     assert worst_ratio < 2.0, worst_ratio
     print(f"Newton steps per factorisation over 50 steps: first {counts[0]}, then {sorted(set(counts[1:]))}; "
           f"warm / cold error ratio at most {worst_ratio:.2f}")
+
+
+def test_block_deflation_of_outlier_directions(ops):
+    """Five strong directions on top of a flat spectrum (outlier features): with vector slots the engine finds them by
+    block power iteration, deflates all five, and the norm it reports -- the bound of what is left -- drops from the
+    second-largest eigenvalue to the bulk's edge; the roots stay exact, and a second call started from the vectors of
+    the first finds the same five with half the sweeps."""
+    n, rows, k = 512, 8192, 2
+    g = torch.Generator().manual_seed(5)
+    stats = []
+    for s in range(k):
+        x = torch.randn(rows, n, generator=g)
+        d, _ = torch.linalg.qr(torch.randn(n, 5, generator=g))
+        x = x + (torch.randn(rows, 5, generator=g) * torch.tensor([4.0, 6.0, 9.0, 12.0, 16.0])) @ d.T
+        stats.append(x.T @ x / rows)
+    ema = torch.stack(stats).cuda()
+    single_norms = torch.zeros(k, device="cuda")
+    ops.inv_roots(ema, DAMPING, 8, 4, norms=single_norms)                      # one direction deflated (the old way)
+    norms, lmin = torch.zeros(k, device="cuda"), torch.zeros(k, device="cuda")
+    track, vectors = torch.zeros(k, n, device="cuda"), torch.zeros(k, 8, n, device="cuda")
+    count = torch.zeros(k, device="cuda", dtype=torch.int32)
+    for restart in (True, False):
+        lo, hi, _, st = ops.inv_roots(ema, DAMPING, 8, 4, norms=norms, track=track, lmin=lmin,
+                                      track_sweeps=12 if restart else 4, track_restart=restart, deflate=vectors,
+                                      deflate_rank=8, deflate_restart=restart, deflated=count)
+        ops.assert_healthy()
+        assert st.tolist() == [0] * k
+        assert count.tolist() == [5] * k, count.tolist()
+        assert (norms < 0.1 * single_norms).all(), (norms.tolist(), single_norms.tolist())
+        for b in range(k):
+            c = ema[b].cpu()
+            assert orc.rel_fro(lo[b].cpu(), orc.inverse_root_truth(c, 0.125, DAMPING)) < 1e-4
+            assert orc.rel_fro(hi[b].cpu(), orc.inverse_root_truth(c, 0.5, DAMPING)) < 5e-4
+            assert torch.equal(lo[b], lo[b].T)
+            # the kept vectors are the statistic's top eigenvectors
+            top = torch.linalg.eigh(c.double())[1][:, -5:]
+            inside = (vectors[b, :5].double().cpu() @ top).norm(dim=1)
+            assert (inside > 1 - 1e-6).all()

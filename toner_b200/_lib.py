@@ -54,6 +54,7 @@ class GemmDesc(C.Structure):
         ("split_ld", C.c_int64), ("split_bs", C.c_int64), ("split_plane", C.c_int64),
         ("split0_scale", C.c_float), ("split1_scale", C.c_float), ("split1_aff_a", C.c_float), ("split1_aff_b", C.c_float),
         ("maxres", C.c_void_p),
+        ("upper_d", C.c_int32),
     ]
 
 
@@ -79,7 +80,7 @@ SIGNATURES = {
     "toner_inv_roots_finish_order_for": (C.c_int, [_f32, _i32, _i32]),
     "toner_inv_roots_ex": (C.c_int, [_vp, _i32, _i32, _f32, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "toner_inv_roots_tracked": (C.c_int, [_vp, _i32, _i32, _f32, _i32, _i32, _i32, _f32, _i32, _vp, _vp, _vp, _vp, _vp, _vp,
-                                          _vp, _vp, _i32, _vp, _sz, _vp]),
+                                          _vp, _vp, _i32, _vp, _i32, _vp, _vp, _sz, _vp]),
     "toner_ns_polar_workspace_bytes": (C.c_size_t, [_i32, _i32, _i32]),
     "toner_ns_polar": (C.c_int, [_vp, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _sz, _vp]),
     "toner_sumsq_scratch_bytes": (C.c_size_t, [_i32]),

@@ -20,14 +20,17 @@ from . import _lib
 from ._lib import check
 from .ops import _need_cuda, _stream
 
-COPY, RMSNORM, SILU_MUL = 0, 1, 2
+COPY, RMSNORM, SILU_MUL, COPY_F32 = 0, 1, 2, 3
 _TABLES: Dict[tuple, Tuple[object, torch.Tensor]] = {}
 _MAX_TABLES = 64
 
 
 def _job(kind: int, a: torch.Tensor, b, dst: torch.Tensor) -> Tuple[int, int, int, int, int, int, int]:
-    if a.dtype != torch.bfloat16 or a.ndim != 3 or a.stride(-1) != 1:
-        raise ValueError("capture sources are (batch, seq, width) BF16 tensors with contiguous features")
+    if kind == COPY and a.dtype == torch.float32:
+        kind = COPY_F32                                  # rounded to BF16 on the way, as autocast would
+    if a.dtype != (torch.float32 if kind == COPY_F32 else torch.bfloat16) or a.ndim != 3 or a.stride(-1) != 1:
+        raise ValueError("capture sources are (batch, seq, width) BF16 tensors with contiguous features "
+                         "(copied rows may also come from FP32 tensors)")
     width = a.size(-1)
     if dst.dtype != torch.bfloat16 or dst.ndim != 2 or dst.size(1) != width or not dst.is_contiguous():
         raise ValueError("capture destinations are contiguous (capacity, width) BF16 row buffers")
@@ -65,7 +68,8 @@ def _run(key: tuple, build, batch: int, at: torch.Tensor, idx: torch.Tensor, eps
 
 def capture_rows(srcs: Sequence[torch.Tensor], bufs: Sequence[torch.Tensor], at: torch.Tensor, idx: torch.Tensor) -> None:
     """bufs[i][at[b P + p]] = srcs[i][b, idx[p]] for BF16 inputs srcs[i] (B, T, D_i) and row buffers (rows, D_i)
-    (capture_rows, reproduce/marin/ops.py:30-54)."""
+    (capture_rows, reproduce/marin/ops.py:30-54).  FP32 inputs are rounded to BF16 (the fast optimizers' hooks see a
+    projection's input before autocast casts it)."""
     if len(srcs) != len(bufs) or not srcs:
         raise ValueError("one row buffer per source")
     batch = srcs[0].size(0)

@@ -11,6 +11,7 @@
 //   kind 0  copy
 //   kind 1  out = bf16(x * rsqrt(mean(x^2) + eps));  row = bf16(float(bf16(w)) * float(out))      (x BF16, w FP32)
 //   kind 2  row = bf16(g * (1 / (1 + exp(-g))) * u)   in FP32 with one rounding                    (g, u BF16)
+//   kind 3  row = bf16(a)                              the source is FP32 (what autocast would round)
 #include <cuda_bf16.h>
 
 #include "runtime.cuh"
@@ -45,7 +46,16 @@ __global__ void __launch_bounds__(32 * kCaptureWarps) capture_rows_kernel(const 
   const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(job.a) + off;
   __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(job.dst) + __ldg(at + r) * (long long)D;
 
-  if (job.kind == TONER_CAPTURE_COPY) {
+  if (job.kind == TONER_CAPTURE_COPY_F32) {
+    const float* af = static_cast<const float*>(job.a) + off;
+    for (int c = 8 * lane; c < D; c += 256) {
+      const float4 lo = __ldg(reinterpret_cast<const float4*>(af + c)), hi = __ldg(reinterpret_cast<const float4*>(af + c + 4));
+      Bf16x8 y;
+      y.v[0] = __floats2bfloat162_rn(lo.x, lo.y); y.v[1] = __floats2bfloat162_rn(lo.z, lo.w);
+      y.v[2] = __floats2bfloat162_rn(hi.x, hi.y); y.v[3] = __floats2bfloat162_rn(hi.z, hi.w);
+      store8(dst + c, y);
+    }
+  } else if (job.kind == TONER_CAPTURE_COPY) {
     int c = 8 * lane;
     for (; c + 768 < D; c += 1024) {  // four independent 16-byte loads in flight per lane
       const Bf16x8 x0 = load8(a + c), x1 = load8(a + c + 256), x2 = load8(a + c + 512), x3 = load8(a + c + 768);
@@ -129,8 +139,9 @@ extern "C" int toner_capture(const toner_capture_job* jobs_device, const toner_c
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   for (int j = 0; j < n_jobs; ++j) {
     const toner_capture_job& q = jobs_host[j];
-    if (q.kind < TONER_CAPTURE_COPY || q.kind > TONER_CAPTURE_SILU_MUL) return fail(kErrArg, "capture: unknown kind");
-    if (!q.a || !q.dst || (q.kind != TONER_CAPTURE_COPY && !q.b)) return fail(kErrArg, "capture: null pointer in a job");
+    if (q.kind < TONER_CAPTURE_COPY || q.kind > TONER_CAPTURE_COPY_F32) return fail(kErrArg, "capture: unknown kind");
+    const bool copies = q.kind == TONER_CAPTURE_COPY || q.kind == TONER_CAPTURE_COPY_F32;
+    if (!q.a || !q.dst || (!copies && !q.b)) return fail(kErrArg, "capture: null pointer in a job");
     if (q.width <= 0 || q.width % 8 || q.batch_stride % 8 || q.row_stride % 8)
       return fail(kErrUnsupported, "capture: width and strides must be multiples of 8 elements");
     if (!al16(q.a) || !al16(q.dst) || (q.b && !al16(q.b))) return fail(kErrUnsupported, "capture: pointers must be 16-byte aligned");

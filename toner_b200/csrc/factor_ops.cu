@@ -353,6 +353,280 @@ __global__ void __launch_bounds__(256) rank1_update_kernel(float* __restrict__ a
   }
 }
 
+
+// ------------------------------------------------------------------ deflation of several dominant directions
+// Statistics of real activations often have a handful of directions far above the rest (outlier features), not just
+// the mean.  Block power iteration with Rayleigh-Ritz finds r <= kMaxDeflate of them at the cost of one pass over the
+// statistic per sweep, whatever r is, and converges with the ratio of the (r+1)-th eigenvalue to the wanted one, so
+// close pairs among the dominant ones do not slow it down; the vectors are kept by the caller between calls.
+// Vectors are stored vector-major: v[(b * vstride + j) * n + c].
+constexpr int kMaxDeflate = 8;
+
+// Y_j = A v_j, j < r: one pass over A (each warp takes two rows), FP64 accumulation
+__global__ void __launch_bounds__(256) block_gemv_kernel(const float* __restrict__ a, const float* __restrict__ v,
+                                                         float* __restrict__ y, int n, int r, int vstride) {
+  const int b = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = (blockIdx.x * 8 + warp) * 2;
+  if (row0 >= n) return;
+  const bool two = row0 + 1 < n;
+  const float* A0 = a + ((long long)b * n + row0) * n;
+  const float* A1 = two ? A0 + n : A0;
+  const float* V = v + (long long)b * vstride * n;
+  double acc0[kMaxDeflate], acc1[kMaxDeflate];
+#pragma unroll
+  for (int j = 0; j < kMaxDeflate; ++j) acc0[j] = acc1[j] = 0.0;
+  for (int c = lane * 4; c < n; c += 128) {
+    const float4 p0 = *reinterpret_cast<const float4*>(A0 + c);
+    const float4 p1 = *reinterpret_cast<const float4*>(A1 + c);
+#pragma unroll
+    for (int j = 0; j < kMaxDeflate; ++j) {
+      if (j < r) {
+        const float4 x = *reinterpret_cast<const float4*>(V + (long long)j * n + c);
+        acc0[j] += (double)p0.x * x.x + (double)p0.y * x.y + (double)p0.z * x.z + (double)p0.w * x.w;
+        acc1[j] += (double)p1.x * x.x + (double)p1.y * x.y + (double)p1.z * x.z + (double)p1.w * x.w;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kMaxDeflate; ++j) {
+    if (j < r) {
+      double s0 = acc0[j], s1 = acc1[j];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        s0 += __shfl_xor_sync(0xffffffffu, s0, o);
+        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+      }
+      if (lane == 0) {
+        float* Y = y + ((long long)b * vstride + j) * n;
+        Y[row0] = (float)s0;
+        if (two) Y[row0 + 1] = (float)s1;
+      }
+    }
+  }
+}
+
+// Sum over the block of one double per thread; every thread gets the total.  256 threads.
+__device__ __forceinline__ double block_sum(double x, double* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  __syncthreads();  // the previous total has been read by everyone
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = x;
+  __syncthreads();
+  double t = 0.0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) t += red[w];
+  return t;
+}
+__device__ __forceinline__ double block_dot(const float* x, const float* y, int n, double* red) {
+  double s = 0.0;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += (double)x[i] * (double)y[i];
+  return block_sum(s, red);
+}
+
+// Orthonormalise the r vectors of every statistic (modified Gram-Schmidt, in place).  A vector that vanishes against
+// the earlier ones is replaced by nothing: it stays zero and its Ritz value will be zero.
+__device__ void orthonormalise(float* V, int n, int r, double* red) {
+  for (int j = 0; j < r; ++j) {
+    float* vj = V + (long long)j * n;
+    for (int i = 0; i < j; ++i) {
+      const float* vi = V + (long long)i * n;
+      const double d = block_dot(vi, vj, n, red);
+      for (int c = threadIdx.x; c < n; c += blockDim.x) vj[c] = (float)((double)vj[c] - d * (double)vi[c]);
+      __syncthreads();
+    }
+    const double nn = block_dot(vj, vj, n, red);
+    const double inv = nn > 0.0 ? 1.0 / sqrt(nn) : 0.0;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) vj[c] = (float)((double)vj[c] * inv);
+    __syncthreads();
+  }
+}
+
+// start vectors: r different fixed +-1 patterns (cold) or the caller's vectors (warm), orthonormalised
+__global__ void __launch_bounds__(256) block_start_kernel(float* __restrict__ v, int n, int r, int vstride, int cold) {
+  __shared__ double red[8];
+  const int b = blockIdx.x;
+  float* V = v + (long long)b * vstride * n;
+  const float s = rsqrtf((float)n);
+  for (int j = 0; j < r; ++j) {
+    // a slot that holds nothing yet (the rank grew since the last call) starts from its fixed pattern, like a cold one
+    float* vj = V + (long long)j * n;
+    const bool seed = cold || !(block_dot(vj, vj, n, red) > 0.0);
+    if (seed)
+      for (int c = threadIdx.x; c < n; c += blockDim.x)
+        vj[c] = ((((unsigned)c + 977u * (unsigned)j) * 2654435761u) >> (15 + (j & 7))) & 1u ? s : -s;
+    __syncthreads();
+  }
+  orthonormalise(V, n, r, red);
+}
+
+// Rayleigh-Ritz on span(V) with Y = A V (V orthonormal): H = V Y^T, H = Q diag(theta) Q^T (Jacobi, FP64, one thread),
+// V <- Q^T V, Y <- Q^T Y (Ritz vectors, descending theta), res_j = ||Y_j - theta_j V_j|| / |theta_j|.  Unless this is
+// the last sweep, V is then replaced by the orthonormalised Y (one more step of the power iteration).
+__global__ void __launch_bounds__(256) ritz_kernel(float* __restrict__ v, float* __restrict__ y, int n, int r, int vstride,
+                                                   int last, float* __restrict__ theta, float* __restrict__ res) {
+  __shared__ double red[8];
+  __shared__ double H[kMaxDeflate][kMaxDeflate], Q[kMaxDeflate][kMaxDeflate], lam[kMaxDeflate];
+  const int b = blockIdx.x;
+  float* V = v + (long long)b * vstride * n;
+  float* Y = y + (long long)b * vstride * n;
+  for (int i = 0; i < r; ++i)
+    for (int j = 0; j <= i; ++j) {
+      const double h = 0.5 * (block_dot(V + (long long)i * n, Y + (long long)j * n, n, red) +
+                              block_dot(V + (long long)j * n, Y + (long long)i * n, n, red));
+      if (threadIdx.x == 0) H[i][j] = H[j][i] = h;
+    }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < r; ++i)
+      for (int j = 0; j < r; ++j) Q[i][j] = i == j ? 1.0 : 0.0;
+    for (int sweep = 0; sweep < 12; ++sweep) {
+      double off = 0.0;
+      for (int pp = 0; pp < r; ++pp)
+        for (int qq = pp + 1; qq < r; ++qq) off += H[pp][qq] * H[pp][qq];
+      if (!(off > 0.0)) break;
+      for (int pp = 0; pp < r; ++pp)
+        for (int qq = pp + 1; qq < r; ++qq) {
+          const double apq = H[pp][qq];
+          if (apq == 0.0) continue;
+          const double tau = (H[qq][qq] - H[pp][pp]) / (2.0 * apq);
+          const double t = (tau >= 0.0 ? 1.0 : -1.0) / (fabs(tau) + sqrt(1.0 + tau * tau));
+          const double cs = 1.0 / sqrt(1.0 + t * t), sn = t * cs;
+          for (int k = 0; k < r; ++k) {  // columns pp, qq of H and Q
+            const double hp = H[k][pp], hq = H[k][qq];
+            H[k][pp] = cs * hp - sn * hq;
+            H[k][qq] = sn * hp + cs * hq;
+            const double qp = Q[k][pp], qv = Q[k][qq];
+            Q[k][pp] = cs * qp - sn * qv;
+            Q[k][qq] = sn * qp + cs * qv;
+          }
+          for (int k = 0; k < r; ++k) {  // rows pp, qq of H
+            const double hp = H[pp][k], hq = H[qq][k];
+            H[pp][k] = cs * hp - sn * hq;
+            H[qq][k] = sn * hp + cs * hq;
+          }
+        }
+    }
+    for (int i = 0; i < r; ++i) lam[i] = H[i][i];
+    for (int i = 0; i < r; ++i) {  // selection sort, descending, columns of Q follow
+      int best = i;
+      for (int j = i + 1; j < r; ++j)
+        if (lam[j] > lam[best]) best = j;
+      if (best != i) {
+        const double t = lam[i]; lam[i] = lam[best]; lam[best] = t;
+        for (int k = 0; k < r; ++k) {
+          const double q = Q[k][i]; Q[k][i] = Q[k][best]; Q[k][best] = q;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {  // rotate both blocks: new vector j = sum_i Q[i][j] old vector i
+    double vv[kMaxDeflate], yy[kMaxDeflate];
+#pragma unroll
+    for (int i = 0; i < kMaxDeflate; ++i) {
+      vv[i] = i < r ? (double)V[(long long)i * n + c] : 0.0;
+      yy[i] = i < r ? (double)Y[(long long)i * n + c] : 0.0;
+    }
+    for (int j = 0; j < r; ++j) {
+      double sv = 0.0, sy = 0.0;
+#pragma unroll
+      for (int i = 0; i < kMaxDeflate; ++i) {
+        if (i < r) {
+          sv += Q[i][j] * vv[i];
+          sy += Q[i][j] * yy[i];
+        }
+      }
+      V[(long long)j * n + c] = (float)sv;
+      Y[(long long)j * n + c] = (float)sy;
+    }
+  }
+  __syncthreads();
+  for (int j = 0; j < r; ++j) {
+    const float* vj = V + (long long)j * n;
+    const float* yj = Y + (long long)j * n;
+    double s = 0.0;
+    const double l = lam[j];
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+      const double d = (double)yj[c] - l * (double)vj[c];
+      s += d * d;
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) {
+      theta[b * kMaxDeflate + j] = (float)l;
+      res[b * kMaxDeflate + j] = l > 0.0 ? (float)(sqrt(s) / l) : INFINITY;
+    }
+  }
+  if (!last) {
+    __syncthreads();
+    for (long long i = threadIdx.x; i < (long long)r * n; i += blockDim.x) V[i] = Y[i];
+    __syncthreads();
+    orthonormalise(V, n, r, red);
+  }
+}
+
+// Which of the r Ritz pairs are deflated: in descending order, as long as each has converged and stands above eight
+// times the mean c of everything that would remain; all accepted directions are moved to that common c.
+//   coef[b][j] = -(theta_j - c)  (0 where not deflated)      corr[b][j] = theta_j^(-1/p) - c^(-1/p)
+__global__ void block_decide_kernel(const float* __restrict__ theta, const float* __restrict__ res, int k, int n, int r,
+                                    float damping, int p, float* __restrict__ coef, float* __restrict__ corr,
+                                    int* __restrict__ count) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= k) return;
+  const double tr = (double)n * (1.0 + (double)damping);  // A has unit mean diagonal plus the damping
+  double sum = 0.0;
+  int m = 0;
+  for (int j = 0; j < r && n - (j + 1) > 0; ++j) {
+    const double t = theta[b * kMaxDeflate + j];
+    const double e = res[b * kMaxDeflate + j];
+    const double c = (tr - sum - t) / (double)(n - (m + 1));
+    if (!(isfinite(t) && isfinite(e) && e < 1e-5 && c > 0.0 && t > 8.0 * c)) break;
+    sum += t;
+    ++m;
+  }
+  const double c = (tr - sum) / (double)(n - m);
+  for (int j = 0; j < kMaxDeflate; ++j) {
+    const bool on = j < m;
+    const double t = on ? (double)theta[b * kMaxDeflate + j] : 0.0;
+    coef[b * kMaxDeflate + j] = on ? (float)-(t - c) : 0.f;
+    corr[b * kMaxDeflate + j] = on ? (float)(pow(t, -1.0 / p) - pow(c, -1.0 / p)) : 0.f;
+  }
+  if (count) count[b] = m;
+}
+
+// A_b += sum_j coef[b][j] v_bj v_bj^T  (terms with a zero coefficient are skipped; exact symmetry is kept: the
+// product v_r v_c has the same bits at (r, c) and (c, r) and the terms are added in the same order)
+__global__ void __launch_bounds__(256) rankr_update_kernel(float* __restrict__ a, const float* __restrict__ v,
+                                                           const float* __restrict__ coef, int n, int r, int vstride) {
+  const int b = blockIdx.y;
+  float cf[kMaxDeflate];
+  bool any = false;
+#pragma unroll
+  for (int j = 0; j < kMaxDeflate; ++j) {
+    cf[j] = j < r ? coef[b * kMaxDeflate + j] : 0.f;
+    any = any || cf[j] != 0.f;
+  }
+  if (!any) return;
+  float* A = a + (long long)b * n * n;
+  const float* V = v + (long long)b * vstride * n;
+  const int n4 = n / 4;
+  const long long total = (long long)n * n4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)(i / n4), c = (int)(i - (long long)row * n4) * 4;
+    float4 x = *reinterpret_cast<float4*>(A + (long long)row * n + c);
+#pragma unroll
+    for (int j = 0; j < kMaxDeflate; ++j) {
+      if (cf[j] != 0.f) {
+        const float vr = V[(long long)j * n + row];
+        const float4 vc = *reinterpret_cast<const float4*>(V + (long long)j * n + c);
+        x.x = fmaf(cf[j], vr * vc.x, x.x); x.y = fmaf(cf[j], vr * vc.y, x.y);
+        x.z = fmaf(cf[j], vr * vc.z, x.z); x.w = fmaf(cf[j], vr * vc.w, x.w);
+      }
+    }
+    *reinterpret_cast<float4*>(A + (long long)row * n + c) = x;
+  }
+}
+
 // With P = A' / ||A'||_F:  lambda_max(P) <= ||P^(2^j)||_F^(1 / 2^j) = (sum lambda^(2^(j+1)))^(1 / 2^(j+1))  for every j, and
 // the bound tightens with j (for a flat spectrum it is n^(-1/2) times n^(1/4), n^(1/8), n^(1/16) for j = 1, 2, 3).
 // bound^2 <- bound^2 * t^2 with t the smallest of the three, 3 % above it for the single-pass products' rounding.
@@ -458,8 +732,11 @@ static size_t per_statistic_bytes(int n) {
   return align_up((size_t)n * n * 4, 256) * 8;
 }
 static size_t small_bytes(int chunk, int n) {
-  // sixteen per-statistic scalars, the reduction scratch, and two n-vectors per statistic (power iteration)
-  return align_up((size_t)chunk * 4, 256) * 16 + align_up(sumsq_scratch_bytes(chunk), 256) + 2 * align_up((size_t)chunk * n * 4, 256);
+  // sixteen per-statistic scalars, four blocks of eight scalars per statistic (Ritz values, residuals, deflation
+  // coefficients, root corrections), the reduction scratch, and two blocks of eight n-vectors per statistic
+  // (block power iteration: V and A V)
+  return align_up((size_t)chunk * 4, 256) * 16 + 4 * align_up((size_t)chunk * 32, 256) +
+         align_up(sumsq_scratch_bytes(chunk), 256) + 2 * align_up((size_t)chunk * 8 * n * 4, 256);
 }
 
 // Largest power of two s with s * bound <= 2^14: FP16 planes of s * x then stay a factor four below overflow
@@ -507,13 +784,14 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
                        float lower, float* root_lo, float* root_hi, float* fro2_lo, int32_t* status, float* norm_out,
                        void* workspace, size_t workspace_bytes, void* stream_) {
   return toner_inv_roots_tracked(ema, k, n, damping, p, q, iters, lower, 0, root_lo, root_hi, fro2_lo, status, norm_out,
-                                 nullptr, nullptr, nullptr, 0, workspace, workspace_bytes, stream_);
+                                 nullptr, nullptr, nullptr, 0, nullptr, 0, nullptr, workspace, workspace_bytes, stream_);
 }
 
 int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
                             float lower, int32_t lower_is_estimate, float* root_lo, float* root_hi, float* fro2_lo,
                             int32_t* status, float* norm_out, float* track, float* lmin_out, float* resid_out,
-                            int32_t track_sweeps, void* workspace, size_t workspace_bytes, void* stream_) {
+                            int32_t track_sweeps, float* deflate, int32_t deflate_rank, int32_t* deflated_out,
+                            void* workspace, size_t workspace_bytes, void* stream_) {
   using namespace toner;
   Context* ctx = context();
   if (!ctx) return kErrCuda;
@@ -533,6 +811,10 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
   const bool estimated = lower_is_estimate != 0 && l0 > l_worst;
   if (estimated && !track) return fail(kErrArg, "inv_roots: an estimated bound needs the tracking vectors to verify it");
   if (track_sweeps < 0 || (track_sweeps & ~(63 | 256))) return fail(kErrArg, "inv_roots: track_sweeps is 0..63, plus 256 to start afresh");
+  const int defl_r = deflate ? (deflate_rank & 15) : 0;      // directions the block iteration looks for (0: one, the old way)
+  const bool defl_cold = deflate && (deflate_rank & 256);
+  if (deflate && (defl_r < 1 || defl_r > kMaxDeflate || (deflate_rank & ~(15 | 256))))
+    return fail(kErrArg, "inv_roots: deflate_rank is 1..8, plus 256 to start from fixed vectors");
   // > 0: certified bound, checked against damping / norm per statistic; < 0: estimate, verified after the chain
   const float lower_used = l0 > l_worst ? (estimated ? -(float)l0 : (float)l0) : 0.f;
   if (iters <= 0) iters = default_iterations(l0, p);
@@ -598,11 +880,18 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
     float* ss8 = small(13);
     float* e_est = small(14);
     float* theta = small(15);
-    float* partials = small(16);
-    const size_t vec = align_up((size_t)kc * n * 4, 256);
-    float* pv = reinterpret_cast<float*>(w + sm * 16 + align_up(sumsq_scratch_bytes(kc), 256));
-    float* py = reinterpret_cast<float*>(reinterpret_cast<char*>(pv) + vec);
-    TONER_CUDA(cudaMemsetAsync(w, 0, sm * 16, stream));
+    const size_t sm8 = align_up((size_t)kc * 32, 256);
+    char* wp = w + sm * 16;
+    float* th8 = reinterpret_cast<float*>(wp); wp += sm8;     // Ritz values, residuals, deflation coefficients and
+    float* res8 = reinterpret_cast<float*>(wp); wp += sm8;    // root corrections of the block deflation: eight per statistic
+    float* coef8 = reinterpret_cast<float*>(wp); wp += sm8;
+    float* corr8 = reinterpret_cast<float*>(wp); wp += sm8;
+    float* partials = reinterpret_cast<float*>(wp); wp += align_up(sumsq_scratch_bytes(kc), 256);
+    const size_t vec = align_up((size_t)kc * 8 * n * 4, 256);
+    float* pv = reinterpret_cast<float*>(wp);
+    float* py = reinterpret_cast<float*>(wp + vec);
+    float* dv = deflate ? deflate + (long long)k0 * kMaxDeflate * n : nullptr;
+    TONER_CUDA(cudaMemsetAsync(w, 0, sm * 16 + 4 * sm8, stream));
 
     const float* C = ema + (long long)k0 * nn;
     const int t32 = (n + 31) / 32;
@@ -610,19 +899,38 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
     count_launch();
     damp_kernel<<<dim3(t32, t32, kc), 256, 0, stream>>>(C, A32, n, damping, trace);
     count_launch();
-    // dominant direction: six power-iteration steps, then deflate where they converged
-    power_start_kernel<<<dim3(8, kc), 256, 0, stream>>>(pv, n);
-    count_launch();
-    for (int pi = 0; pi < kPowerSteps; ++pi) {
-      gemv_kernel<<<dim3((n + 7) / 8, kc), 256, 0, stream>>>(A32, pv, py, n);
+    if (defl_r > 0) {
+      // dominant directions: block power iteration with Rayleigh-Ritz on the caller's vectors (six sweeps from fixed
+      // vectors, three from last call's), then deflate those that converged and stand above the rest
+      block_start_kernel<<<kc, 256, 0, stream>>>(dv, n, defl_r, kMaxDeflate, defl_cold ? 1 : 0);
       count_launch();
-      power_norm_kernel<<<kc, 256, 0, stream>>>(pv, py, n, lam, pres);
+      const int sweeps = defl_cold ? 6 : 3;
+      for (int sw = 0; sw < sweeps; ++sw) {
+        block_gemv_kernel<<<dim3((n + 15) / 16, kc), 256, 0, stream>>>(A32, dv, py, n, defl_r, kMaxDeflate);
+        count_launch();
+        ritz_kernel<<<kc, 256, 0, stream>>>(dv, py, n, defl_r, kMaxDeflate, sw == sweeps - 1 ? 1 : 0, th8, res8);
+        count_launch();
+      }
+      block_decide_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(th8, res8, kc, n, defl_r, damping, p, coef8, corr8,
+                                                               deflated_out ? deflated_out + k0 : nullptr);
+      count_launch();
+      rankr_update_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(A32, dv, coef8, n, defl_r, kMaxDeflate);
+      count_launch();
+    } else {
+      // dominant direction: six power-iteration steps, then deflate where they converged
+      power_start_kernel<<<dim3(8, kc), 256, 0, stream>>>(pv, n);
+      count_launch();
+      for (int pi = 0; pi < kPowerSteps; ++pi) {
+        gemv_kernel<<<dim3((n + 7) / 8, kc), 256, 0, stream>>>(A32, pv, py, n);
+        count_launch();
+        power_norm_kernel<<<kc, 256, 0, stream>>>(pv, py, n, lam, pres);
+        count_launch();
+      }
+      deflate_decide_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(lam, pres, kc, n, damping, p, neg_sigma, corr);
+      count_launch();
+      rank1_update_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(A32, pv, neg_sigma, n);
       count_launch();
     }
-    deflate_decide_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(lam, pres, kc, n, damping, p, neg_sigma, corr);
-    count_launch();
-    rank1_update_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(A32, pv, neg_sigma, n);
-    count_launch();
     TONER_CUDA(cudaGetLastError());
     {
       int rc0 = sumsq_det(A32, kc, n, n, n, nn, partials, sumsq_a, stream);
@@ -761,7 +1069,8 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
           rc = sym_product(Xcur, s_x, Mb[1], s_f, o, kPromoteX);
           if (rc) return rc;
           // put the deflated direction back: A^{-1/p} = A'^{-1/p} + (lambda_1^{-1/p} - c^{-1/p}) v v^T
-          rank1_update_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(R, pv, corr, n);
+          if (defl_r > 0) rankr_update_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(R, dv, corr8, n, defl_r, kMaxDeflate);
+          else rank1_update_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(R, pv, corr, n);
           count_launch();
           TONER_CUDA(cudaGetLastError());
           rc = sumsq_det(R, kc, n, n, n, nn, partials, fro_tmp, stream);

@@ -67,6 +67,7 @@ struct GemmParams {
   int d16_fmt;  // 0 FP16, 1 BF16
   int packed;   // C and D are packed upper triangles (row r starts at r*N - r(r-1)/2 - r ... see packed_off)
   int mirror;   // tri: also store the transposed element
+  int upper_d;  // tri + mirror: the FP32 result D is not mirrored (its lower triangle is never read)
   int vec_ok;   // leading dimensions and batch strides allow 16-byte vector access
   float* sumsq;           // per batch: sum of d^2 over the full (mirrored) result
   unsigned int* maxabs;   // per batch: max |d| as FP32 bits
@@ -258,7 +259,7 @@ __device__ __forceinline__ void epilogue_block_vec(const GemmParams& p, const Ep
       const int j = 4 * it + sub;  // source column = target row
       const float v0 = src[j], v1 = src[kEpiStride + j], v2 = src[2 * kEpiStride + j], v3 = src[3 * kEpiStride + j];
       const long long trow = c0 + j;
-      if (e.Db) *reinterpret_cast<float4*>(e.Db + trow * p.ldd + tcol) = make_float4(v0, v1, v2, v3);
+      if (e.Db && !p.upper_d) *reinterpret_cast<float4*>(e.Db + trow * p.ldd + tcol) = make_float4(v0, v1, v2, v3);
       if (e.Hb) *reinterpret_cast<uint2*>(e.Hb + trow * p.ld16 + tcol) = pack4_16(v0, v1, v2, v3, p.d16_fmt);
       if (e.S0b) store_split4(e.S0b + trow * p.s_ld + tcol, p.s_plane, s0 * v0, s0 * v1, s0 * v2, s0 * v3);
       if (e.S1b) store_split4(e.S1b + trow * p.s_ld + tcol, p.s_plane, s1 * v0, s1 * v1, s1 * v2, s1 * v3);
@@ -308,7 +309,7 @@ __device__ __forceinline__ void epilogue_block_scalar(const GemmParams& p, const
         const int c = c0 + j;
         if (c > row) {
           const float v = stage[lane * kEpiStride + j];
-          if (e.Db) e.Db[(long long)c * p.ldd + row] = v;
+          if (e.Db && !p.upper_d) e.Db[(long long)c * p.ldd + row] = v;
           if (e.Hb) e.Hb[(long long)c * p.ld16 + row] = to_bits16(v, p.d16_fmt);
           if (e.S0b) store_split1(e.S0b + (long long)c * p.s_ld + row, p.s_plane, p.s0_scale * v);
           if (e.S1b) store_split1(e.S1b + (long long)c * p.s_ld + row, p.s_plane, p.s1_scale * p.s1_aff_b * v);

@@ -226,6 +226,7 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
   p.D16 = d.d16; p.ld16 = d.ld16; p.d16_bs = d.d16_bs; p.d16_fmt = d.d16_fmt;
   p.packed = d.packed ? 1 : 0;
   p.mirror = d.mirror ? 1 : 0;
+  p.upper_d = (d.upper_d && d.tri && d.mirror) ? 1 : 0;
   auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
   p.vec_ok = !d.packed && (!d.c || (d.ldc % 4 == 0 && d.c_bs % 4 == 0 && al16(d.c))) &&
              (!d.d || (d.ldd % 4 == 0 && d.d_bs % 4 == 0 && al16(d.d))) &&

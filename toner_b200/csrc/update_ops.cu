@@ -283,6 +283,7 @@ int toner_ns_polar(const float* u, int32_t batch, int32_t m, int32_t n, int32_t 
       g.b = g.a;
       g.m = a; g.n = a; g.k = wide ? n : m; g.batch = batch; g.segs = 1; g.fmt = 1;
       g.tri = 1; g.mirror = 1; g.alpha = 1.f;
+      g.upper_d = 1;  // the FP32 Gram is read back only as the upper-triangle C of the polynomial product below
       g.d = gram; g.ldd = a; g.d_bs = aa;
       g.d16 = gram_b; g.ld16 = a; g.d16_bs = aa; g.d16_fmt = 1;
       rc = launch_gemm(g, stream);

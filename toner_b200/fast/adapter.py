@@ -210,6 +210,9 @@ class _FastToner(torch.optim.Optimizer):
         self._hooks = []
         self._device = device
         self._positions = torch.tensor(positions, device=device, dtype=torch.int32)
+        self._positions64 = self._positions.to(torch.int64)
+        self._row_targets = {}
+        self._pending = []
         self._rows_per_microbatch = micro_batch_size * len(positions)
         local_rows = self._rows_per_microbatch * accumulation_steps
         # Optional (not in the reference's adapter; its engine has it as chunk_stats / chunk_wait): the row buffers hold
@@ -283,12 +286,14 @@ class _FastToner(torch.optim.Optimizer):
             self._seen.add((layer, role))
             if previous is None:
                 self._input_signatures[(layer, stat)] = signature
-                lo = (self._microbatches % self._piece_microbatches) * self._rows_per_microbatch
-                dst = getattr(self._buffers[layer], f"input_rows_{stat}")[lo: lo + self._rows_per_microbatch]
+                if x.dtype not in (torch.bfloat16, torch.float32):
+                    x = x.float()
                 if x.stride(2) != 1 or (x.stride(1) * x.element_size()) % 16 or (x.stride(0) * x.element_size()) % 16 \
                         or x.data_ptr() % 16:
                     x = x.contiguous()
-                ops.gather_rows(x, self._positions, dst)   # sampled rows straight into the statistic's row buffer
+                # The sampled rows of every statistic are written by ONE launch when the forward has finished
+                # (_flush_capture): until then the input is kept alive here, as autograd keeps it for backward.
+                self._pending.append((x, getattr(self._buffers[layer], f"input_rows_{stat}")))
 
         return hook
 
@@ -302,6 +307,7 @@ class _FastToner(torch.optim.Optimizer):
             raise RuntimeError("all microbatches of this step are captured; call step() before the next forward")
         self._seen = set()
         self._input_signatures = {}
+        self._pending = []
         if self._microbatches and self._microbatches % self._piece_microbatches == 0:
             self._core.chunk_wait()               # the previous piece's Grams must have read the row buffers
         self._capturing = True
@@ -311,15 +317,29 @@ class _FastToner(torch.optim.Optimizer):
             ran, wanted = len(self._seen), len(self.blocks) * len(self._roles)
             if ran != wanted:
                 raise RuntimeError(f"the captured forward ran {ran} of the {wanted} configured projections")
+            self._flush_capture()
             complete = True
         finally:
             self._capturing = False
+            self._pending = []
             # a failed or partial forward discards every microbatch captured so far in this step
             self._microbatches = self._microbatches + 1 if complete else 0
             if not complete:
                 self._core.discard_pieces()
             elif self._microbatches % self._piece_microbatches == 0 and self._microbatches < self.accumulation_steps:
                 self._core.chunk_stats()          # a full piece that is not the step's last
+
+    def _flush_capture(self):
+        """The sampled rows of this micro-batch, for every layer and statistic, in one launch (toner_capture):
+        row (b, p) of an input goes to row  slot * rows_per_microbatch + b * P + p  of the statistic's buffer."""
+        from .. import capture
+        slot = self._microbatches % self._piece_microbatches
+        at = self._row_targets.get(slot)
+        if at is None:
+            lo = slot * self._rows_per_microbatch
+            at = self._row_targets[slot] = torch.arange(lo, lo + self._rows_per_microbatch, device=self._device,
+                                                        dtype=torch.int64)
+        capture.capture_rows([x for x, _ in self._pending], [b for _, b in self._pending], at, self._positions64)
 
     def begin(self):
         """Start statistics and factors asynchronously after the final forward, before backward."""

@@ -308,14 +308,18 @@ def inv_roots(ema: torch.Tensor, damping: float, p: int, q: int = 1, *, iters: i
               workspace: Optional[torch.Tensor] = None, chunk: Optional[int] = None, lower: float = 0.0,
               norms: Optional[torch.Tensor] = None, lower_is_estimate: bool = False,
               track: Optional[torch.Tensor] = None, lmin: Optional[torch.Tensor] = None,
-              resid: Optional[torch.Tensor] = None, track_sweeps: int = 0, track_restart: bool = False):
+              resid: Optional[torch.Tensor] = None, track_sweeps: int = 0, track_restart: bool = False,
+              deflate: Optional[torch.Tensor] = None, deflate_rank: int = 1, deflate_restart: bool = False,
+              deflated: Optional[torch.Tensor] = None):
     """A^(-1/p) and A^(-q/p) of the damped, trace-normalised statistics (toner_inv_roots_tracked).
 
     ``lower``: a lower bound of the normalised spectrum valid for every statistic (0: the bound that always
     holds); ``norms`` (k,) receives the bound of lambda_max(A'_b) the engine normalised by, from which the next call's
     bound can be derived.  ``track`` (k, n), ``lmin`` (k,), ``track_sweeps``, ``track_restart``, ``lower_is_estimate``,
     ``resid`` (k,): tracking of the smallest eigenvalue between calls and a bound that is an estimate, verified after
-    the chain (see the header).  Returns (root_lo, root_hi or None, fro2_lo, status); nothing is synchronised."""
+    the chain; ``deflate`` (k, 8, n), ``deflate_rank``, ``deflate_restart``, ``deflated`` (k,) int32: several dominant
+    directions found by block power iteration and deflated (see the header).
+    Returns (root_lo, root_hi or None, fro2_lo, status); nothing is synchronised."""
     _need_cuda(ema)
     if ema.ndim == 2:
         ema = ema.unsqueeze(0)
@@ -339,9 +343,13 @@ def inv_roots(ema: torch.Tensor, damping: float, p: int, q: int = 1, *, iters: i
     if track is not None and (track.shape != (k, n) or track.dtype != torch.float32 or not track.is_contiguous()):
         raise ValueError("the tracking vectors are a contiguous FP32 (k, n) tensor")
     sweeps = (int(track_sweeps) & 63) | (256 if track_restart else 0)
+    if deflate is not None and (deflate.shape != (k, 8, n) or deflate.dtype != torch.float32 or not deflate.is_contiguous()):
+        raise ValueError("the deflation vectors are a contiguous FP32 (k, 8, n) tensor")
+    rank = (int(deflate_rank) & 15) | (256 if deflate_restart else 0)
     check(_lib.load().toner_inv_roots_tracked(ema.data_ptr(), k, n, damping, p, q, iters, lower, int(lower_is_estimate),
                                               root_lo.data_ptr(), _ptr(root_hi), fro2_lo.data_ptr(), status.data_ptr(),
                                               _ptr(norms), _ptr(track), _ptr(lmin), _ptr(resid), sweeps,
+                                              _ptr(deflate), rank, _ptr(deflated),
                                               workspace.data_ptr(), workspace.numel(), _stream()),
           "toner_inv_roots_tracked")
     return root_lo, root_hi, fro2_lo, status

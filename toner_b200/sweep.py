@@ -153,6 +153,33 @@ def bench_roots(a):
                                  "single-pass one 1, over the tiles meeting the upper triangle"})
 
 
+def bench_roots_tracked(a):
+    """The factor engine as the optimizers drive it: a first call that learns the spectrum (the bound that always
+    holds, eight vector slots for dominant directions), then repeated calls scheduled from what it learnt."""
+    from . import core
+    f = core.FactorSet(a.k, a.n, torch.device("cuda"), (a.q / a.p, 1.0 / a.p) if a.q > 1 else (1.0 / a.p, 1.0 / a.p), 1e-3)
+    f.ema.copy_(spd_stack(a.k, a.n, a.cond))
+    for _ in range(3):
+        f.compute()
+        f.finish()
+
+    def fn():
+        f.compute()
+        f.finish()
+
+    ms, best = timed(fn, 1, a.reps, False)
+    log2p, log2q = int(math.log2(a.p)), int(math.log2(a.q))
+    split = (f.iterations - 1) * (log2p + 2) + log2q
+    single = f.finish_order - 1
+    flops = a.k * (split + single) * 2 * a.n ** 3
+    return report("inv_roots_tracked", {"k": a.k, "n": a.n, "p": a.p, "q": a.q, "cond": a.cond}, ms, best, flops=flops,
+                  extra={"iterations": f.iterations, "finish_order": f.finish_order, "split_products": split,
+                         "single_pass_products": single, "deflated": int(f.deflated_host.max()),
+                         "estimate": bool(f._estimate_in_flight), "repairs": f.repairs,
+                         "note": "includes the host wait for the flags; three single-pass squarings for the norm bound, "
+                                 "the block power iteration and the tracking sweeps are not counted as work"})
+
+
 def bench_ns(a):
     g = torch.Generator(device="cuda").manual_seed(0)
     u = torch.randn(a.batch, a.m, a.n, device="cuda", generator=g)
@@ -255,7 +282,7 @@ def bench_capture(a):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("kernel", choices=["syrk", "roots", "ns", "gemm", "ema", "update", "capture", "all"])
+    ap.add_argument("kernel", choices=["syrk", "roots", "tracked", "ns", "gemm", "ema", "update", "capture", "all", "large"])
     ap.add_argument("--rows", type=int, default=65536)
     ap.add_argument("--n", type=int, default=2048)
     ap.add_argument("--m", type=int, default=2048)
@@ -281,12 +308,26 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("the kernel sweep needs a CUDA device (there is no CPU path)")
     torch.cuda.set_device(0)
-    table = {"syrk": bench_syrk, "roots": bench_roots, "ns": bench_ns, "gemm": bench_gemm, "ema": bench_ema,
-             "update": bench_update, "capture": bench_capture}
+    table = {"syrk": bench_syrk, "roots": bench_roots, "tracked": bench_roots_tracked, "ns": bench_ns, "gemm": bench_gemm,
+             "ema": bench_ema, "update": bench_update, "capture": bench_capture}
+    import copy
+    if a.kernel == "large":
+        # the upper end of the sweep: a million rows, width 8192, condition 1e2 .. 1e6 (a few GB per case)
+        for rows, n, k in ((1048576, 768, 2), (1048576, 2048, 1), (262144, 4096, 1), (262144, 8192, 1)):
+            b = copy.copy(a); b.rows, b.n, b.k = rows, n, k
+            bench_syrk(b)
+            torch.cuda.empty_cache()
+        for n, k, cond in ((2048, 4, 1e2), (2048, 4, 1e6), (8192, 1, 1e4)):
+            b = copy.copy(a); b.n, b.k, b.cond, b.p, b.q = n, k, cond, 8, 4
+            bench_roots(b)
+            bench_roots_tracked(b)
+            torch.cuda.empty_cache()
+        b = copy.copy(a); b.m, b.n, b.batch = 8192, 32768, 1
+        bench_ns(b)
+        return
     if a.kernel != "all":
         table[a.kernel](a)
         return
-    import copy
     for rows, n, k in ((65536, 768, 8), (65536, 2048, 4), (262144, 2048, 1), (65536, 4096, 2), (65536, 8192, 1)):
         b = copy.copy(a); b.rows, b.n, b.k = rows, n, k
         bench_syrk(b)
