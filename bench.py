@@ -224,6 +224,9 @@ def run_fast(args, w: Workload) -> None:
     core = opt._core
     if args.sm_reserve is not None and world > 1:
         core.sm_reserve = int(args.sm_reserve)
+    if args.single_deflation:
+        for g in core.groups.values():
+            g.factors.block_deflation = False
     gen = torch.Generator(device=dev).manual_seed(99)   # gradients are replicated (already synchronised)
     for p in core.params:
         p.grad = torch.randn(p.shape, device=dev, generator=gen) * 1e-3
@@ -330,7 +333,7 @@ def run_fast(args, w: Workload) -> None:
     by_spectrum = {}
     extra = [s for s in (args.extra_spectra.split(",") if args.extra_spectra else []) if s and s != args.spectrum]
     for spectrum in extra:
-        r = measure(spectrum, max(3, args.warmup), max(1, min(args.steps, 2)))
+        r = measure(spectrum, max(5, args.warmup), max(1, min(args.steps, 2)))   # the deflation block widens over a few steps
         by_spectrum[spectrum] = {
             "ms": round(r["ms"], 3), "phases_ms": {k: round(v, 2) for k, v in r["phases"].items()},
             "newton_steps": {k: c["newton_steps"] for k, c in r["counts"].items()},
@@ -646,6 +649,8 @@ def main() -> None:
     ap.add_argument("--no-capture", action="store_true", help="skip the row-capture timing")
     ap.add_argument("--sm-reserve", type=int, default=None,
                     help="SMs the GEMMs leave to NCCL while a collective overlaps them (several ranks; default: the engine's)")
+    ap.add_argument("--single-deflation", action="store_true",
+                    help="factor engine deflates one dominant direction only (A/B against the block power iteration)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (for profiler runs)")
     args = ap.parse_args()
     w = workload_of(args)

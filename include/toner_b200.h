@@ -262,9 +262,10 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
  *                  `deflate` (DEVICE, k * 8 * n floats, kept by the caller between calls; optional): eight vector slots
  *                  per statistic for the dominant eigen-directions.  With it the engine looks for deflate_rank (1..8)
  *                  directions instead of one, by block power iteration with Rayleigh-Ritz (one pass over the statistic
- *                  per sweep whatever the rank; three sweeps from the buffer's vectors, six from fixed ones when 256 is
+ *                  per sweep whatever the rank; four sweeps from the buffer's vectors, eight from fixed ones when 256 is
  *                  added to deflate_rank), and deflates those that converged (residual below 1e-5) and stand above 8x
- *                  the mean of everything else, in descending order.  deflated_out (DEVICE, optional, k ints): how many.
+ *                  the mean of everything else, in descending order.  deflated_out (DEVICE, optional, k ints): how many, in
+ *                  bits 0..7; bits 8..15: how many Ritz values stand above that mark whether converged or not.
  *                  Outlier features of an activation statistic are such directions; each one deflated lowers
  *                  lambda_max(A') and with it the number of Newton steps.
  * The upper end needs no estimate: norm_out is a certified bound, the smallest of ||A'||_F times ||P^2||_F^(1/2),

@@ -103,11 +103,13 @@ class FactorSet:
         self.lmin_host = torch.zeros(k, dtype=torch.float32).pin_memory()
         self.track_restart = True        # the vectors hold nothing yet (or the statistics were replaced)
         # Dominant directions (outlier features): eight vector slots per statistic, found by block power iteration and
-        # deflated where they stand out.  The engine looks for one more direction than it deflated last time.
+        # deflated where they stand out.  The block is two vectors wider than the number of directions that looked like
+        # outliers last time (a block wider than the group of outliers is what makes close outliers converge).
         self.deflate = torch.zeros(k, 8, n, device=device, dtype=torch.float32)
         self.deflated = torch.zeros(k, device=device, dtype=torch.int32)
         self.deflated_host = torch.zeros(k, dtype=torch.int32).pin_memory()
-        self.deflate_rank = 2
+        self.deflate_rank = 4
+        self.block_deflation = True      # False: the engine's own single-vector deflation (one dominant direction)
         self.lower_is_estimate = False
         self.estimate_backoff = 0        # steps left during which only certified bounds are used (after a bound failed)
         self.bound_failures = 0
@@ -169,7 +171,8 @@ class FactorSet:
                       track=self.track if self.tracking else None, lmin=self.lmin if self.tracking else None,
                       track_sweeps=(12 if self.track_restart else 4) if self.tracking else 0,
                       track_restart=self.track_restart,
-                      deflate=self.deflate if self.tracking else None, deflate_rank=self.deflate_rank,
+                      deflate=self.deflate if self.tracking and self.block_deflation else None,
+                      deflate_rank=self.deflate_rank,
                       deflate_restart=self.track_restart, deflated=self.deflated if self.tracking else None)
         self.track_restart = False
         self._estimate_in_flight = self.lower_is_estimate
@@ -214,8 +217,9 @@ class FactorSet:
         # bound that always holds; an estimate that failed its verification is not tried again for eight steps.
         top = float(self.norms_host.max())
         worst = self.damping / (self.n * (1.0 + self.damping))
-        if self.tracking:   # room for as many directions again as the statistic with the most outliers had
-            self.deflate_rank = max(2, min(8, 2 * int(self.deflated_host.max())))
+        if self.tracking and self.block_deflation:
+            candidates = int((self.deflated_host >> 8).max())
+            self.deflate_rank = max(2, min(8, candidates + 2))
         self.lower, self.lower_is_estimate = 0.0, False
         if getattr(self, "_estimate_in_flight", False) and any(c in (1, 4) for c in codes):
             self.estimate_backoff = 8     # (a gross overestimate already fails the convergence test, status 1)

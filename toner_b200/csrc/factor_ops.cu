@@ -251,11 +251,14 @@ __global__ void __launch_bounds__(256) gemv_kernel(const float* __restrict__ a, 
   if (row >= n) return;
   const float* A = a + ((long long)b * n + row) * n;
   const float* X = v + (long long)b * n;
+  // Four products at a time are summed in FP32 (their rounding, 6e-8 of the partial sum, is that of the FP32 result
+  // itself) and the partial sums in FP64: one conversion per four elements instead of eight -- conversions to FP64 run
+  // at a quarter of the FP64 rate and were what bound this kernel.
   double acc = 0.0;
   for (int c = lane * 4; c < n; c += 128) {
     const float4 av = *reinterpret_cast<const float4*>(A + c);
     const float4 xv = *reinterpret_cast<const float4*>(X + c);
-    acc += (double)av.x * xv.x + (double)av.y * xv.y + (double)av.z * xv.z + (double)av.w * xv.w;
+    acc += (double)fmaf(av.x, xv.x, fmaf(av.y, xv.y, fmaf(av.z, xv.z, av.w * xv.w)));
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -362,46 +365,58 @@ __global__ void __launch_bounds__(256) rank1_update_kernel(float* __restrict__ a
 // Vectors are stored vector-major: v[(b * vstride + j) * n + c].
 constexpr int kMaxDeflate = 8;
 
-// Y_j = A v_j, j < r: one pass over A (each warp takes two rows), FP64 accumulation
+// Y_j = A v_j, j < r: one pass over A.  A block takes 32 rows (four per warp) and walks the columns 256 at a time; the
+// 256-column slice of all r vectors is staged in shared memory once per block, so the vectors are read from L2 once per
+// 32 rows instead of once per row pair (that traffic, not the pass over A, bounded the first version of this kernel).
+// Eight products at a time are summed in FP32, the partial sums in FP64 (see gemv_kernel).
+constexpr int kBlockGemvRows = 32;
 __global__ void __launch_bounds__(256) block_gemv_kernel(const float* __restrict__ a, const float* __restrict__ v,
                                                          float* __restrict__ y, int n, int r, int vstride) {
+  __shared__ float4 sv[kMaxDeflate][64];
   const int b = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row0 = (blockIdx.x * 8 + warp) * 2;
-  if (row0 >= n) return;
-  const bool two = row0 + 1 < n;
-  const float* A0 = a + ((long long)b * n + row0) * n;
-  const float* A1 = two ? A0 + n : A0;
+  const int row0 = blockIdx.x * kBlockGemvRows + warp * 4;
   const float* V = v + (long long)b * vstride * n;
-  double acc0[kMaxDeflate], acc1[kMaxDeflate];
+  const float* A = a + (long long)b * n * n;
+  double acc[4][kMaxDeflate];
 #pragma unroll
-  for (int j = 0; j < kMaxDeflate; ++j) acc0[j] = acc1[j] = 0.0;
-  for (int c = lane * 4; c < n; c += 128) {
-    const float4 p0 = *reinterpret_cast<const float4*>(A0 + c);
-    const float4 p1 = *reinterpret_cast<const float4*>(A1 + c);
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int j = 0; j < kMaxDeflate; ++j) {
-      if (j < r) {
-        const float4 x = *reinterpret_cast<const float4*>(V + (long long)j * n + c);
-        acc0[j] += (double)p0.x * x.x + (double)p0.y * x.y + (double)p0.z * x.z + (double)p0.w * x.w;
-        acc1[j] += (double)p1.x * x.x + (double)p1.y * x.y + (double)p1.z * x.z + (double)p1.w * x.w;
+    for (int j = 0; j < kMaxDeflate; ++j) acc[i][j] = 0.0;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c0 = 0; c0 < n; c0 += 256) {
+    __syncthreads();  // the previous slice has been read
+    for (int i = threadIdx.x; i < kMaxDeflate * 64; i += 256) {
+      const int j = i >> 6, col = c0 + (i & 63) * 4;
+      sv[j][i & 63] = (j < r && col < n) ? *reinterpret_cast<const float4*>(V + (long long)j * n + col) : zero;
+    }
+    __syncthreads();
+    const int ca = c0 + lane * 4, cb = ca + 128;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = row0 + i;
+      if (row < n) {
+        const float* Ar = A + (long long)row * n;
+        const float4 p0 = ca < n ? *reinterpret_cast<const float4*>(Ar + ca) : zero;
+        const float4 p1 = cb < n ? *reinterpret_cast<const float4*>(Ar + cb) : zero;
+#pragma unroll
+        for (int j = 0; j < kMaxDeflate; ++j) {
+          const float4 x0 = sv[j][lane], x1 = sv[j][lane + 32];
+          const float s0 = fmaf(p0.x, x0.x, fmaf(p0.y, x0.y, fmaf(p0.z, x0.z, p0.w * x0.w)));
+          const float s1 = fmaf(p1.x, x1.x, fmaf(p1.y, x1.y, fmaf(p1.z, x1.z, p1.w * x1.w)));
+          acc[i][j] += (double)(s0 + s1);
+        }
       }
     }
   }
 #pragma unroll
-  for (int j = 0; j < kMaxDeflate; ++j) {
-    if (j < r) {
-      double s0 = acc0[j], s1 = acc1[j];
+  for (int i = 0; i < 4; ++i) {
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-        s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-      }
-      if (lane == 0) {
-        float* Y = y + ((long long)b * vstride + j) * n;
-        Y[row0] = (float)s0;
-        if (two) Y[row0 + 1] = (float)s1;
-      }
+    for (int j = 0; j < kMaxDeflate; ++j) {
+      double t = acc[i][j];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+      if (lane == 0 && j < r && row0 + i < n) y[((long long)b * vstride + j) * n + row0 + i] = (float)t;
     }
   }
 }
@@ -424,32 +439,84 @@ __device__ __forceinline__ double block_dot(const float* x, const float* y, int 
   return block_sum(s, red);
 }
 
-// Orthonormalise the r vectors of every statistic (modified Gram-Schmidt, in place).  A vector that vanishes against
-// the earlier ones is replaced by nothing: it stays zero and its Ritz value will be zero.
-__device__ void orthonormalise(float* V, int n, int r, double* red) {
-  for (int j = 0; j < r; ++j) {
-    float* vj = V + (long long)j * n;
-    for (int i = 0; i < j; ++i) {
-      const float* vi = V + (long long)i * n;
-      const double d = block_dot(vi, vj, n, red);
-      for (int c = threadIdx.x; c < n; c += blockDim.x) vj[c] = (float)((double)vj[c] - d * (double)vi[c]);
-      __syncthreads();
-    }
-    const double nn = block_dot(vj, vj, n, red);
-    const double inv = nn > 0.0 ? 1.0 / sqrt(nn) : 0.0;
-    for (int c = threadIdx.x; c < n; c += blockDim.x) vj[c] = (float)((double)vj[c] * inv);
-    __syncthreads();
+// Sums over the block of K doubles per thread (256 threads): out[i] holds the total of acc[i] afterwards (shared
+// memory, valid for every thread after the call).  `part` is 8 * K doubles of shared scratch.
+template <int K>
+__device__ __forceinline__ void block_sum_many(double (&acc)[K], double* part, double* out) {
+#pragma unroll
+  for (int i = 0; i < K; ++i) {
+    double x = acc[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    acc[i] = x;
   }
+  __syncthreads();  // earlier readers of part / out are done
+  if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+    for (int i = 0; i < K; ++i) part[(threadIdx.x >> 5) * K + i] = acc[i];
+  }
+  __syncthreads();
+  if (threadIdx.x < K) {
+    double t = 0.0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += part[w * K + threadIdx.x];
+    out[threadIdx.x] = t;
+  }
+  __syncthreads();
 }
 
-// start vectors: r different fixed +-1 patterns (cold) or the caller's vectors (warm), orthonormalised
+constexpr int kPairs = kMaxDeflate * (kMaxDeflate + 1) / 2;  // entries of a symmetric r x r matrix, r = 8
+__device__ __forceinline__ int pair_index(int i, int j) { return i * (i + 1) / 2 + j; }  // j <= i
+
+// Cholesky-QR of the r vectors held in Y (r x n, vector-major): G = Y Y^T = L L^T (FP64, one thread), V = L^-1 Y.
+// `gram` holds G's lower triangle (pair_index order) on entry.  A vector that is (numerically) a combination of the
+// earlier ones comes out as zero; its slot is seeded afresh by the next call.
+__device__ void cholesky_orthonormalise(const float* Y, float* V, int n, int r, const double* gram, double (*L)[kMaxDeflate]) {
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < r; ++i) {
+      for (int j = 0; j <= i; ++j) {
+        double sum = gram[pair_index(i, j)];
+        for (int k = 0; k < j; ++k) sum -= L[i][k] * L[j][k];
+        if (i == j) {
+          L[i][i] = (sum > 1e-24 * gram[pair_index(i, i)] && sum > 0.0) ? sqrt(sum) : 0.0;
+        } else {
+          L[i][j] = L[j][j] > 0.0 ? sum / L[j][j] : 0.0;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    double out[kMaxDeflate];
+#pragma unroll
+    for (int j = 0; j < kMaxDeflate; ++j) {
+      if (j < r) {
+        double sum = (double)Y[(long long)j * n + c];
+#pragma unroll
+        for (int i = 0; i < kMaxDeflate; ++i)
+          if (i < j) sum -= L[j][i] * out[i];
+        out[j] = L[j][j] > 0.0 ? sum / L[j][j] : 0.0;
+      } else {
+        out[j] = 0.0;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxDeflate; ++j)
+      if (j < r) V[(long long)j * n + c] = (float)out[j];
+  }
+  __syncthreads();
+}
+
+// start vectors: the caller's vectors (warm), or r different fixed +-1 patterns (cold, and for a slot that holds
+// nothing yet because the rank grew since the last call), orthonormalised
 __global__ void __launch_bounds__(256) block_start_kernel(float* __restrict__ v, int n, int r, int vstride, int cold) {
   __shared__ double red[8];
+  __shared__ double part[8 * kPairs], gram[kPairs];
+  __shared__ double L[kMaxDeflate][kMaxDeflate];
   const int b = blockIdx.x;
   float* V = v + (long long)b * vstride * n;
   const float s = rsqrtf((float)n);
   for (int j = 0; j < r; ++j) {
-    // a slot that holds nothing yet (the rank grew since the last call) starts from its fixed pattern, like a cold one
     float* vj = V + (long long)j * n;
     const bool seed = cold || !(block_dot(vj, vj, n, red) > 0.0);
     if (seed)
@@ -457,34 +524,65 @@ __global__ void __launch_bounds__(256) block_start_kernel(float* __restrict__ v,
         vj[c] = ((((unsigned)c + 977u * (unsigned)j) * 2654435761u) >> (15 + (j & 7))) & 1u ? s : -s;
     __syncthreads();
   }
-  orthonormalise(V, n, r, red);
+  double acc[kPairs];
+#pragma unroll
+  for (int i = 0; i < kPairs; ++i) acc[i] = 0.0;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    double x[kMaxDeflate];
+#pragma unroll
+    for (int i = 0; i < kMaxDeflate; ++i) x[i] = i < r ? (double)V[(long long)i * n + c] : 0.0;
+#pragma unroll
+    for (int i = 0; i < kMaxDeflate; ++i)
+#pragma unroll
+      for (int j = 0; j <= i; ++j) acc[i * (i + 1) / 2 + j] += x[i] * x[j];
+  }
+  block_sum_many<kPairs>(acc, part, gram);
+  cholesky_orthonormalise(V, V, n, r, gram, L);
 }
 
 // Rayleigh-Ritz on span(V) with Y = A V (V orthonormal): H = V Y^T, H = Q diag(theta) Q^T (Jacobi, FP64, one thread),
 // V <- Q^T V, Y <- Q^T Y (Ritz vectors, descending theta), res_j = ||Y_j - theta_j V_j|| / |theta_j|.  Unless this is
-// the last sweep, V is then replaced by the orthonormalised Y (one more step of the power iteration).
+// the last sweep, V is then replaced by the orthonormalised Y (one more step of the power iteration).  Three passes
+// over the two blocks of vectors; every reduction is taken for all pairs at once.
 __global__ void __launch_bounds__(256) ritz_kernel(float* __restrict__ v, float* __restrict__ y, int n, int r, int vstride,
                                                    int last, float* __restrict__ theta, float* __restrict__ res) {
-  __shared__ double red[8];
-  __shared__ double H[kMaxDeflate][kMaxDeflate], Q[kMaxDeflate][kMaxDeflate], lam[kMaxDeflate];
+  constexpr int R = kMaxDeflate;
+  __shared__ double part[8 * R * R], sums[R * R];
+  __shared__ double H[R][R], Q[R][R], lam[R], L[R][R];
   const int b = blockIdx.x;
   float* V = v + (long long)b * vstride * n;
   float* Y = y + (long long)b * vstride * n;
-  for (int i = 0; i < r; ++i)
-    for (int j = 0; j <= i; ++j) {
-      const double h = 0.5 * (block_dot(V + (long long)i * n, Y + (long long)j * n, n, red) +
-                              block_dot(V + (long long)j * n, Y + (long long)i * n, n, red));
-      if (threadIdx.x == 0) H[i][j] = H[j][i] = h;
+  {
+    double acc[R * R];
+#pragma unroll
+    for (int i = 0; i < R * R; ++i) acc[i] = 0.0;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+      double vv[R], yy[R];
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        vv[i] = i < r ? (double)V[(long long)i * n + c] : 0.0;
+        yy[i] = i < r ? (double)Y[(long long)i * n + c] : 0.0;
+      }
+#pragma unroll
+      for (int i = 0; i < R; ++i)
+#pragma unroll
+        for (int j = 0; j < R; ++j) acc[i * R + j] += vv[i] * yy[j];
     }
-  __syncthreads();
+    block_sum_many<R * R>(acc, part, sums);
+  }
   if (threadIdx.x == 0) {
     for (int i = 0; i < r; ++i)
-      for (int j = 0; j < r; ++j) Q[i][j] = i == j ? 1.0 : 0.0;
+      for (int j = 0; j < r; ++j) {
+        H[i][j] = 0.5 * (sums[i * R + j] + sums[j * R + i]);
+        Q[i][j] = i == j ? 1.0 : 0.0;
+      }
     for (int sweep = 0; sweep < 12; ++sweep) {
       double off = 0.0;
       for (int pp = 0; pp < r; ++pp)
         for (int qq = pp + 1; qq < r; ++qq) off += H[pp][qq] * H[pp][qq];
-      if (!(off > 0.0)) break;
+      double diag = 0.0;
+      for (int pp = 0; pp < r; ++pp) diag += H[pp][pp] * H[pp][pp];
+      if (!(off > 1e-30 * diag)) break;   // off-diagonal part below FP64 rounding of the diagonal: converged
       for (int pp = 0; pp < r; ++pp)
         for (int qq = pp + 1; qq < r; ++qq) {
           const double apq = H[pp][qq];
@@ -521,48 +619,56 @@ __global__ void __launch_bounds__(256) ritz_kernel(float* __restrict__ v, float*
     }
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < n; c += blockDim.x) {  // rotate both blocks: new vector j = sum_i Q[i][j] old vector i
-    double vv[kMaxDeflate], yy[kMaxDeflate];
+  {
+    // rotate both blocks (new vector j = sum_i Q[i][j] old vector i); on the way: the squared residuals and the Gram
+    // matrix of the rotated Y (for its orthonormalisation)
+    double acc[kPairs + R];
 #pragma unroll
-    for (int i = 0; i < kMaxDeflate; ++i) {
-      vv[i] = i < r ? (double)V[(long long)i * n + c] : 0.0;
-      yy[i] = i < r ? (double)Y[(long long)i * n + c] : 0.0;
-    }
-    for (int j = 0; j < r; ++j) {
-      double sv = 0.0, sy = 0.0;
-#pragma unroll
-      for (int i = 0; i < kMaxDeflate; ++i) {
-        if (i < r) {
-          sv += Q[i][j] * vv[i];
-          sy += Q[i][j] * yy[i];
-        }
-      }
-      V[(long long)j * n + c] = (float)sv;
-      Y[(long long)j * n + c] = (float)sy;
-    }
-  }
-  __syncthreads();
-  for (int j = 0; j < r; ++j) {
-    const float* vj = V + (long long)j * n;
-    const float* yj = Y + (long long)j * n;
-    double s = 0.0;
-    const double l = lam[j];
+    for (int i = 0; i < kPairs + R; ++i) acc[i] = 0.0;
     for (int c = threadIdx.x; c < n; c += blockDim.x) {
-      const double d = (double)yj[c] - l * (double)vj[c];
-      s += d * d;
+      double vv[R], yy[R], nv[R], ny[R];
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        vv[i] = i < r ? (double)V[(long long)i * n + c] : 0.0;
+        yy[i] = i < r ? (double)Y[(long long)i * n + c] : 0.0;
+      }
+#pragma unroll
+      for (int j = 0; j < R; ++j) {
+        double sv = 0.0, sy = 0.0;
+        if (j < r) {
+#pragma unroll
+          for (int i = 0; i < R; ++i) {
+            if (i < r) {
+              sv += Q[i][j] * vv[i];
+              sy += Q[i][j] * yy[i];
+            }
+          }
+          // what is stored is what later passes read: round before the sums
+          const float fv = (float)sv, fy = (float)sy;
+          V[(long long)j * n + c] = fv;
+          Y[(long long)j * n + c] = fy;
+          sv = fv;
+          sy = fy;
+        }
+        nv[j] = sv;
+        ny[j] = sy;
+      }
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+#pragma unroll
+        for (int j = 0; j <= i; ++j) acc[i * (i + 1) / 2 + j] += ny[i] * ny[j];
+        const double d = i < r ? ny[i] - lam[i] * nv[i] : 0.0;
+        acc[kPairs + i] += d * d;
+      }
     }
-    s = block_sum(s, red);
-    if (threadIdx.x == 0) {
-      theta[b * kMaxDeflate + j] = (float)l;
-      res[b * kMaxDeflate + j] = l > 0.0 ? (float)(sqrt(s) / l) : INFINITY;
-    }
+    block_sum_many<kPairs + R>(acc, part, sums);
   }
-  if (!last) {
-    __syncthreads();
-    for (long long i = threadIdx.x; i < (long long)r * n; i += blockDim.x) V[i] = Y[i];
-    __syncthreads();
-    orthonormalise(V, n, r, red);
+  if (threadIdx.x < r) {
+    const double l = lam[threadIdx.x];
+    theta[b * R + threadIdx.x] = (float)l;
+    res[b * R + threadIdx.x] = l > 0.0 ? (float)(sqrt(sums[kPairs + threadIdx.x]) / l) : INFINITY;
   }
+  if (!last) cholesky_orthonormalise(Y, V, n, r, sums, L);
 }
 
 // Which of the r Ritz pairs are deflated: in descending order, as long as each has converged and stands above eight
@@ -591,7 +697,12 @@ __global__ void block_decide_kernel(const float* __restrict__ theta, const float
     coef[b * kMaxDeflate + j] = on ? (float)-(t - c) : 0.f;
     corr[b * kMaxDeflate + j] = on ? (float)(pow(t, -1.0 / p) - pow(c, -1.0 / p)) : 0.f;
   }
-  if (count) count[b] = m;
+  // also reported (bits 8..15): how many Ritz values stand above 8x the rest whether converged or not -- directions
+  // that look like outliers; a caller that iterates fewer vectors than there are of those widens its block
+  int cand = 0;
+  for (int j = 0; j < r; ++j)
+    if ((double)theta[b * kMaxDeflate + j] > 8.0 * c) ++cand;
+  if (count) count[b] = m | (cand << 8);
 }
 
 // A_b += sum_j coef[b][j] v_bj v_bj^T  (terms with a zero coefficient are skipped; exact symmetry is kept: the
@@ -900,13 +1011,14 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
     damp_kernel<<<dim3(t32, t32, kc), 256, 0, stream>>>(C, A32, n, damping, trace);
     count_launch();
     if (defl_r > 0) {
-      // dominant directions: block power iteration with Rayleigh-Ritz on the caller's vectors (six sweeps from fixed
-      // vectors, three from last call's), then deflate those that converged and stand above the rest
+      // dominant directions: block power iteration with Rayleigh-Ritz on the caller's vectors (eight sweeps from fixed
+      // vectors -- the first three or four only find the subspace --, four from last call's), then deflate those that
+      // converged and stand above the rest
       block_start_kernel<<<kc, 256, 0, stream>>>(dv, n, defl_r, kMaxDeflate, defl_cold ? 1 : 0);
       count_launch();
-      const int sweeps = defl_cold ? 6 : 3;
+      const int sweeps = defl_cold ? 8 : 4;
       for (int sw = 0; sw < sweeps; ++sw) {
-        block_gemv_kernel<<<dim3((n + 15) / 16, kc), 256, 0, stream>>>(A32, dv, py, n, defl_r, kMaxDeflate);
+        block_gemv_kernel<<<dim3((n + kBlockGemvRows - 1) / kBlockGemvRows, kc), 256, 0, stream>>>(A32, dv, py, n, defl_r, kMaxDeflate);
         count_launch();
         ritz_kernel<<<kc, 256, 0, stream>>>(dv, py, n, defl_r, kMaxDeflate, sw == sweeps - 1 ? 1 : 0, th8, res8);
         count_launch();

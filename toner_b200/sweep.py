@@ -174,7 +174,7 @@ def bench_roots_tracked(a):
     flops = a.k * (split + single) * 2 * a.n ** 3
     return report("inv_roots_tracked", {"k": a.k, "n": a.n, "p": a.p, "q": a.q, "cond": a.cond}, ms, best, flops=flops,
                   extra={"iterations": f.iterations, "finish_order": f.finish_order, "split_products": split,
-                         "single_pass_products": single, "deflated": int(f.deflated_host.max()),
+                         "single_pass_products": single, "deflated": int((f.deflated_host & 255).max()),
                          "estimate": bool(f._estimate_in_flight), "repairs": f.repairs,
                          "note": "includes the host wait for the flags; three single-pass squarings for the norm bound, "
                                  "the block power iteration and the tracking sweeps are not counted as work"})
