@@ -199,6 +199,37 @@ def test_activation_statistics_matches_golden(tb, golden):
             pass
 
 
+def test_layers_reading_one_tensor_share_their_gram(tb):
+    """q, k and v read the same tensor: one Gram is computed and all three get it (the reference computes three equal
+    ones); a later tensor that happens to have the same shape is not confused with it, and two microbatches add up."""
+    q, k, v, o = (torch.nn.Linear(32, 32, bias=False).cuda() for _ in range(4))
+    stats = tb.ActivationStatistics({"q": q, "k": k, "v": v, "o": o}, head=4, stride=3, distributed=False)
+    got = {}
+
+    class Recorder:
+        def update_statistics(self, means):
+            got.update(means)
+
+    gen = torch.Generator().manual_seed(4)
+    xs = [torch.randn(2, 19, 32, generator=gen).cuda() for _ in range(2)]
+    rows_x, rows_a = [], []
+    for x in xs:
+        with stats.capture():
+            a = q(x) + k(x) + v(x)
+            o(a)
+        assert stats._alias == {"k": "q", "v": "q"}
+        rows_x.append(orc.sampled_rows(x.cpu(), 4, 3))
+        rows_a.append(orc.sampled_rows(a.detach().cpu(), 4, 3))
+    stats.commit(Recorder())
+    want_x = orc.gram(torch.cat(rows_x)) / sum(r.shape[0] for r in rows_x)
+    want_a = orc.gram(torch.cat(rows_a)) / sum(r.shape[0] for r in rows_a)
+    for lin in (q, k, v):
+        assert orc.rel_fro(got[lin.weight].cpu(), want_x) < 2e-6
+    assert got[q.weight].data_ptr() == got[k.weight].data_ptr() == got[v.weight].data_ptr()
+    assert orc.rel_fro(got[o.weight].cpu(), want_a) < 2e-6
+    stats.close()
+
+
 def test_nanogpt_stack_with_activation_statistics_and_adamt(tb):
     """The 12-layer modded-nanoGPT shape: ActivationStatistics(head 32, stride 16) over its 72 projections on one
     batch of 8 x 1024 tokens under BF16 autocast (752 rows per statistic), committed to AdamT(betas=(0.9, 0.95)),

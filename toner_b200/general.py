@@ -169,6 +169,7 @@ class _TonerGeneral(Optimizer):
         error (src/toner/reference.py:51-81)."""
         self._ensure_built()
         owner = {p: g for g in self.param_groups for p in g["params"]}
+        finite = {}
         for p, cov in second_moments.items():   # nothing is touched until every entry has passed
             if p not in owner:
                 raise ValueError("Received a statistic for a parameter not owned by this optimizer")
@@ -176,10 +177,13 @@ class _TonerGeneral(Optimizer):
                 raise ValueError("Statistic shape must match the matrix weight's input dimension")
             if cov.device != p.device:
                 raise ValueError("Input statistics and matrix weights must be on the same device")
-            if not cov.is_floating_point() or not bool(torch.isfinite(cov).all()):
+            if not cov.is_floating_point():
                 raise ValueError("Input statistics must be finite floating-point matrices")
             if self.state[p].get("statistics_ready", False):
                 raise RuntimeError("Statistics already updated; aggregate microbatches before update_statistics()")
+            finite.setdefault(cov.data_ptr(), torch.isfinite(cov).all())     # one flag per distinct statistic
+        if finite and not bool(torch.stack(list(finite.values())).all()):    # one wait for all of them
+            raise ValueError("Input statistics must be finite floating-point matrices")
         for p, cov in second_moments.items():
             bucket, i = self._bucket_of[p]
             state, beta = self.state[p], owner[p]["statistic_momentum"]

@@ -49,6 +49,10 @@ class ActivationStatistics:
         self._active = self._closed = False
         self._sums: Dict[str, torch.Tensor] = {}     # packed upper triangles, summed over microbatches
         self._counts: Dict[str, int] = {}            # rows behind each sum
+        # Layers that read one and the same tensor (q, k, v of an attention block) have one and the same Gram: within a
+        # capture() the first of them computes it and the others share the result (the reference computes it three times).
+        self._shared: Dict[tuple, tuple] = {}        # input signature -> (layer that holds its sum, the tensor)
+        self._alias: Dict[str, str] = {}             # layer -> layer whose sum it shares
         self._positions: Dict[tuple, torch.Tensor] = {}
         weights_seen = set()
         for name, layer in self.layers.items():
@@ -101,6 +105,20 @@ class ActivationStatistics:
                 raise ValueError(f"layer '{name}': input rows must have {module.in_features} features")
             if not x.is_cuda:
                 raise ValueError(f"layer '{name}': toner_b200 captures CUDA activations only (there is no CPU path)")
+            # Same storage, layout and version as a tensor another layer read in this forward: the same rows.  The first
+            # reader's tensor is kept alive until the forward ends, so its address cannot be handed to a different
+            # tensor in the meantime.
+            signature = (x.data_ptr(), tuple(x.shape), tuple(x.stride()), x.dtype, x._version)
+            first = self._shared.get(signature)
+            if first is not None and (self._alias.get(name) == first[0] or
+                                      (name not in self._alias and name not in self._sums)):
+                self._alias[name] = first[0]
+                return
+            if name in self._alias:
+                raise RuntimeError(f"layer '{name}' read the same tensor as '{self._alias[name]}' in an earlier microbatch "
+                                   "of this step but not in this one")
+            if first is None:
+                self._shared[signature] = (name, x)
             if x.ndim > 2:  # (..., sequence, features): keep the sampled positions of every sequence
                 key = (x.shape[-2], x.device)
                 idx = self._positions.get(key)
@@ -129,12 +147,14 @@ class ActivationStatistics:
         if self._active:
             raise RuntimeError("capture() is already active; nesting would count activations twice")
         self._active = True
+        self._shared = {}
         failed = True
         try:
             yield self
             failed = False
         finally:
             self._active = False
+            self._shared = {}
             if failed:  # a forward that raised may have captured only some layers: drop the pending step
                 self.clear()
 
@@ -146,14 +166,19 @@ class ActivationStatistics:
             raise RuntimeError("commit() after close()")
         if self._active:
             raise RuntimeError("commit() inside capture(); leave the context first")
-        absent = sorted(set(self.layers) - set(self._sums))
+        absent = sorted(set(self.layers) - set(self._sums) - set(self._alias))
         if absent:
             raise RuntimeError("nothing was captured for layer(s): " + ", ".join(absent))
         pooled = self.distributed and dist.is_available() and dist.is_initialized()
         means = {}
+        done: Dict[str, torch.Tensor] = {}
         for name, layer in self.layers.items():
-            packed = self._sums[name]
-            rows = self._counts[name]
+            source = self._alias.get(name, name)
+            if source in done:                       # shares its input with a layer already pooled: the same mean
+                means[layer.weight] = done[source]
+                continue
+            packed = self._sums[source]
+            rows = self._counts[source]
             if pooled:
                 count = torch.tensor(rows, device=packed.device, dtype=torch.int64)
                 dist.all_reduce(packed, group=self.process_group)
@@ -162,7 +187,7 @@ class ActivationStatistics:
             n = layer.in_features
             mean = torch.zeros(1, n, n, device=packed.device, dtype=torch.float32)
             ops.unpack_ema(packed, mean, 0.0, 1.0 / float(rows))
-            means[layer.weight] = mean[0]
+            means[layer.weight] = done[source] = mean[0]
         optimizer.update_statistics(means)
         self.clear()
 
@@ -172,6 +197,7 @@ class ActivationStatistics:
             raise RuntimeError("clear() inside capture()")
         self._sums = {}
         self._counts = {}
+        self._alias = {}
 
     def close(self) -> None:
         while self._handles:
