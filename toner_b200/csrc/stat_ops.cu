@@ -120,10 +120,9 @@ __global__ void __launch_bounds__(256) split16_kernel(const float* __restrict__ 
   if (vec) {
     const long long total4 = per / 4;
     const int c4 = cols / 4;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+    auto split4 = [&](long long i, const float4 q) {
       const int r = (int)(i / c4), c = (int)(i - (long long)r * c4) * 4;
-      const float4 q = *reinterpret_cast<const float4*>(X + (long long)r * ld + c);
-      float v[4] = {q.x, q.y, q.z, q.w};
+      const float v[4] = {q.x, q.y, q.z, q.w};
       __half h[4], l[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -133,7 +132,19 @@ __global__ void __launch_bounds__(256) split16_kernel(const float* __restrict__ 
       }
       *reinterpret_cast<uint2*>(hi + (long long)r * cols + c) = *reinterpret_cast<uint2*>(h);
       *reinterpret_cast<uint2*>(lo + (long long)r * cols + c) = *reinterpret_cast<uint2*>(l);
+    };
+    auto load4 = [&](long long i) {
+      const int r = (int)(i / c4), c = (int)(i - (long long)r * c4) * 4;
+      return *reinterpret_cast<const float4*>(X + (long long)r * ld + c);
+    };
+    // four independent 16-byte loads in flight per thread before the first store
+    const long long step = (long long)gridDim.x * blockDim.x;
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + 3 * step < total4; i += 4 * step) {
+      const float4 q0 = load4(i), q1 = load4(i + step), q2 = load4(i + 2 * step), q3 = load4(i + 3 * step);
+      split4(i, q0); split4(i + step, q1); split4(i + 2 * step, q2); split4(i + 3 * step, q3);
     }
+    for (; i < total4; i += step) split4(i, load4(i));
   } else {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per; i += (long long)gridDim.x * blockDim.x) {
       const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
@@ -161,8 +172,19 @@ __global__ void __launch_bounds__(256) sumsq_partial_kernel(const float* __restr
     const long long per = (total4 + gridDim.x - 1) / gridDim.x;
     const long long lo = per * blockIdx.x, hi = (lo + per < total4) ? lo + per : total4;
     const float4* X4 = reinterpret_cast<const float4*>(X);
+    // four independent 16-byte loads in flight per thread; the order of the additions is fixed by the indices alone,
+    // so the result stays bitwise reproducible
     float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-    for (long long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    long long i = lo + threadIdx.x;
+    const long long step = blockDim.x;
+    for (; i + 3 * step < hi; i += 4 * step) {
+      const float4 a = X4[i], b = X4[i + step], c = X4[i + 2 * step], d = X4[i + 3 * step];
+      s0 = fmaf(a.x, a.x, s0); s1 = fmaf(a.y, a.y, s1); s2 = fmaf(a.z, a.z, s2); s3 = fmaf(a.w, a.w, s3);
+      s0 = fmaf(b.x, b.x, s0); s1 = fmaf(b.y, b.y, s1); s2 = fmaf(b.z, b.z, s2); s3 = fmaf(b.w, b.w, s3);
+      s0 = fmaf(c.x, c.x, s0); s1 = fmaf(c.y, c.y, s1); s2 = fmaf(c.z, c.z, s2); s3 = fmaf(c.w, c.w, s3);
+      s0 = fmaf(d.x, d.x, s0); s1 = fmaf(d.y, d.y, s1); s2 = fmaf(d.z, d.z, s2); s3 = fmaf(d.w, d.w, s3);
+    }
+    for (; i < hi; i += step) {
       const float4 v = X4[i];
       s0 = fmaf(v.x, v.x, s0); s1 = fmaf(v.y, v.y, s1); s2 = fmaf(v.z, v.z, s2); s3 = fmaf(v.w, v.w, s3);
     }
