@@ -97,7 +97,8 @@ typedef struct toner_gemm_desc {
   uint32_t* maxabs;         /*   max |d| as FP32 bits, */
   uint32_t* maxaff;         /*   max |aff_a*[r==c] + aff_b*d| as FP32 bits */
   float aff_a, aff_b;
-  int32_t tile_n;           /* 0 = choose; else 128 or 256 (128-row tiles), or 512 = 256 x 256 tiles on CTA pairs */
+  int32_t tile_n;           /* 0 = choose; else 128 or 256 (128-row tiles), 512 = 256 x 256 tiles on CTA pairs,
+                               1024 = 256 x 512 tiles on CTA pairs (no chained accumulation) */
   int32_t promote;          /* > 0: k-blocks (64 deep) per tensor-core accumulation chain; chains are summed in
                                FP32 registers with round-to-nearest (the tensor core truncates).  0: one chain */
   int32_t raster;           /* tile columns per rasterisation group for full schedules (0: default 8) */

@@ -118,10 +118,9 @@ def test_iteration_counts_are_stated(ops):
 
 @pytest.mark.parametrize("p,q", [(8, 4), (4, 1), (2, 1)])
 def test_finishing_series_at_every_order(ops, p, q):
-    """The iteration stops where Newton steps plus finishing series cost the fewest plane passes (the spectrum of M is
-    then within 0.5 of 1) and the order of the series follows from that distance.  Sweeping the caller's bound moves
-    the stopping point, so orders from 2 up to the cap are exercised; every one must give the same roots as FP64
-    truth."""
+    """The iteration stops where Newton steps plus finishing polynomial cost the fewest plane passes (the spectrum of M
+    is then within 0.6 of 1) and the degree of the polynomial follows from that distance.  Sweeping the caller's bound
+    moves the stopping point, so several degrees are exercised; every one must give the same roots as FP64 truth."""
     n = 384
     stats = torch.stack([spd(n, 3e2, 11), spd(n, 1e3, 12)]).cuda()
     norms = torch.zeros(2, device="cuda")

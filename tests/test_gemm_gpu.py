@@ -34,7 +34,7 @@ def close(got, want, k, tol=4e-7):
     assert err <= tol * (k ** 0.5) * scale + 1e-30, (err, scale)
 
 
-@pytest.mark.parametrize("tile_n", [128, 256, 512])
+@pytest.mark.parametrize("tile_n", [128, 256, 512, 1024])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_k_major_square(ops, tile_n, dtype):
     m = n = k = 256
@@ -46,7 +46,7 @@ def test_k_major_square(ops, tile_n, dtype):
 
 
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, False), (False, True), (True, True)])
-@pytest.mark.parametrize("tile_n", [128, 256, 512])   # 512: 256 x 256 tiles on CTA pairs
+@pytest.mark.parametrize("tile_n", [128, 256, 512, 1024])   # 512 / 1024: 256 x 256 / 256 x 512 tiles on CTA pairs
 def test_layouts_ragged_batched(ops, a_mn, b_mn, tile_n):
     """Sizes that are not multiples of the tile or of the k-block; three matrices per call."""
     batch, m, n, k = 3, 200, 328, 136
@@ -70,6 +70,21 @@ def test_many_tiles_persistent_loop(ops):
     d2 = torch.empty_like(d)
     ops.gemm(ops.operand(a), ops.operand(b), m=m, n=n, k=k, batch=1, fmt=1, d=d2)
     assert torch.equal(d, d2), "same inputs must give bitwise equal results"
+
+
+def test_wide_tiles_persistent_loop(ops):
+    """256 x 512 tiles on CTA pairs, more tiles than pairs: the single accumulator's two halves are handed back and
+    forth several times per CTA.  Each element is accumulated in the same order as with 256 x 256 tiles: same bits."""
+    m, n, k = 4096, 6144 + 72, 320
+    a, b = rnd((m, k), torch.bfloat16, 15), rnd((n, k), torch.bfloat16, 16)
+    d = torch.full((1, m, n), float("nan"), device="cuda")
+    ops.gemm(ops.operand(a), ops.operand(b), m=m, n=n, k=k, batch=1, fmt=1, d=d, tile_n=1024)
+    ops.assert_healthy()
+    close(d[0], ref_mm(a, b, False, False), k)
+    d2 = torch.empty_like(d)
+    ops.gemm(ops.operand(a), ops.operand(b), m=m, n=n, k=k, batch=1, fmt=1, d=d2, tile_n=512)
+    ops.assert_healthy()
+    assert torch.equal(d, d2)
 
 
 def test_epilogue_affine_and_outputs(ops):
@@ -97,7 +112,7 @@ def test_epilogue_affine_and_outputs(ops):
 
 
 @pytest.mark.parametrize("n", [256, 328, 768])
-@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("tile_n", [128, 256, 1024])
 def test_symmetric_tiles_mirror_and_packed(ops, n, tile_n):
     batch, k = 2, 200
     x = rnd((batch, k, n), torch.bfloat16, 10)  # X^T X: both operands are the MN-major view of X
@@ -178,7 +193,8 @@ def test_cta_pair_symmetric_split_product_matches_single_cta_tiles(ops, promote)
     a = ops.operand(planes, seg_z=(0, 0, batch))
     b = ops.operand(planes, seg_z=(0, batch, 0))
     out = {}
-    for tile in (256, 512):
+    tiles = (256, 512) if promote else (256, 512, 1024)      # the wide tile has no chained accumulation
+    for tile in tiles:
         d = torch.full((batch, n, n), float("nan"), device="cuda")
         sp = torch.zeros(2, batch, n, n, device="cuda", dtype=torch.float16)
         mx = torch.zeros(batch, device="cuda", dtype=torch.int32)
@@ -187,13 +203,14 @@ def test_cta_pair_symmetric_split_product_matches_single_cta_tiles(ops, promote)
         ops.assert_healthy()
         out[tile] = (d, mx.clone())
     want = x.double() @ x.double()
-    for tile in (256, 512):
+    for tile in tiles:
         # one chain over the whole depth adds by truncation (about 1.2e-7 per k-block on the all-positive diagonal)
         tol = 2e-6 if promote else 1e-5
         assert (out[tile][0].double() - want).abs().max().item() <= tol * want.abs().max().item()
         assert torch.equal(out[tile][0], out[tile][0].transpose(1, 2))
-    assert torch.equal(out[256][0], out[512][0])        # same accumulation order, same bits
-    assert torch.equal(out[256][1], out[512][1])
+    for tile in tiles[1:]:
+        assert torch.equal(out[256][0], out[tile][0])   # same accumulation order, same bits
+        assert torch.equal(out[256][1], out[tile][1])
 
 
 def test_a_wait_that_runs_out_is_reported_not_fatal(ops):

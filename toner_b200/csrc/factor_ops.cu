@@ -5,7 +5,7 @@
 //   A'  = A - (lambda_1 - c) v v^T                            (dominant direction deflated when power iteration finds it)
 //   M_0 = A' / beta,  beta >= lambda_max(A')                  (beta = min(||A'||_F, 1.04 ||A'||_F ||P^2||_F^(1/2)), P = A'/||A'||_F)
 //   T_k = a_k I - b_k M_k ;  X_{k+1} = X_k T_k ;  M_{k+1} = T_k^p M_k          (X_0 = I)
-//   X_K = X_{K-1} (I + a1 R + a2 R^2 + a3 R^3),  R = I - M_{K-1}                (binomial series of (I - R)^(-1/p))
+//   X_K = X_{K-1} (c0 I + c1 R + c2 R^2 + ... ),  R = I - M_{K-1}               (Chebyshev fit of (1 - r)^(-1/p))
 //   X_K ~ M_0^{-1/p}  =>  A^{-1/p} = X_K beta^{-1/p} + (lambda_1^{-1/p} - c^{-1/p}) v v^T
 // (a_k, b_k) map the interval [l_k, 1] known to contain the spectrum of M_k onto [l_{k+1}, 1] with
 // l_{k+1} as large as a linear T allows (the ends of the interval and the interior maximum of
@@ -81,33 +81,113 @@ constexpr int kPromoteX = 0;
 // power-iteration steps spent on the dominant direction (each one pass over the statistic)
 constexpr int kPowerSteps = 6;
 
-// The last step does not square the error once more; it finishes with the binomial series of (I - R)^(-1/p),
-// R = I - M:  X <- X (I + a_1 R + a_2 R^2 + ... + a_m R^m), a_j = a_{j-1} (1/p + j - 1) / j.  The spectrum of R lies
-// in [0, e] with e known from the schedule, so the order m is fixed in advance: the smallest whose tail
-// a_{m+1} e^{m+1} / (1 - e) is below 4e-6.  The powers come from m - 1 single-pass products of FP16 planes in Horner
-// form (a third of a split-precision product each; R is small, so its rounding to FP16 costs about 5e-4 a_2 e^2), which
-// is cheaper than the log2(p) + 2 split-precision products of one more Newton step; the step count is the one with
-// the fewest plane passes in total.
-constexpr double kFinishRadius = 0.5;
+// The last step does not square the error once more; it finishes with a polynomial q(R) ~ (I - R)^(-1/p), R = I - M:
+// X <- X q(R).  The spectrum of R lies in [0, e] with e known from the schedule, so q is fixed in advance: the
+// Chebyshev interpolant of (1 - r)^(-1/p) on [kFinishLow, kFinishGrow e + kFinishPad] (the margins cover rounding
+// at the lower end and the allowance an estimated bound is verified with at the upper end) of the smallest degree
+// whose relative error stays below kFinishTail there.  Spreading the error over the interval takes about half
+// the degree of the binomial series, whose error sits at r = e alone (e = 0.5, p = 8: degree 6 instead of 12).
+// The powers come from m - 1 single-pass products of FP16 planes in Horner form (a third of a split-precision
+// product each; R is small, so its rounding to FP16 costs about 5e-4 c_2 e^2), which is cheaper than the log2(p) + 2
+// split-precision products of one more Newton step; the step count is the one with the fewest plane passes in total.
+constexpr double kFinishRadius = 0.6;
 constexpr int kMaxFinishOrder = 12;
-constexpr double kFinishTail = 4e-6;
+constexpr double kFinishTail = 3e-6;
+constexpr double kFinishLow = -0.02, kFinishGrow = 1.15, kFinishPad = 1e-3;
 
-static double finish_coefficient(int p, int j) {
-  double a = 1.0;
-  for (int i = 1; i <= j; ++i) a *= (1.0 / p + i - 1) / i;
-  return a;
+struct FinishPoly {
+  int order = 0;                       // 0: no degree up to the cap reaches the bound at this distance
+  double c[kMaxFinishOrder + 1] = {};  // q(r) = sum_j c[j] r^j
+};
+
+// Degree-m Chebyshev interpolant of (1 - r)^(-1/p) on [lo, hi] as monomial coefficients; returns its largest
+// relative error on the interval.
+static double finish_fit(int p, double lo, double hi, int m, double* c) {
+  const double kPi = 3.14159265358979323846;
+  double cheb[kMaxFinishOrder + 1];
+  for (int j = 0; j <= m; ++j) {
+    double acc = 0.0;
+    for (int k = 0; k <= m; ++k) {
+      const double th = kPi * (k + 0.5) / (m + 1);
+      const double r = lo + (hi - lo) * (std::cos(th) + 1.0) * 0.5;
+      acc += std::pow(1.0 - r, -1.0 / p) * std::cos(j * th);
+    }
+    cheb[j] = acc * (j == 0 ? 1.0 : 2.0) / (m + 1);
+  }
+  // sum_j cheb[j] T_j(x) in powers of x (T_{j+1} = 2 x T_j - T_{j-1}) ...
+  double t0[kMaxFinishOrder + 1] = {1.0}, t1[kMaxFinishOrder + 1] = {0.0, 1.0}, px[kMaxFinishOrder + 1] = {};
+  px[0] = cheb[0];
+  for (int i = 0; i <= m; ++i) px[i] += (m >= 1 ? cheb[1] : 0.0) * t1[i];
+  for (int j = 2; j <= m; ++j) {
+    double t2[kMaxFinishOrder + 1] = {};
+    for (int i = 0; i <= m; ++i) t2[i] = (i > 0 ? 2.0 * t1[i - 1] : 0.0) - t0[i];
+    for (int i = 0; i <= m; ++i) {
+      px[i] += cheb[j] * t2[i];
+      t0[i] = t1[i];
+      t1[i] = t2[i];
+    }
+  }
+  // ... then in powers of r, x = alpha r + beta (Horner over the polynomial in x)
+  const double alpha = 2.0 / (hi - lo), beta = -(hi + lo) / (hi - lo);
+  for (int i = 0; i <= m; ++i) c[i] = 0.0;
+  for (int j = m; j >= 0; --j) {
+    for (int i = m; i >= 1; --i) c[i] = c[i] * beta + c[i - 1] * alpha;
+    c[0] = c[0] * beta + px[j];
+  }
+  double worst = 0.0;
+  const int samples = 256;
+  for (int i = 0; i <= samples; ++i) {
+    const double r = lo + (hi - lo) * i / samples;
+    double q = 0.0;
+    for (int j = m; j >= 0; --j) q = q * r + c[j];
+    worst = std::fmax(worst, std::fabs(q * std::pow(1.0 - r, 1.0 / p) - 1.0));
+  }
+  return worst;
 }
-// 0: no order up to the cap reaches the tail bound at this distance
-static int finish_order_or_zero(int p, double e) {
-  if (e >= 1.0) return 0;
-  for (int m = 2; m <= kMaxFinishOrder; ++m)
-    if (finish_coefficient(p, m + 1) * std::pow(e, m + 1) / (1.0 - e) < kFinishTail) return m;
-  return 0;
+
+// In powers of r the fit's coefficients grow as the interval approaches the singularity at r = 1 (sooner for small p):
+// sums with cancellation, which single-pass FP16 products would not survive and whose Horner intermediates
+// W_j = sum_{k >= j} c_k r^(k-j+1) would leave the range the operand planes are scaled for.  Such a fit is not used.
+constexpr double kFinishMaxCond = 2.5;   // sum_k |c_k| hi^k, against q(r) <= 1.8
+constexpr double kFinishMaxTerm = 3.5;   // bound of every W_j (planes hold |x| <= 4)
+
+static bool finish_usable(const FinishPoly& f, double hi) {
+  double cond = 0.0;
+  for (int k = f.order; k >= 0; --k) cond = cond * hi + std::fabs(f.c[k]);   // Horner of sum |c_k| hi^k
+  if (cond > kFinishMaxCond) return false;
+  double w = 0.0;
+  for (int j = f.order; j >= 1; --j) {
+    w = (w + std::fabs(f.c[j])) * hi;
+    if (w > kFinishMaxTerm) return false;
+  }
+  return true;
 }
-static int finish_order(int p, double e) {
-  const int m = finish_order_or_zero(p, e);
-  return m ? m : kMaxFinishOrder;  // a caller's own (too small) step count: the best the cap allows; status reports it
+
+static FinishPoly finish_poly(int p, double e) {
+  FinishPoly f;
+  if (!(e < kFinishRadius)) return f;
+  const double hi = kFinishGrow * e + kFinishPad;
+  for (int m = 2; m <= kMaxFinishOrder; ++m) {
+    if (finish_fit(p, kFinishLow, hi, m, f.c) < kFinishTail) {
+      f.order = m;
+      if (!finish_usable(f, hi)) f.order = 0;
+      return f;
+    }
+  }
+  return f;
 }
+static int finish_order_or_zero(int p, double e) { return finish_poly(p, e).order; }
+// A caller's own (too small) step count leaves M too far from I for a usable fit: the binomial series of
+// (1 - r)^(-1/p) at the cap (all coefficients positive and below 1); status reports the statistic.
+static FinishPoly finish_poly_or_best(int p, double e) {
+  FinishPoly f = finish_poly(p, e);
+  if (f.order) return f;
+  f.order = kMaxFinishOrder;
+  f.c[0] = 1.0;
+  for (int j = 1; j <= kMaxFinishOrder; ++j) f.c[j] = f.c[j - 1] * (1.0 / p + j - 1) / j;
+  return f;
+}
+static int finish_order(int p, double e) { return finish_poly_or_best(p, e).order; }
 
 static int default_iterations(double l0, int p) {
   // k steps of M, then the finishing step on X alone: the k with the fewest plane passes,
@@ -120,7 +200,7 @@ static int default_iterations(double l0, int p) {
     double l;
     newton_schedule(l0, p, k, &l);
     const double e = 1.0 - l;
-    const int m = e < kFinishRadius ? finish_order_or_zero(p, e) : 0;
+    const int m = finish_order_or_zero(p, e);
     if (m) {
       const long cost = 3L * k * (log2p + 2) + (m - 1);
       if (!best || cost < best_cost) {
@@ -933,7 +1013,8 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
   const std::vector<NewtonStep> sched = newton_schedule(l0, p, iters, nullptr);
   double l_last;  // lower bound of the spectrum of the last M, i.e. after iters - 1 updates
   newton_schedule(l0, p, iters - 1, &l_last);
-  const int order = finish_order(p, 1.0 - l_last);
+  const FinishPoly fin = finish_poly_or_best(p, 1.0 - l_last);
+  const int order = fin.order;
   int log2p = 0;
   while ((1 << log2p) < p) ++log2p;
 
@@ -1153,20 +1234,21 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
           count_launch();
           TONER_CUDA(cudaGetLastError());
           // Tcur holds planes of R = I - M and A32 the FP32 M (both from the last update of M).  Horner steps
-          // W_j = a_j R + R W_{j+1} (W_m = a_m R) build T = I + W_1; the terms linear in M enter in FP32 as beta * c.
+          // W_j = c_j R + R W_{j+1} (W_m = c_m R) build q(R) = c_0 I + W_1; the terms linear in M enter in FP32 as
+          // beta * c.
           const float s_w = plane_scale(1.0), s_f = plane_scale(2.0);
           const __half* wcur = Tcur;
           float s_cur = s_t;
-          double gain = finish_coefficient(p, order);
+          double gain = fin.c[order];
           for (int j = order - 1; j >= 1; --j) {
-            const double aj = finish_coefficient(p, j);
+            const double aj = fin.c[j];
             Out w;
             w.segs = 1;
             w.gain = gain;
             w.c = A32; w.beta = (float)-aj;
             w.s1 = Mb[j & 1];
             w.s1_scale = (j == 1) ? s_f : s_w;
-            w.s1_a = (float)(j == 1 ? 1.0 + aj : aj);
+            w.s1_a = (float)(j == 1 ? fin.c[0] + aj : aj);
             w.s1_b = 1.f;
             rc = sym_product(Tcur, s_t, wcur, s_cur, w, 0);
             if (rc) return rc;

@@ -103,8 +103,14 @@ __host__ __device__ inline int gemm_tiles_per_batch(int M, int N, int BN, int tr
 
 // kPair: two CTAs of a cluster work on one 256 x BN tile (cta_group::2); each holds 128 rows of A and BN/2
 // rows of B per stage, so a stage is two thirds the size and the ring two stages deeper.
+// BN = 512 (pairs only) is the wide tile: two 256-column MMAs per k-step share the A rows, which cuts the operand
+// bytes fetched per flop by a quarter (48 KB per CTA and k-block for twice the work of 32 KB).  Its accumulator
+// fills all 512 columns of tensor memory, so there is no second buffer: the epilogue of a tile overlaps the next
+// tile's MMAs only half by half.  It pays where the accumulation is long (K in the thousands of k-blocks, as in
+// the statistic X^T X, or three plane passes of a wide matrix).
 template <int BN, bool kPair = false>
 struct GemmSmem {
+  static constexpr bool kWide = kPair && BN == 512;
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBRows = kPair ? BN / 2 : BN;   // rows of B this CTA loads per stage
   static constexpr int kBBytes = kBRows * kBK * 2;
@@ -114,7 +120,7 @@ struct GemmSmem {
   static constexpr int kBarBytes = 256;
   static constexpr int kEpiBytes = 8 * 32 * 33 * 4;  // one padded 32 x 32 FP32 staging block per epilogue warp
   static constexpr int kTotal = kTileBytes + kBarBytes + kEpiBytes + 1024;  // 1024: alignment slack
-  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kTmemCols = kWide ? 512 : 2 * BN;
 };
 
 __device__ __forceinline__ void tile_coord(const GemmParams& p, int BN, int TM, int t, int tiles_per_batch, int tiles_n,
@@ -327,6 +333,10 @@ __device__ __forceinline__ void epilogue_block_scalar(const GemmParams& p, const
 template <int BN, bool kChained, bool kPair = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __grid_constant__ GemmParams p) {
   using S = GemmSmem<BN, kPair>;
+  static_assert(BN == 128 || BN == 256 || (BN == 512 && kPair && !kChained), "tile widths: 128, 256, or 512 on a pair");
+  constexpr bool kWide = S::kWide;
+  constexpr int BNI = kWide ? 256 : BN;                // columns of one MMA instruction
+  constexpr int NJ = BN / BNI;                         // MMAs per k-step (column halves of a wide tile)
   constexpr int TM = kPair ? 2 * kBM : kBM;            // rows of one scheduled tile
   const uint32_t cta_rank = kPair ? ptx::cluster_ctarank() : 0u;
   const bool leader = cta_rank == 0;
@@ -403,7 +413,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
     }
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(tfull_bar(s), 1);
-      ptx::mbar_init(tempty_bar(s), kPair ? 16 : 8);  // one arrival per epilogue warp (of both CTAs of a pair)
+      // one arrival per epilogue warp (of both CTAs of a pair); per half of a wide tile: the four warps that read it
+      ptx::mbar_init(tempty_bar(s), kWide ? 8 : (kPair ? 16 : 8));
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
@@ -424,7 +435,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp < 4) {
-  ptx::reg_dec<40>();
+  ptx::reg_dec<48>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -440,7 +451,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         ptx::fence_tensormap_acquire(amap);
         ptx::fence_tensormap_acquire(bmap);
         // a pair splits the tile's rows (A) and its columns (B) between its two CTAs
-        const int m0 = tm * TM + (int)cta_rank * kBM, n0 = tn * BN + (int)cta_rank * S::kBRows;
+        // (of a wide tile each CTA holds 128 columns of either 256-column half: n0 is its share of the first half)
+        const int m0 = tm * TM + (int)cta_rank * kBM, n0 = tn * BN + (int)cta_rank * (kWide ? BNI / 2 : S::kBRows);
         for (int si = 0; si < p.segs && ok; ++si) {
           const int seg = rest_first ? (si + 1 == p.segs ? 0 : si + 1) : si;
           const int za = b * p.a_z_stride + p.a_seg_z[seg];
@@ -467,7 +479,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
               } else {
                 ptx::tma_load_3d_pair(sa, amap, lbar, k0, m0, za);
               }
-              if (p.b_mn) {
+              if constexpr (kWide) {
+                if (p.b_mn) {
+#pragma unroll
+                  for (int s = 0; s < 4; ++s)
+                    ptx::tma_load_3d_pair(sb + s * 8192, bmap, lbar, n0 + (s >> 1) * BNI + (s & 1) * 64, k0, zb);
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 2; ++j) ptx::tma_load_3d_pair(sb + j * 16384, bmap, lbar, k0, n0 + j * BNI, zb);
+                }
+              } else if (p.b_mn) {
 #pragma unroll
                 for (int s = 0; s < S::kBRows / 64; ++s) ptx::tma_load_3d_pair(sb + s * 8192, bmap, lbar, n0 + s * 64, k0, zb);
               } else {
@@ -495,7 +516,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
           }
         }
       }
-      if (p.prof) atomicAdd(p.prof + 3, (unsigned long long)prof_wait);
+      if (p.prof && leader) atomicAdd(p.prof + 3, (unsigned long long)prof_wait);
       if (!ok || *abort_flag) {
         // Copies already issued must land before this CTA gives its shared memory back (the closing barrier waits
         // for threads, not for bulk copies).  Stage s was last filled in this round if s < stage, else in the round
@@ -518,11 +539,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
     // ------------------------------------------------------------ MMA issuer (of a pair: the leader CTA only)
     if (lane == 0 && leader) {
       const uint32_t idesc = (1u << 4) | ((uint32_t)p.fmt << 7) | ((uint32_t)p.fmt << 10) | ((uint32_t)p.a_mn << 15) |
-                             ((uint32_t)p.b_mn << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
+                             ((uint32_t)p.b_mn << 16) | ((uint32_t)(BNI >> 3) << 17) | ((uint32_t)(TM >> 4) << 24);
       // K-major: 8-row groups 1024 B apart, k advances 32 B inside the swizzled row.
       // MN-major: 64-element slabs 8192 B apart (LBO), 8-k-row groups 1024 B apart (SBO), k advances 16 rows = 2048 B.
-      const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
-      const uint32_t a_step = p.a_mn ? 2048u : 32u, b_step = p.b_mn ? 2048u : 32u;
+      // The descriptor's upper word (8-row groups 1024 B apart, version, 128-byte swizzle) never changes; the lower
+      // word is the address in 16-byte units plus the leading-dimension offset, so a k-step is an addition.
+      const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+      const uint32_t a_lo_const = ((p.a_mn ? 8192u : 16u) >> 4) << 16, b_lo_const = ((p.b_mn ? 8192u : 16u) >> 4) << 16;
+      const uint32_t a_step16 = (p.a_mn ? 2048u : 32u) >> 4, b_step16 = (p.b_mn ? 2048u : 32u) >> 4;
       int stage = 0;
       uint32_t phase = 0;
       uint32_t gchunk = 0;  // accumulator hand-offs so far; buffer = gchunk & 1
@@ -533,18 +557,25 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         for (int ch = 0; ch < chunks_per_tile && ok; ++ch, ++gchunk) {
           int kb_begin, kb_end;
           chunk_range(ch, kb_begin, kb_end);
-          const int buf = gchunk & 1u;
-          const long long w0 = p.prof ? clock64() : 0;
-          const bool got_acc = ptx::mbar_wait(tempty_bar(buf), ((gchunk >> 1) & 1u) ^ 1u, kWaitCycles);
-          if (p.prof) prof_acc += clock64() - w0;
-          if (!got_acc || *abort_flag) {
-            report(p.status, kTimeoutMma);
-            raise_abort();
-            ok = false;
-            break;
-          }
-          ptx::tc_fence_after();
-          const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+          // The wide tile has one accumulator of two halves, each with its own "drained" barrier (tempty 0 / 1): the
+          // MMAs of the first k-block's first half start as soon as that half has been read out.
+          const int buf = kWide ? 0 : (int)(gchunk & 1u);
+          const uint32_t acc_parity = (kWide ? (gchunk & 1u) : ((gchunk >> 1) & 1u)) ^ 1u;
+          auto wait_drained = [&](int bar) {
+            const long long w0 = p.prof ? clock64() : 0;
+            const bool got_acc = ptx::mbar_wait(tempty_bar(bar), acc_parity, kWaitCycles);
+            if (p.prof) prof_acc += clock64() - w0;
+            if (!got_acc || *abort_flag) {
+              report(p.status, kTimeoutMma);
+              raise_abort();
+              ok = false;
+              return false;
+            }
+            ptx::tc_fence_after();
+            return true;
+          };
+          if (!wait_drained(buf)) break;
+          const uint32_t d_tmem = tmem_base + (uint32_t)(kWide ? 0 : buf * BN);
           for (int kb = kb_begin; kb < kb_end; ++kb) {
             const long long w1 = p.prof ? clock64() : 0;
             const bool got_ops = ptx::mbar_wait(full_bar(stage), phase, kWaitCycles);
@@ -557,14 +588,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
             }
             ptx::tc_fence_after();
             const uint32_t sa = base + stage * S::kStageBytes;
-            const uint32_t sb = sa + S::kABytes;
+            const uint32_t a_lo = ((sa & 0x3FFFFu) >> 4) | a_lo_const;
+            const uint32_t b_lo = (((sa + S::kABytes) & 0x3FFFFu) >> 4) | b_lo_const;
+            const uint32_t fresh = (kb != kb_begin) ? 1u : 0u;
 #pragma unroll
-            for (int k = 0; k < kBK / kUmmaK; ++k) {
-              const uint64_t da = ptx::smem_desc(sa + k * a_step, a_lbo, 1024u);
-              const uint64_t db = ptx::smem_desc(sb + k * b_step, b_lbo, 1024u);
-              if constexpr (kPair) ptx::mma_f16_pair(d_tmem, da, db, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
-              else ptx::mma_f16(d_tmem, da, db, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
+            for (int j = 0; j < NJ; ++j) {
+              if (kWide && j == 1 && kb == kb_begin && !wait_drained(1)) break;
+#pragma unroll
+              for (int k = 0; k < kBK / kUmmaK; ++k) {
+                const uint64_t da = ((uint64_t)desc_hi << 32) | (a_lo + k * a_step16);
+                const uint64_t db = ((uint64_t)desc_hi << 32) | (b_lo + j * ((BNI / 2) * kBK * 2 / 16) + k * b_step16);
+                if constexpr (kPair) ptx::mma_f16_pair(d_tmem + j * BNI, da, db, idesc, k != 0 ? 1u : fresh);
+                else ptx::mma_f16(d_tmem, da, db, idesc, k != 0 ? 1u : fresh);
+              }
             }
+            if (!ok) break;
             // frees the stage (in both CTAs of a pair) once these MMAs have read it
             if constexpr (kPair) {
               ptx::mma_commit_pair(empty_bar(stage));
@@ -596,7 +634,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
     }
   }
   } else {
-    ptx::reg_inc<232>();
+    ptx::reg_inc<224>();
     // ------------------------------------------------------------ epilogue (warps 4..11)
     // Warp w may read TMEM lanes [32*(w&3), +32); two warps share a lane group and split the columns.
     constexpr int NCH = BN / 64;  // 32-column chunks per warp
@@ -621,7 +659,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
       auto wait_chain = [&](int buf) {
         const long long w0 = p.prof ? clock64() : 0;
         // every lane observes the barrier itself, so each one is ordered after the MMAs' TMEM writes
-        const int waited = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), (gchunk >> 1) & 1u, kWaitCycles) ? 1 : 0);
+        const uint32_t parity = kWide ? (gchunk & 1u) : ((gchunk >> 1) & 1u);
+        const int waited = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(buf), parity, kWaitCycles) ? 1 : 0);
         if (!waited || *abort_flag) {
           if (lane == 0) {
             report(p.status, kTimeoutEpilogue);
@@ -642,7 +681,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         }
       };
       auto tmem_of = [&](int buf) {
-        return tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * BN + half * (BN / 2));
+        return tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)((kWide ? 0 : buf * BN) + half * (BN / 2));
       };
 
       if (chained) {
@@ -674,7 +713,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
           if (p.prof) prof_sum += clock64() - a0;
         }
         if (!alive) break;
-      } else if (!wait_chain(gchunk & 1u)) {
+      } else if (!wait_chain(kWide ? 0 : (int)(gchunk & 1u))) {
         alive = false;
         break;
       }
@@ -695,7 +734,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
       e.S1b = p.S1 ? p.S1 + (long long)b * p.s_bs : nullptr;
       float ssq = 0.f, mabs = 0.f, maff = 0.f, mres = 0.f;
       const bool rows_inside = row_first + 32 <= p.M;
-      const uint32_t taddr = tmem_of(gchunk & 1u);
+      const uint32_t taddr = tmem_of(kWide ? 0 : (int)(gchunk & 1u));
       float* const mine = stage + lane * kEpiStride;
 #pragma unroll 1
       for (int cc = 0; cc < NCH; ++cc) {
@@ -741,7 +780,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         }
       }
       if (!chained) {
-        release(gchunk & 1u);
+        // wide tile: this warp read columns of half `half` only, and that half's barrier counts its four lane groups
+        // of both CTAs
+        release(kWide ? half : (int)(gchunk & 1u));
         ++gchunk;
       }
       if (p.prof) prof_out += clock64() - o0;
@@ -762,7 +803,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tcgen05_kernel(const __g
         }
       }
     }
-    if (p.prof && warp == 4 && lane == 0) {
+    if (p.prof && leader && warp == 4 && lane == 0) {
       atomicAdd(p.prof + 4, (unsigned long long)prof_wait);
       atomicAdd(p.prof + 5, (unsigned long long)prof_out);
       atomicAdd(p.prof + 6, (unsigned long long)prof_sum);

@@ -84,6 +84,7 @@ Context* context() {
   cudaFuncSetAttribute(gemm_tcgen05_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<128>::kTotal);
   cudaFuncSetAttribute(gemm_tcgen05_kernel<256, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256, true>::kTotal);
   cudaFuncSetAttribute(gemm_tcgen05_kernel<256, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256, true>::kTotal);
+  cudaFuncSetAttribute(gemm_tcgen05_kernel<512, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<512, true>::kTotal);
   c.device = dev;
   return &c;
 }
@@ -186,20 +187,32 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
     if (tpair >= ctx->gemm_sms / 2) {
       bn = 256;
       pair = true;
+      // The wide tile: long accumulations only (its epilogue is not hidden behind the next tile), enough tiles for
+      // several waves, and a width for which the 512-column steps do not overshoot the triangle by much.
+      const long long twide = (long long)gemm_tiles_per_batch(d.m, d.n, 512, d.tri, 256) * d.batch;
+      const long long depth = (long long)d.k * d.segs;
+      if (ctx->gemm_wide_k > 0 && d.promote <= 0 && depth >= ctx->gemm_wide_k && twide >= 4LL * (ctx->gemm_sms / 2) &&
+          2 * twide * 100 <= tpair * 106)
+        bn = 512;
     } else {
       bn = (t256 >= ctx->gemm_sms) ? 256 : 128;
     }
   } else if (bn == 512) {
     bn = 256;
     pair = true;
+  } else if (bn == 1024) {
+    if (d.promote > 0) return fail(kErrArg, "gemm: the wide tile has no chained accumulation");
+    bn = 512;
+    pair = true;
   }
-  if (bn != 128 && bn != 256) return fail(kErrArg, "gemm: tile_n must be 0, 128, 256 or 512 (256 x 256 on a CTA pair)");
+  if (bn != 128 && bn != 256 && !(bn == 512 && pair))
+    return fail(kErrArg, "gemm: tile_n must be 0, 128, 256, 512 (256 x 256 on a CTA pair) or 1024 (256 x 512 on a pair)");
 
   GemmParams p;
   std::memset(&p, 0, sizeof(p));
   int rc = get_maps(ctx, d.a, d.batch, kBM, stream, &p.a_maps);
   if (rc) return rc;
-  rc = get_maps(ctx, d.b, d.batch, pair ? bn / 2 : bn, stream, &p.b_maps);
+  rc = get_maps(ctx, d.b, d.batch, pair ? 128 : bn, stream, &p.b_maps);  // a pair's CTA loads B in boxes of 128 rows
   if (rc) return rc;
   p.a_map_stride = d.a.list ? 1 : 0;
   p.b_map_stride = d.b.list ? 1 : 0;
@@ -254,7 +267,7 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
     cfg.blockDim = dim3(kGemmThreads);
-    cfg.dynamicSmemBytes = GemmSmem<256, true>::kTotal;
+    cfg.dynamicSmemBytes = bn == 512 ? GemmSmem<512, true>::kTotal : GemmSmem<256, true>::kTotal;
     cfg.stream = stream;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
@@ -263,7 +276,8 @@ int launch_gemm(const toner_gemm_desc& d, cudaStream_t stream) {
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    if (chained) TONER_CUDA(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<256, true, true>, p));
+    if (bn == 512) TONER_CUDA(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<512, false, true>, p));
+    else if (chained) TONER_CUDA(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<256, true, true>, p));
     else TONER_CUDA(cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<256, false, true>, p));
     count_launch();
     return 0;

@@ -35,6 +35,7 @@ struct Context {
   int device = -1;
   int num_sms = 0;
   int gemm_sms = 0;  // CTAs the persistent GEMM may occupy (toner_set_gemm_sm_limit)
+  int gemm_wide_k = 16384;  // accumulation depth (k x segments) from which 256 x 512 tiles are chosen; 0: never
   CUtensorMap* arena_dev = nullptr;   // tensor maps live here; slots are never rewritten between resets
   CUtensorMap* arena_host = nullptr;  // pinned mirror used as the copy source
   int arena_cap = 0, arena_used = 0;

@@ -297,7 +297,7 @@ def main():
     ap.add_argument("--mode", default="ema", choices=["ema", "packed"])
     ap.add_argument("--split", action="store_true")
     ap.add_argument("--tri", action="store_true")
-    ap.add_argument("--tile", type=int, default=0, help="force a tile: 128, 256, or 512 for 256x256 on CTA pairs (0: the library chooses)")
+    ap.add_argument("--tile", type=int, default=0, help="force a tile: 128, 256, 512 for 256x256 on CTA pairs, 1024 for 256x512 on pairs (0: the library chooses)")
     ap.add_argument("--promote", type=int, default=ops.PROMOTE_ACCURATE, help="k-blocks per accumulation chain of a split product")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--reps", type=int, default=10)
