@@ -268,7 +268,8 @@ __global__ void __launch_bounds__(256) damp_kernel(const float* __restrict__ c, 
 
 // FP16 hi/lo planes of the two operands the iteration starts from, from A (FP32, damped and normalised):
 //   M_0 = A / ||A||_F  (scaled by s_m)      T_0 = a I - b M_0  (scaled by s_t)      X_1 = T_0
-// planes layout [2][batch][n][n], hi plane first.
+// planes layout [2][batch][n][n], hi plane first.  With t_planes == nullptr only the hi plane of M_0 is written (all
+// that the single-pass squarings of the norm bound read).
 __global__ void __launch_bounds__(256) init_planes_kernel(const float* __restrict__ a32, int n, int batch,
                                                           const float* __restrict__ sumsq, float a, float b, float s_m,
                                                           float s_t, __half* __restrict__ m_planes,
@@ -289,6 +290,12 @@ __global__ void __launch_bounds__(256) init_planes_kernel(const float* __restric
     const float4 v = A[i];
     const float m[4] = {v.x * f, v.y * f, v.z * f, v.w * f};
     __half h[4], l[4], g[4], k[4];
+    if (t_planes == nullptr) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) h[e] = __float2half_rn(m[e] * s_m);
+      *reinterpret_cast<uint2*>(mh + i * 4) = *reinterpret_cast<uint2*>(h);
+      continue;
+    }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float x = m[e] * s_m;
@@ -445,28 +452,36 @@ __global__ void __launch_bounds__(256) rank1_update_kernel(float* __restrict__ a
 // Vectors are stored vector-major: v[(b * vstride + j) * n + c].
 constexpr int kMaxDeflate = 8;
 
-// Y_j = A v_j, j < r: one pass over A.  A block takes 32 rows (four per warp) and walks the columns 256 at a time; the
-// 256-column slice of all r vectors is staged in shared memory once per block, so the vectors are read from L2 once per
+// Y_j = A v_j, j < R: one pass over A.  A block takes 32 rows (four per warp) and walks the columns 256 at a time; the
+// 256-column slice of the vectors is staged in shared memory once per block, so the vectors are read from L2 once per
 // 32 rows instead of once per row pair (that traffic, not the pass over A, bounded the first version of this kernel).
-// Eight products at a time are summed in FP32, the partial sums in FP64 (see gemv_kernel).
+// The products of four slices (32 per lane) are summed in FP32 before they join the FP64 sums: conversions and FP64
+// additions run at a fraction of the FP32 rate, and with one per eight products they, not the pass over A, set the
+// pace.  R (the number of vectors, rounded up to even) is a template argument so that absent vectors cost nothing.
 constexpr int kBlockGemvRows = 32;
+template <int R>
 __global__ void __launch_bounds__(256) block_gemv_kernel(const float* __restrict__ a, const float* __restrict__ v,
                                                          float* __restrict__ y, int n, int r, int vstride) {
-  __shared__ float4 sv[kMaxDeflate][64];
+  __shared__ float4 sv[R][64];
   const int b = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row0 = blockIdx.x * kBlockGemvRows + warp * 4;
   const float* V = v + (long long)b * vstride * n;
   const float* A = a + (long long)b * n * n;
-  double acc[4][kMaxDeflate];
+  double acc[4][R];
+  float part[4][R];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
-    for (int j = 0; j < kMaxDeflate; ++j) acc[i][j] = 0.0;
+    for (int j = 0; j < R; ++j) {
+      acc[i][j] = 0.0;
+      part[i][j] = 0.f;
+    }
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int c0 = 0; c0 < n; c0 += 256) {
+  int slice = 0;
+  for (int c0 = 0; c0 < n; c0 += 256, ++slice) {
     __syncthreads();  // the previous slice has been read
-    for (int i = threadIdx.x; i < kMaxDeflate * 64; i += 256) {
+    for (int i = threadIdx.x; i < R * 64; i += 256) {
       const int j = i >> 6, col = c0 + (i & 63) * 4;
       sv[j][i & 63] = (j < r && col < n) ? *reinterpret_cast<const float4*>(V + (long long)j * n + col) : zero;
     }
@@ -480,20 +495,29 @@ __global__ void __launch_bounds__(256) block_gemv_kernel(const float* __restrict
         const float4 p0 = ca < n ? *reinterpret_cast<const float4*>(Ar + ca) : zero;
         const float4 p1 = cb < n ? *reinterpret_cast<const float4*>(Ar + cb) : zero;
 #pragma unroll
-        for (int j = 0; j < kMaxDeflate; ++j) {
+        for (int j = 0; j < R; ++j) {
           const float4 x0 = sv[j][lane], x1 = sv[j][lane + 32];
           const float s0 = fmaf(p0.x, x0.x, fmaf(p0.y, x0.y, fmaf(p0.z, x0.z, p0.w * x0.w)));
           const float s1 = fmaf(p1.x, x1.x, fmaf(p1.y, x1.y, fmaf(p1.z, x1.z, p1.w * x1.w)));
-          acc[i][j] += (double)(s0 + s1);
+          part[i][j] += s0 + s1;
         }
       }
+    }
+    if ((slice & 3) == 3) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+          acc[i][j] += (double)part[i][j];
+          part[i][j] = 0.f;
+        }
     }
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
 #pragma unroll
-    for (int j = 0; j < kMaxDeflate; ++j) {
-      double t = acc[i][j];
+    for (int j = 0; j < R; ++j) {
+      double t = acc[i][j] + (double)part[i][j];
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
       if (lane == 0 && j < r && row0 + i < n) y[((long long)b * vstride + j) * n + row0 + i] = (float)t;
@@ -1099,7 +1123,11 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
       count_launch();
       const int sweeps = defl_cold ? 8 : 4;
       for (int sw = 0; sw < sweeps; ++sw) {
-        block_gemv_kernel<<<dim3((n + kBlockGemvRows - 1) / kBlockGemvRows, kc), 256, 0, stream>>>(A32, dv, py, n, defl_r, kMaxDeflate);
+        const dim3 bg((n + kBlockGemvRows - 1) / kBlockGemvRows, kc);
+        if (defl_r <= 2) block_gemv_kernel<2><<<bg, 256, 0, stream>>>(A32, dv, py, n, defl_r, kMaxDeflate);
+        else if (defl_r <= 4) block_gemv_kernel<4><<<bg, 256, 0, stream>>>(A32, dv, py, n, defl_r, kMaxDeflate);
+        else if (defl_r <= 6) block_gemv_kernel<6><<<bg, 256, 0, stream>>>(A32, dv, py, n, defl_r, kMaxDeflate);
+        else block_gemv_kernel<8><<<bg, 256, 0, stream>>>(A32, dv, py, n, defl_r, kMaxDeflate);
         count_launch();
         ritz_kernel<<<kc, 256, 0, stream>>>(dv, py, n, defl_r, kMaxDeflate, sw == sweeps - 1 ? 1 : 0, th8, res8);
         count_launch();
@@ -1131,7 +1159,7 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
     }
     float s_t = plane_scale(sched[0].a);
     init_planes_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(A32, n, kc, sumsq_a, (float)sched[0].a, (float)sched[0].b, s_m,
-                                                                s_t, Mb[0], Tb[0], Xb[1]);
+                                                                s_t, Mb[0], nullptr, nullptr);
     count_launch();
     TONER_CUDA(cudaGetLastError());
     {
