@@ -115,6 +115,7 @@ class FactorSet:
         self.bound_failures = 0
         self.status_event: Optional[torch.cuda.Event] = None
         self.health = ops.Health()
+        self._root_bounds = None
         self.lo_planes = torch.empty(2, k, n, n, device=device, dtype=torch.float16)
         self.lo_inv = torch.empty(k, device=device, dtype=torch.float32)
         if self.q > 1:
@@ -193,10 +194,15 @@ class FactorSet:
         self.lower, self.lower_is_estimate, self.track_restart, self.estimate_backoff = 0.0, False, True, 0
 
     def _split(self) -> None:
-        tmp = self.scratch.get("split_max", (self.k,), torch.int32, self.device)
-        ops.split16(self.root_lo, planes=self.lo_planes, inv_scale=self.lo_inv, scratch=tmp)
+        # Operand planes of the roots, scaled by a bound known without a pass over them: the statistic is factored
+        # with damping added, so no entry of A^-s exceeds damping^-s.
+        if self._root_bounds is None:
+            bits = lambda s: torch.full((self.k,), 1.01 * self.damping ** -s, device=self.device,
+                                        dtype=torch.float32).view(torch.int32)
+            self._root_bounds = (bits(1.0 / self.p), bits(self.q / self.p))
+        ops.split16(self.root_lo, planes=self.lo_planes, inv_scale=self.lo_inv, maxabs=self._root_bounds[0])
         if self.q > 1:
-            ops.split16(self.root_hi, planes=self.hi_planes, inv_scale=self.hi_inv, scratch=tmp)
+            ops.split16(self.root_hi, planes=self.hi_planes, inv_scale=self.hi_inv, maxabs=self._root_bounds[1])
             ops.sumsq(self.root_hi, out=self.fro2_hi,
                       scratch=self.scratch.bytes_like("sumsq", ops.sumsq_scratch_bytes(self.k), self.device))
 

@@ -925,11 +925,15 @@ __global__ void lmin_from_root_kernel(const float* __restrict__ theta, float pow
 // Per statistic: the scale that turns M_0^{-1/p} into A^{-1/p}, and the convergence status from the
 // distance max|I - M| gathered when the last M was produced (0 converged, 1 above tol, 2 non-finite).
 // 3: the statistic's spectrum reaches below the lower bound the schedule was built for (caller's bound too high).
+// Also the bound of the finished root's entries for its operand planes: a symmetric positive matrix has no entry above
+// its largest eigenvalue, and A >= damping I by construction, so |A^(-1/p)|_ij <= damping^(-1/p) -- known without a
+// pass over the result.
 __global__ void finish_kernel(const unsigned int* __restrict__ resid, const float* __restrict__ sumsq_a,
                               float* root_scale_lo, int* status, float* norm_out, int k, int p, float tol, float damping,
-                              float lower_used) {
+                              float lower_used, unsigned int* __restrict__ root_max_bits, float root_bound) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= k) return;
+  root_max_bits[b] = __float_as_uint(root_bound);
   const float ub = sqrtf(fmaxf(sumsq_a[b], 1e-60f));
   root_scale_lo[b] = powf(ub, -1.f / p);
   if (norm_out) norm_out[b] = ub;
@@ -1258,7 +1262,7 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
           // fold ||A||_F^{-1/p} into the product; the distance of M from I was gathered when M was produced
           finish_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(resid, sumsq_a, scale_lo, status ? status + k0 : nullptr,
                                                             norm_out ? norm_out + k0 : nullptr, kc, p, 0.5f, damping,
-                                                            lower_used);
+                                                            lower_used, max_r, (float)root_bound);
           count_launch();
           TONER_CUDA(cudaGetLastError());
           // Tcur holds planes of R = I - M and A32 the FP32 M (both from the last update of M).  Horner steps
@@ -1298,7 +1302,7 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
           rc = sumsq_det(R, kc, n, n, n, nn, partials, fro_tmp, stream);
           if (rc) return rc;
           if (q > 1) {  // operand planes of the finished root for the squarings below
-            rc = split16(R, nullptr, kc, n, n, n, nn, 0.f, 1.f, nullptr, max_r, Xb[xi], inv_r, stream);
+            rc = split16(R, nullptr, kc, n, n, n, nn, 0.f, 1.f, max_r, nullptr, Xb[xi], inv_r, stream);
             if (rc) return rc;
           }
           Xcur = Xb[xi];
