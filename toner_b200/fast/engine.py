@@ -194,23 +194,25 @@ class FastTonerCore:
             if [it[0] for it in items] != list(range(layers)):
                 raise ValueError(f"role {role} must have exactly one matrix per layer")
             plan.append((role, items))
-        # Exchange layout.  The roles are worked through largest matrices first, and their changes sit in two flat
-        # buffers: the first is all-gathered (one large NCCL transfer) while the roles of the second are still being
-        # computed, the second right after them.  One buffer when there is nothing to exchange.
+        # Exchange layout.  Roles of one matrix shape go through Newton-Schulz together and their changes sit in one flat
+        # buffer (a "part"); the parts are worked through largest first, and each is all-gathered (one large NCCL
+        # transfer) while the next ones are still being computed.  Only the last part's transfer has nothing to hide
+        # behind, and it is the smallest.  One buffer when there is nothing to exchange.
         plan.sort(key=lambda pr: -pr[1][0][2].numel())
-        sizes = [items[0][2].numel() for _, items in plan]   # per layer: the split must not depend on what a rank owns
-        cut = len(plan)
         if world > 1 and len(plan) > 1:
-            acc = 0
-            for i, size in enumerate(sizes[:-1]):
-                acc += size
-                if acc >= 0.55 * sum(sizes):
-                    cut = i + 1
-                    break
+            by_shape: Dict[Tuple[int, ...], List[int]] = {}
+            for i, (_, items) in enumerate(plan):
+                by_shape.setdefault(tuple(items[0][2].shape), []).append(i)
+            groups_of = sorted(by_shape.values(), key=lambda idx: -sum(plan[i][1][0][2].numel() for i in idx))
+            plan = [plan[i] for idx in groups_of for i in idx]
+            bounds, at = [], 0
+            for idx in groups_of:
+                bounds.append((at, at + len(idx)))
+                at += len(idx)
+        else:
+            bounds = [(0, len(plan))]
         self.parts = []
-        for lo_i, hi_i in ((0, cut), (cut, len(plan))):
-            if lo_i == hi_i:
-                continue
+        for lo_i, hi_i in bounds:
             numels = [items[0][2].numel() for _, items in plan[lo_i:hi_i]]
             unit = sum(numels)                                   # elements one layer contributes to this part
             total = self.per_layers * unit
