@@ -269,8 +269,14 @@ int toner_inv_roots_ex(const float* ema, int32_t k, int32_t n, float damping, in
  *                  bits 0..7; bits 8..15: how many Ritz values stand above that mark whether converged or not.
  *                  Outlier features of an activation statistic are such directions; each one deflated lowers
  *                  lambda_max(A') and with it the number of Newton steps.
- * The upper end needs no estimate: norm_out is a certified bound, the smallest of ||A'||_F times ||P^2||_F^(1/2),
- * ||P^4||_F^(1/4), ||P^8||_F^(1/8) (three single-pass squarings). */
+ * The upper end: norm_out is a certified bound, the smallest of ||A'||_F times ||P^2||_F^(1/2), ||P^4||_F^(1/4),
+ * ||P^8||_F^(1/8) (three single-pass squarings).  With 512 added to deflate_rank (only with lower_is_estimate = 1 and
+ * without 256) it is an estimate instead and the squarings are skipped: 1.4 times the largest Ritz value of the block
+ * iteration that was NOT deflated, never above ||A'||_F.  That value errs low, by up to a fifth at the dense edge of
+ * a bulk, once its vector is a few calls old (the caller's business: a fresh slot's value sits near the mean
+ * eigenvalue).  An eigenvalue of
+ * A' / norm above 1 comes out of the first Newton step below the lower bound and lags like one below `lower`; the
+ * verification looks for it with four more steps from that Ritz vector, status 4 as above. */
 int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
                             float lower, int32_t lower_is_estimate, float* root_lo, float* root_hi, float* fro2_lo,
                             int32_t* status, float* norm_out, float* track, float* lmin_out, float* resid_out,

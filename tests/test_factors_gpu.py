@@ -374,3 +374,64 @@ def test_block_deflation_of_outlier_directions(ops):
                 top = torch.linalg.eigh(c.double())[1][:, -5:]
                 inside = (vectors[b, :5].double().cpu() @ top).norm(dim=1)
                 assert (inside > 1 - 1e-6).all()
+
+
+def test_norm_from_the_block_iteration(ops):
+    """Once the block's vectors have followed a statistic for a few calls, the largest Ritz value that was not deflated
+    (times 1.4) replaces the certified norm bound and its three squarings: the norm reported stays above lambda_max of
+    what is left and close to it, the schedule is no longer, nothing is flagged and the roots are as exact as before."""
+    from toner_b200 import core
+    n, k = 512, 3
+    f = core.FactorSet(k, n, torch.device("cuda"), (0.5, 0.125), DAMPING)
+    f.ema.copy_(_activation_like(n, 8192, seed=21, k=k))
+    seen = []
+    for call in range(6):
+        f.compute()
+        assert f.finish() == 0
+        seen.append((f.ritz_in_flight, f.iterations, f.finish_order, f.norms_host.clone()))
+    assert not seen[0][0] and not seen[1][0] and seen[-1][0], [s[0] for s in seen]
+    assert f.repairs == 0 and f.fallbacks == 0 and f.bound_failures == 0
+    certified = next(s for s in seen if not s[0] and s[1] <= 3)           # a tracked call before the switch
+    assert seen[-1][1] == certified[1] and seen[-1][2] <= certified[2] + 1, (seen[-1][:3], certified[:3])
+    for b in range(k):
+        _, true_max = _extremes(f.ema[b])
+        est = seen[-1][3][b].item()
+        assert true_max < est < 1.5 * true_max, (true_max, est)           # above lambda_max(A'), and close to it
+        c = f.ema[b].cpu()
+        assert orc.rel_fro(f.root_lo[b].cpu(), orc.inverse_root_truth(c, 0.125, DAMPING)) < 5e-5
+        assert orc.rel_fro(f.root_hi[b].cpu(), orc.inverse_root_truth(c, 0.5, DAMPING)) < 2e-4
+
+
+def test_a_norm_estimate_that_is_too_low_is_caught(ops):
+    """The Ritz value is only as good as its vector.  Vectors that miss the top of the spectrum (here: exact
+    eigenvectors from its middle, which a few sweeps do not leave) give a norm below lambda_max; the statistic's largest
+    eigenvalues then start ABOVE 1, lag or diverge, and every statistic must come back flagged, never silently wrong.
+    With the vectors a proper call leaves behind the same request succeeds."""
+    n, k = 384, 2
+    stats = torch.stack([spd(n, 30.0, 31), spd(n, 30.0, 32)]).cuda()      # no outliers: nothing is deflated
+    norms, lmin = torch.zeros(k, device="cuda"), torch.zeros(k, device="cuda")
+    track, vectors = torch.zeros(k, n, device="cuda"), torch.zeros(k, 8, n, device="cuda")
+    count = torch.zeros(k, device="cuda", dtype=torch.int32)
+    kw = dict(norms=norms, track=track, lmin=lmin, deflate=vectors, deflate_rank=4, deflated=count)
+    ops.inv_roots(stats, DAMPING, 8, 4, track_sweeps=12, track_restart=True, deflate_restart=True, **kw)
+    lo_ref, hi_ref, _, st = ops.inv_roots(stats, DAMPING, 8, 4, track_sweeps=4, **kw)
+    assert st.tolist() == [0] * k and (count & 255).tolist() == [0] * k
+    lower = 0.5 * float((lmin / norms).min())
+    good = vectors.clone()
+    lo, hi, _, st = ops.inv_roots(stats, DAMPING, 8, 4, lower=lower, lower_is_estimate=True, track_sweeps=4,
+                                  ritz_norm=True, **kw)
+    ops.assert_healthy()
+    assert st.tolist() == [0] * k
+    for b in range(k):
+        assert orc.rel_fro(lo[b].cpu(), lo_ref[b].cpu()) < 5e-5 and orc.rel_fro(hi[b].cpu(), hi_ref[b].cpu()) < 2e-4
+    for b in range(k):
+        c = stats[b].double().cpu()
+        vec = torch.linalg.eigh(0.5 * (c + c.T))[1]
+        vectors[b, :4] = vec[:, n // 2: n // 2 + 4].T.float().cuda()
+    _, _, _, st = ops.inv_roots(stats, DAMPING, 8, 4, lower=lower, lower_is_estimate=True, track_sweeps=4,
+                                ritz_norm=True, **kw)
+    ops.assert_healthy()
+    assert all(s in (1, 4) for s in st.tolist()), st.tolist()
+    vectors.copy_(good)
+    with pytest.raises(Exception):       # the norm estimate is verified together with an estimated lower bound only
+        ops.inv_roots(stats, DAMPING, 8, 4, lower=lower, track_sweeps=4, ritz_norm=True, **kw)

@@ -110,6 +110,9 @@ class FactorSet:
         self.deflated_host = torch.zeros(k, dtype=torch.int32).pin_memory()
         self.deflate_rank = 4
         self.block_deflation = True      # False: the engine's own single-vector deflation (one dominant direction)
+        self.ritz_norm = True            # the norm from the block iteration once it has followed the statistic for two steps
+        self._warm_calls = 0             # tracked calls in a row whose vectors came from the call before
+        self._rank_used = 0              # block width of the last call
         self.lower_is_estimate = False
         self.estimate_backoff = 0        # steps left during which only certified bounds are used (after a bound failed)
         self.bound_failures = 0
@@ -166,6 +169,16 @@ class FactorSet:
         """Enqueue the Newton factor computation and the operand split of the results."""
         if self.k == 0 or (self.inner_strength == 0 and self.outer_strength == 0):
             return
+        blocked = self.tracking and self.block_deflation
+        # The largest Ritz value left in the statistic replaces the norm bound's three squarings when the vector it
+        # belongs to is at least two calls old (a fresh slot's Rayleigh quotient sits near the MEAN eigenvalue) and the
+        # lower bound is an estimate as well, so that both are verified after the chain.
+        ritz = (blocked and self.ritz_norm and self.lower_is_estimate and not self.track_restart
+                and self._warm_calls >= 2
+                and int((self.deflated_host & 255).max()) < min(self._rank_used, self.deflate_rank))
+        self._warm_calls = 0 if (self.track_restart or not blocked) else self._warm_calls + 1
+        self._rank_used = self.deflate_rank if blocked else 0
+        self.ritz_in_flight = bool(ritz)
         ops.inv_roots(self.ema, self.damping, self.p, self.q, root_lo=self.root_lo, root_hi=self.root_hi,
                       fro2_lo=self.fro2_lo, status=self.status, workspace=self.workspace, lower=self.lower,
                       norms=self.norms, lower_is_estimate=self.lower_is_estimate,
@@ -174,7 +187,8 @@ class FactorSet:
                       track_restart=self.track_restart,
                       deflate=self.deflate if self.tracking and self.block_deflation else None,
                       deflate_rank=self.deflate_rank,
-                      deflate_restart=self.track_restart, deflated=self.deflated if self.tracking else None)
+                      deflate_restart=self.track_restart, deflated=self.deflated if self.tracking else None,
+                      ritz_norm=ritz)
         self.track_restart = False
         self._estimate_in_flight = self.lower_is_estimate
         self.iterations = (ops.inv_roots_iterations_for(self.lower, self.p) if self.lower > 0
@@ -192,6 +206,7 @@ class FactorSet:
     def statistics_replaced(self) -> None:
         """The EMAs were overwritten from outside (a checkpoint): nothing learnt from earlier factorisations applies."""
         self.lower, self.lower_is_estimate, self.track_restart, self.estimate_backoff = 0.0, False, True, 0
+        self._warm_calls = 0
 
     def _split(self) -> None:
         # Operand planes of the roots, scaled by a bound known without a pass over them: the statistic is factored

@@ -778,9 +778,11 @@ __global__ void __launch_bounds__(256) ritz_kernel(float* __restrict__ v, float*
 // Which of the r Ritz pairs are deflated: in descending order, as long as each has converged and stands above eight
 // times the mean c of everything that would remain; all accepted directions are moved to that common c.
 //   coef[b][j] = -(theta_j - c)  (0 where not deflated)      corr[b][j] = theta_j^(-1/p) - c^(-1/p)
+// rest_top[b] / rest_idx[b]: the largest Ritz value that stays in A' and its vector's index (0 / -1 when every vector of
+// the block was deflated: nothing is known about the remainder then).
 __global__ void block_decide_kernel(const float* __restrict__ theta, const float* __restrict__ res, int k, int n, int r,
                                     float damping, int p, float* __restrict__ coef, float* __restrict__ corr,
-                                    int* __restrict__ count) {
+                                    int* __restrict__ count, float* __restrict__ rest_top, int* __restrict__ rest_idx) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= k) return;
   const double tr = (double)n * (1.0 + (double)damping);  // A has unit mean diagonal plus the damping
@@ -807,6 +809,34 @@ __global__ void block_decide_kernel(const float* __restrict__ theta, const float
   for (int j = 0; j < r; ++j)
     if ((double)theta[b * kMaxDeflate + j] > 8.0 * c) ++cand;
   if (count) count[b] = m | (cand << 8);
+  const float rest = m < r ? theta[b * kMaxDeflate + m] : 0.f;
+  const bool known = m < r && isfinite(rest) && rest > 0.f;
+  rest_top[b] = known ? rest : 0.f;
+  rest_idx[b] = known ? m : -1;
+}
+
+// An ESTIMATE of lambda_max(A') in place of the certified bound: kRitzGrow times the largest Ritz value that was not
+// deflated, never above the Frobenius norm already in bound2.  A Rayleigh quotient errs low, and at the dense upper
+// edge of an activation statistic's bulk it stays low however long the block has followed the statistic: 17-20 % on
+// the benchmark's statistics (Marchenko-Pastur edges 1.36 and 1.63, Ritz values 1.08 and 1.30).  The factor leaves
+// ten percent above that.  Three squarings give n^(1/16) = 1.7 times lambda_max for a flat spectrum and cost three
+// passes; what the estimate risks -- eigenvalues of M_0 above 1, which the first Newton step sends BELOW the new lower
+// bound -- is looked for after the chain (see the verification).
+constexpr float kRitzGrow = 1.4f;
+__global__ void ritz_norm_kernel(float* __restrict__ bound2, const float* __restrict__ rest_top, int k) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= k) return;
+  const float t = kRitzGrow * rest_top[b];
+  if (t > 0.f && t * t < bound2[b]) bound2[b] = t * t;
+}
+
+// v2[b] = the Ritz vector rest_idx[b] of statistic b (zero where there is none)
+__global__ void __launch_bounds__(256) pick_vector_kernel(const float* __restrict__ v, const int* __restrict__ idx,
+                                                          float* __restrict__ out, int n, int vstride) {
+  const int b = blockIdx.y;
+  const int j = idx[b];
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
+    out[(long long)b * n + i] = j >= 0 ? v[((long long)b * vstride + j) * n + i] : 0.f;
 }
 
 // A_b += sum_j coef[b][j] v_bj v_bj^T  (terms with a zero coefficient are skipped; exact symmetry is kept: the
@@ -904,11 +934,12 @@ __global__ void __launch_bounds__(256) power_shift_kernel(float* __restrict__ v,
 
 // status 4 where the distance of the last M from the identity, estimated by power iteration on I - M, exceeds what the
 // schedule was built for: the caller's estimate of the spectrum's lower end was too high for this statistic.
-__global__ void verify_kernel(const float* __restrict__ e_est, float e_allowed, int* __restrict__ status, float* __restrict__ e_out,
-                              int k) {
+__global__ void verify_kernel(const float* __restrict__ e_est, const float* __restrict__ e_top, float e_allowed,
+                              int* __restrict__ status, float* __restrict__ e_out, int k) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= k) return;
-  const float e = e_est[b];
+  float e = e_est[b];
+  if (e_top) e = isfinite(e_top[b]) ? fmaxf(e, e_top[b]) : e_top[b];
   if (e_out) e_out[b] = e;
   if (status && status[b] == 0 && (!isfinite(e) || e > e_allowed)) status[b] = 4;
 }
@@ -951,10 +982,10 @@ static size_t per_statistic_bytes(int n) {
   return align_up((size_t)n * n * 4, 256) * 8;
 }
 static size_t small_bytes(int chunk, int n) {
-  // sixteen per-statistic scalars, four blocks of eight scalars per statistic (Ritz values, residuals, deflation
+  // twenty per-statistic scalars, four blocks of eight scalars per statistic (Ritz values, residuals, deflation
   // coefficients, root corrections), the reduction scratch, and two blocks of eight n-vectors per statistic
   // (block power iteration: V and A V)
-  return align_up((size_t)chunk * 4, 256) * 16 + 4 * align_up((size_t)chunk * 32, 256) +
+  return align_up((size_t)chunk * 4, 256) * 20 + 4 * align_up((size_t)chunk * 32, 256) +
          align_up(sumsq_scratch_bytes(chunk), 256) + 2 * align_up((size_t)chunk * 8 * n * 4, 256);
 }
 
@@ -1032,8 +1063,13 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
   if (track_sweeps < 0 || (track_sweeps & ~(63 | 256))) return fail(kErrArg, "inv_roots: track_sweeps is 0..63, plus 256 to start afresh");
   const int defl_r = deflate ? (deflate_rank & 15) : 0;      // directions the block iteration looks for (0: one, the old way)
   const bool defl_cold = deflate && (deflate_rank & 256);
-  if (deflate && (defl_r < 1 || defl_r > kMaxDeflate || (deflate_rank & ~(15 | 256))))
-    return fail(kErrArg, "inv_roots: deflate_rank is 1..8, plus 256 to start from fixed vectors");
+  const bool ritz_norm = deflate && (deflate_rank & 512);   // norm from the block iteration instead of three squarings
+  if (deflate && (defl_r < 1 || defl_r > kMaxDeflate || (deflate_rank & ~(15 | 256 | 512))))
+    return fail(kErrArg, "inv_roots: deflate_rank is 1..8, plus 256 to start from fixed vectors, plus 512 to take the "
+                         "norm from the block iteration");
+  if (ritz_norm && (defl_cold || !estimated))
+    return fail(kErrArg, "inv_roots: the norm estimate needs vectors from an earlier call and an estimated lower bound "
+                         "(both are verified together after the chain)");
   // > 0: certified bound, checked against damping / norm per statistic; < 0: estimate, verified after the chain
   const float lower_used = l0 > l_worst ? (estimated ? -(float)l0 : (float)l0) : 0.f;
   if (iters <= 0) iters = default_iterations(l0, p);
@@ -1100,8 +1136,11 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
     float* ss8 = small(13);
     float* e_est = small(14);
     float* theta = small(15);
+    float* rest_top = small(16);
+    int* rest_idx = reinterpret_cast<int*>(small(17));
+    float* e_top = small(18);
     const size_t sm8 = align_up((size_t)kc * 32, 256);
-    char* wp = w + sm * 16;
+    char* wp = w + sm * 20;
     float* th8 = reinterpret_cast<float*>(wp); wp += sm8;     // Ritz values, residuals, deflation coefficients and
     float* res8 = reinterpret_cast<float*>(wp); wp += sm8;    // root corrections of the block deflation: eight per statistic
     float* coef8 = reinterpret_cast<float*>(wp); wp += sm8;
@@ -1111,7 +1150,7 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
     float* pv = reinterpret_cast<float*>(wp);
     float* py = reinterpret_cast<float*>(wp + vec);
     float* dv = deflate ? deflate + (long long)k0 * kMaxDeflate * n : nullptr;
-    TONER_CUDA(cudaMemsetAsync(w, 0, sm * 16 + 4 * sm8, stream));
+    TONER_CUDA(cudaMemsetAsync(w, 0, sm * 20 + 4 * sm8, stream));
 
     const float* C = ema + (long long)k0 * nn;
     const int t32 = (n + 31) / 32;
@@ -1137,7 +1176,7 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
         count_launch();
       }
       block_decide_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(th8, res8, kc, n, defl_r, damping, p, coef8, corr8,
-                                                               deflated_out ? deflated_out + k0 : nullptr);
+                                                               deflated_out ? deflated_out + k0 : nullptr, rest_top, rest_idx);
       count_launch();
       rankr_update_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(A32, dv, coef8, n, defl_r, kMaxDeflate);
       count_launch();
@@ -1162,6 +1201,14 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
       if (rc0) return rc0;
     }
     float s_t = plane_scale(sched[0].a);
+    if (ritz_norm) {
+      ritz_norm_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(sumsq_a, rest_top, kc);
+      count_launch();
+      init_planes_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(A32, n, kc, sumsq_a, (float)sched[0].a, (float)sched[0].b,
+                                                                  s_m, s_t, Mb[0], Tb[0], Xb[1]);
+      count_launch();
+      TONER_CUDA(cudaGetLastError());
+    } else {
     init_planes_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(A32, n, kc, sumsq_a, (float)sched[0].a, (float)sched[0].b, s_m,
                                                                 s_t, Mb[0], nullptr, nullptr);
     count_launch();
@@ -1211,6 +1258,7 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
                                                                   s_m, s_t, Mb[0], Tb[0], Xb[1]);
       count_launch();
       TONER_CUDA(cudaGetLastError());
+    }
     }
 
     // D = (A planes) * (B planes)^T / (sa * sb): symmetric result, FP32-accurate; outputs as requested
@@ -1407,7 +1455,25 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
           power_shift_kernel<<<kc, 256, 0, stream>>>(pv, py, n, e_est);
           count_launch();
         }
-        verify_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(e_est, (float)(1.15 * (1.0 - l_last) + 1e-3),
+        if (ritz_norm) {
+          // The norm was an estimate too.  Eigenvalues of M_0 above 1 (the estimate was too low for them) come out of
+          // the first Newton step BELOW the lower bound the schedule continues from -- T = a I - b M is small there --
+          // and lag the same way; they belong to the top of A', so the same four steps from the largest Ritz vector
+          // that stayed in A' find them.  (An eigenvalue beyond a / b, where T changes sign, makes M grow instead and
+          // fails the convergence test.)
+          float* pv2 = pv + (long long)kc * n;
+          float* py2 = py + (long long)kc * n;
+          pick_vector_kernel<<<dim3(8, kc), 256, 0, stream>>>(dv, rest_idx, pv2, n, kMaxDeflate);
+          count_launch();
+          for (int sw = 0; sw < 4; ++sw) {
+            gemv_kernel<<<dim3((n + 7) / 8, kc), 256, 0, stream>>>(A32, pv2, py2, n);
+            count_launch();
+            power_shift_kernel<<<kc, 256, 0, stream>>>(pv2, py2, n, e_top);
+            count_launch();
+          }
+        }
+        verify_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(e_est, ritz_norm ? e_top : nullptr,
+                                                          (float)(1.15 * (1.0 - l_last) + 1e-3),
                                                           status ? status + k0 : nullptr,
                                                           resid_out ? resid_out + k0 : nullptr, kc);
         count_launch();

@@ -310,7 +310,7 @@ def inv_roots(ema: torch.Tensor, damping: float, p: int, q: int = 1, *, iters: i
               track: Optional[torch.Tensor] = None, lmin: Optional[torch.Tensor] = None,
               resid: Optional[torch.Tensor] = None, track_sweeps: int = 0, track_restart: bool = False,
               deflate: Optional[torch.Tensor] = None, deflate_rank: int = 1, deflate_restart: bool = False,
-              deflated: Optional[torch.Tensor] = None):
+              deflated: Optional[torch.Tensor] = None, ritz_norm: bool = False):
     """A^(-1/p) and A^(-q/p) of the damped, trace-normalised statistics (toner_inv_roots_tracked).
 
     ``lower``: a lower bound of the normalised spectrum valid for every statistic (0: the bound that always
@@ -318,7 +318,8 @@ def inv_roots(ema: torch.Tensor, damping: float, p: int, q: int = 1, *, iters: i
     bound can be derived.  ``track`` (k, n), ``lmin`` (k,), ``track_sweeps``, ``track_restart``, ``lower_is_estimate``,
     ``resid`` (k,): tracking of the smallest eigenvalue between calls and a bound that is an estimate, verified after
     the chain; ``deflate`` (k, 8, n), ``deflate_rank``, ``deflate_restart``, ``deflated`` (k,) int32: several dominant
-    directions found by block power iteration and deflated (see the header).
+    directions found by block power iteration and deflated (see the header); ``ritz_norm``: take the norm from that
+    iteration's largest remaining Ritz value instead of three squarings (an estimate, verified with ``lower``).
     Returns (root_lo, root_hi or None, fro2_lo, status); nothing is synchronised."""
     _need_cuda(ema)
     if ema.ndim == 2:
@@ -345,7 +346,7 @@ def inv_roots(ema: torch.Tensor, damping: float, p: int, q: int = 1, *, iters: i
     sweeps = (int(track_sweeps) & 63) | (256 if track_restart else 0)
     if deflate is not None and (deflate.shape != (k, 8, n) or deflate.dtype != torch.float32 or not deflate.is_contiguous()):
         raise ValueError("the deflation vectors are a contiguous FP32 (k, 8, n) tensor")
-    rank = (int(deflate_rank) & 15) | (256 if deflate_restart else 0)
+    rank = (int(deflate_rank) & 15) | (256 if deflate_restart else 0) | (512 if ritz_norm else 0)
     check(_lib.load().toner_inv_roots_tracked(ema.data_ptr(), k, n, damping, p, q, iters, lower, int(lower_is_estimate),
                                               root_lo.data_ptr(), _ptr(root_hi), fro2_lo.data_ptr(), status.data_ptr(),
                                               _ptr(norms), _ptr(track), _ptr(lmin), _ptr(resid), sweeps,
