@@ -140,6 +140,13 @@ def roots_traffic(k: int, n: int) -> int:
     return int(564e6 * k * n * n / (8 * 2048 * 2048))
 
 
+# The update phase's largest launch is the Newton-Schulz x-update of the widest role group (x <- a x + B x: reads B and x
+# in BF16 and x in FP32, writes x in FP32 and BF16).  Its capture on 24 matrices of 2048^2 (section 5 of the same
+# summary) moved 821 + 553 MB; the traffic is proportional to the number of elements of x.
+def update_traffic(count: int, m: int, n: int) -> int:
+    return int(1374e6 * count * m * n / (24 * 2048 * 2048))
+
+
 def tri_fraction(n: int, bm: int = 128, bn: int = 256) -> float:
     """Share of the bm x bn result tiles that meet the upper triangle of an n x n symmetric product."""
     tm, tn = -(-n // bm), -(-n // bn)
@@ -379,13 +386,17 @@ def run_fast(args, w: Workload) -> None:
                 per_phase[name] = {"ms": round(ph[name], 3), "tflops_per_gpu": round(work / world / ph[name] / 1e9, 1)}
         if "exchange" in ph and "update" in per_phase:
             per_phase["update"]["exchange_ms"] = round(ph["exchange"], 3)
+        for v in per_phase.values():
+            v["frac"] = round(v["tflops_per_gpu"] / pk["tflops"], 4)
         top = max(per_phase, key=lambda k: per_phase[k]["ms"]) if per_phase else None
         roof = None
         if top:
             a = per_phase[top]["tflops_per_gpu"]
             roof = {"bound": "tensor", "kernel": "gemm_tcgen05_kernel", "phase": top, "achieved": a, "peak": pk["tflops"],
                     "unit": "TFLOP/s", "frac": round(a / pk["tflops"], 4),
-                    "traffic": (roots_traffic(layers // world, mlp) if top == "roots" else None),
+                    "traffic": (roots_traffic(layers // world, mlp) if top == "roots" else
+                                update_traffic(2 * layers // world, mlp, hidden) if top == "update" and w.layout == "llama"
+                                else None),
                     "peak_source": pk["source"] + " (sustained cuBLAS BF16: the kernel runs inside a long step)",
                     "note": "achieved = algorithmic single-pass flops of the phase / its CUDA-event time on the launching "
                             "stream; the phase is >97% this kernel by ncu share"}
