@@ -435,3 +435,42 @@ def test_a_norm_estimate_that_is_too_low_is_caught(ops):
     vectors.copy_(good)
     with pytest.raises(Exception):       # the norm estimate is verified together with an estimated lower bound only
         ops.inv_roots(stats, DAMPING, 8, 4, lower=lower, track_sweeps=4, ritz_norm=True, **kw)
+
+
+def test_abrupt_changes_of_the_statistic_are_never_silently_wrong(ops):
+    """FactorSet carries estimates of both ends of the spectrum and a block of vectors from step to step.  When the
+    statistic changes abruptly under it -- new outlier directions of every strength, another mean, an ill-conditioned
+    bulk, and back -- those are stale.  The a-posteriori checks must then flag, the repair round must run, and the
+    roots handed to the optimizer must be right at EVERY step, flagged or not."""
+    from toner_b200 import core
+    n, k, rows = 384, 3, 3072
+    g = torch.Generator().manual_seed(77)
+
+    def stat(kind, seed):
+        gg = torch.Generator().manual_seed(seed)
+        x = torch.randn(rows, n, generator=gg) + 0.5 * torch.randn(1, n, generator=torch.Generator().manual_seed(5))
+        if kind.startswith("spike"):
+            strength = float(kind[5:])
+            d, _ = torch.linalg.qr(torch.randn(n, 3, generator=gg))
+            x = x + (torch.randn(rows, 3, generator=gg) * torch.tensor([1.0, 0.7, 0.5]) * strength) @ d.T
+        elif kind == "mean":
+            x = x + 2.0 * torch.randn(1, n, generator=gg)
+        elif kind == "ill":
+            return spd(n, 1e4, seed)
+        return x.T @ x / rows
+
+    f = core.FactorSet(k, n, torch.device("cuda"), (0.5, 0.125), DAMPING)
+    plan = ["iid"] * 5 + ["spike1.5"] * 3 + ["spike3"] * 3 + ["spike12"] * 4 + ["iid"] * 4 + ["mean"] * 3 + ["ill"] * 4 + ["iid"] * 5
+    used_estimate = False
+    for step, kind in enumerate(plan):
+        f.ema.copy_(torch.stack([stat(kind, 1000 + 10 * plan.index(kind) + b) for b in range(k)]))
+        f.compute()
+        used_estimate = used_estimate or f.ritz_in_flight
+        f.finish()
+        for b in range(k):
+            c = f.ema[b].cpu()
+            e_lo = orc.rel_fro(f.root_lo[b].cpu(), orc.inverse_root_truth(c, 0.125, DAMPING))
+            e_hi = orc.rel_fro(f.root_hi[b].cpu(), orc.inverse_root_truth(c, 0.5, DAMPING))
+            assert e_lo < 2e-4 and e_hi < 6e-4, (step, kind, b, e_lo, e_hi, f.repairs, f.fallbacks)
+    assert used_estimate                      # the norm estimate was in use when the changes came
+    print(f"repairs {f.repairs}, eigendecomposition fallbacks {f.fallbacks}, bound failures {f.bound_failures}")
