@@ -474,3 +474,20 @@ def test_abrupt_changes_of_the_statistic_are_never_silently_wrong(ops):
             assert e_lo < 2e-4 and e_hi < 6e-4, (step, kind, b, e_lo, e_hi, f.repairs, f.fallbacks)
     assert used_estimate                      # the norm estimate was in use when the changes came
     print(f"repairs {f.repairs}, eigendecomposition fallbacks {f.fallbacks}, bound failures {f.bound_failures}")
+
+
+def test_wide_tiles_in_the_factor_engine_give_the_same_bits(ops):
+    """Three 5632-wide statistics in one call are enough tiles for the 256 x 512 tile variant of the deep split-precision
+    products (X T, the finishing product, the squarings of the root); one statistic per call runs the same products on
+    256 x 256 tiles.  Every element is accumulated in the same order either way, so the roots must be bit-identical --
+    this pins the wide variant's operand-plane outputs, mirrored halves and affine epilogue inside the engine."""
+    n, k = 5632, 3
+    stats = _activation_like(n, 8192, seed=41, k=k)
+    lo, hi, _, st = ops.inv_roots(stats, DAMPING, 8, 4)
+    ops.assert_healthy()
+    assert st.tolist() == [0] * k
+    for b in range(k):
+        lo1, hi1, _, st1 = ops.inv_roots(stats[b:b + 1].contiguous(), DAMPING, 8, 4)
+        assert st1.tolist() == [0]
+        assert torch.equal(lo[b], lo1[0]) and torch.equal(hi[b], hi1[0]), b
+    ops.assert_healthy()

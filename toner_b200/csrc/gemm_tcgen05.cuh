@@ -2,7 +2,7 @@
 //
 //   D[b] = alpha_b * sum_seg A_seg[b] * B_seg[b]^T   (+ beta_b * C[b])
 //
-// One persistent CTA per SM, warp-specialised:
+// One persistent CTA per SM (or one CTA pair per SM pair: cta_group::2, 256 x 256 or 256 x 512 tiles), warp-specialised:
 //   warp 0      TMA producer: 128-byte-swizzled operand tiles into a shared-memory ring
 //   warp 1      allocates tensor memory and issues tcgen05.mma (one thread), accumulating in TMEM
 //   warps 4..11 epilogue: tcgen05.ld the accumulator (double-buffered, so it overlaps the next chain's
