@@ -270,11 +270,24 @@ __global__ void __launch_bounds__(256) damp_kernel(const float* __restrict__ c, 
 //   M_0 = A / ||A||_F  (scaled by s_m)      T_0 = a I - b M_0  (scaled by s_t)      X_1 = T_0
 // planes layout [2][batch][n][n], hi plane first.  With t_planes == nullptr only the hi plane of M_0 is written (all
 // that the single-pass squarings of the norm bound read).
+// With defl_v the input is A and the deflation A' = A + sum_j coef[j] v_j v_j^T is applied on the way (the terms of
+// rankr_update_kernel, in its order), so that A' is never written.
 __global__ void __launch_bounds__(256) init_planes_kernel(const float* __restrict__ a32, int n, int batch,
                                                           const float* __restrict__ sumsq, float a, float b, float s_m,
                                                           float s_t, __half* __restrict__ m_planes,
-                                                          __half* __restrict__ t_planes, __half* __restrict__ x_planes) {
+                                                          __half* __restrict__ t_planes, __half* __restrict__ x_planes,
+                                                          const float* __restrict__ defl_v = nullptr,
+                                                          const float* __restrict__ defl_coef = nullptr, int defl_r = 0,
+                                                          int vstride = 0) {
   const int bi = blockIdx.y;
+  float cf[8];
+  bool any = false;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    cf[j] = (defl_v != nullptr && j < defl_r) ? defl_coef[bi * 8 + j] : 0.f;
+    any = any || cf[j] != 0.f;
+  }
+  const float* DV = defl_v ? defl_v + (long long)bi * vstride * n : nullptr;
   const long long nn = (long long)n * n;
   const float4* A = reinterpret_cast<const float4*>(a32 + bi * nn);
   const float f = rsqrtf(fmaxf(sumsq[bi], 1e-60f));
@@ -287,7 +300,18 @@ __global__ void __launch_bounds__(256) init_planes_kernel(const float* __restric
   const int n4 = n / 4;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nn / 4; i += (long long)gridDim.x * blockDim.x) {
     const int r = (int)(i / n4), c = (int)(i - (long long)r * n4) * 4;
-    const float4 v = A[i];
+    float4 v = A[i];
+    if (any) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (cf[j] != 0.f) {
+          const float vr = DV[(long long)j * n + r];
+          const float4 vc = *reinterpret_cast<const float4*>(DV + (long long)j * n + c);
+          v.x = fmaf(cf[j], vr * vc.x, v.x); v.y = fmaf(cf[j], vr * vc.y, v.y);
+          v.z = fmaf(cf[j], vr * vc.z, v.z); v.w = fmaf(cf[j], vr * vc.w, v.w);
+        }
+      }
+    }
     const float m[4] = {v.x * f, v.y * f, v.z * f, v.w * f};
     __half h[4], l[4], g[4], k[4];
     if (t_planes == nullptr) {
@@ -450,7 +474,7 @@ __global__ void __launch_bounds__(256) rank1_update_kernel(float* __restrict__ a
 // statistic per sweep, whatever r is, and converges with the ratio of the (r+1)-th eigenvalue to the wanted one, so
 // close pairs among the dominant ones do not slow it down; the vectors are kept by the caller between calls.
 // Vectors are stored vector-major: v[(b * vstride + j) * n + c].
-constexpr int kMaxDeflate = 8;
+constexpr int kMaxDeflate = 8;  // (init_planes_kernel keeps that many coefficients in registers)
 
 // Y_j = A v_j, j < R: one pass over A.  A block takes 32 rows (four per warp) and walks the columns 256 at a time; the
 // 256-column slice of the vectors is staged in shared memory once per block, so the vectors are read from L2 once per
@@ -782,7 +806,8 @@ __global__ void __launch_bounds__(256) ritz_kernel(float* __restrict__ v, float*
 // the block was deflated: nothing is known about the remainder then).
 __global__ void block_decide_kernel(const float* __restrict__ theta, const float* __restrict__ res, int k, int n, int r,
                                     float damping, int p, float* __restrict__ coef, float* __restrict__ corr,
-                                    int* __restrict__ count, float* __restrict__ rest_top, int* __restrict__ rest_idx) {
+                                    int* __restrict__ count, float* __restrict__ rest_top, int* __restrict__ rest_idx,
+                                    float* __restrict__ rest_trace) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= k) return;
   const double tr = (double)n * (1.0 + (double)damping);  // A has unit mean diagonal plus the damping
@@ -813,30 +838,38 @@ __global__ void block_decide_kernel(const float* __restrict__ theta, const float
   const bool known = m < r && isfinite(rest) && rest > 0.f;
   rest_top[b] = known ? rest : 0.f;
   rest_idx[b] = known ? m : -1;
+  rest_trace[b] = (float)(c * (double)n);   // trace of A' (every deflated direction moved to c): above its Frobenius norm
 }
 
 // An ESTIMATE of lambda_max(A') in place of the certified bound: kRitzGrow times the largest Ritz value that was not
-// deflated, never above the Frobenius norm already in bound2.  A Rayleigh quotient errs low, and at the dense upper
+// deflated, never above the trace of A' (which bounds its Frobenius norm).  A Rayleigh quotient errs low, and at the dense upper
 // edge of an activation statistic's bulk it stays low however long the block has followed the statistic: 17-20 % on
 // the benchmark's statistics (Marchenko-Pastur edges 1.36 and 1.63, Ritz values 1.08 and 1.30).  The factor leaves
 // ten percent above that.  Three squarings give n^(1/16) = 1.7 times lambda_max for a flat spectrum and cost three
 // passes; what the estimate risks -- eigenvalues of M_0 above 1, which the first Newton step sends BELOW the new lower
 // bound -- is looked for after the chain (see the verification).
 constexpr float kRitzGrow = 1.4f;
-__global__ void ritz_norm_kernel(float* __restrict__ bound2, const float* __restrict__ rest_top, int k) {
+__global__ void ritz_norm_kernel(float* __restrict__ bound2, const float* __restrict__ rest_top,
+                                 const float* __restrict__ rest_trace, int k) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= k) return;
+  const float cap = rest_trace[b];      // ||A'||_F <= trace(A') for a positive matrix: costs no pass over A'
   const float t = kRitzGrow * rest_top[b];
-  if (t > 0.f && t * t < bound2[b]) bound2[b] = t * t;
+  bound2[b] = (t > 0.f && t < cap) ? t * t : cap * cap;
 }
 
 // v2[b] = the Ritz vector rest_idx[b] of statistic b (zero where there is none)
-__global__ void __launch_bounds__(256) pick_vector_kernel(const float* __restrict__ v, const int* __restrict__ idx,
-                                                          float* __restrict__ out, int n, int vstride) {
+// out[b][0] = first[b] (the tracked direction), out[b][1] = the Ritz vector rest_idx[b] of statistic b (zero where there
+// is none): the two starting vectors of the verification, side by side for the two-vector pass over M
+__global__ void __launch_bounds__(256) pick_vector_kernel(const float* __restrict__ first, const float* __restrict__ v,
+                                                          const int* __restrict__ idx, float* __restrict__ out, int n,
+                                                          int vstride) {
   const int b = blockIdx.y;
   const int j = idx[b];
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x)
-    out[(long long)b * n + i] = j >= 0 ? v[((long long)b * vstride + j) * n + i] : 0.f;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    out[((long long)b * 2) * n + i] = first[(long long)b * n + i];
+    out[((long long)b * 2 + 1) * n + i] = j >= 0 ? v[((long long)b * vstride + j) * n + i] : 0.f;
+  }
 }
 
 // A_b += sum_j coef[b][j] v_bj v_bj^T  (terms with a zero coefficient are skipped; exact symmetry is kept: the
@@ -895,11 +928,13 @@ __global__ void tighten_bound_kernel(float* __restrict__ bound2, const float* __
 
 // v <- (v - y) / ||v - y||  with y = M v:  one power-iteration step on R = I - M;  e[b] = the Rayleigh quotient of R at
 // the incoming v, 1 - v.y / v.v (0 where v is zero: nothing is known).
+// Vector j = blockIdx.y of statistic b sits at (b * vs + j) * n; its quotient goes to e[j * e_stride + b].
 __global__ void __launch_bounds__(256) power_shift_kernel(float* __restrict__ v, const float* __restrict__ y, int n,
-                                                          float* __restrict__ e) {
+                                                          float* __restrict__ e, int vs = 1, long long e_stride = 0) {
   const int b = blockIdx.x;
-  float* V = v + (long long)b * n;
-  const float* Y = y + (long long)b * n;
+  float* V = v + ((long long)b * vs + blockIdx.y) * n;
+  const float* Y = y + ((long long)b * vs + blockIdx.y) * n;
+  e += (long long)blockIdx.y * e_stride;
   __shared__ double red[3][8];
   __shared__ double tot[3];
   double vy = 0.0, vv = 0.0, tt = 0.0;
@@ -1139,6 +1174,7 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
     float* rest_top = small(16);
     int* rest_idx = reinterpret_cast<int*>(small(17));
     float* e_top = small(18);
+    float* rest_trace = small(19);
     const size_t sm8 = align_up((size_t)kc * 32, 256);
     char* wp = w + sm * 20;
     float* th8 = reinterpret_cast<float*>(wp); wp += sm8;     // Ritz values, residuals, deflation coefficients and
@@ -1176,10 +1212,13 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
         count_launch();
       }
       block_decide_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(th8, res8, kc, n, defl_r, damping, p, coef8, corr8,
-                                                               deflated_out ? deflated_out + k0 : nullptr, rest_top, rest_idx);
+                                                               deflated_out ? deflated_out + k0 : nullptr, rest_top, rest_idx,
+                                                               rest_trace);
       count_launch();
-      rankr_update_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(A32, dv, coef8, n, defl_r, kMaxDeflate);
-      count_launch();
+      if (!ritz_norm) {   // (with the norm estimate the deflation is applied where the operand planes are formed)
+        rankr_update_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(A32, dv, coef8, n, defl_r, kMaxDeflate);
+        count_launch();
+      }
     } else {
       // dominant direction: six power-iteration steps, then deflate where they converged
       power_start_kernel<<<dim3(8, kc), 256, 0, stream>>>(pv, n);
@@ -1196,16 +1235,19 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
       count_launch();
     }
     TONER_CUDA(cudaGetLastError());
-    {
+    if (!ritz_norm) {
       int rc0 = sumsq_det(A32, kc, n, n, n, nn, partials, sumsq_a, stream);
       if (rc0) return rc0;
     }
     float s_t = plane_scale(sched[0].a);
     if (ritz_norm) {
-      ritz_norm_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(sumsq_a, rest_top, kc);
+      // Neither A' nor its Frobenius norm is formed: the norm is the estimate (capped by the trace), and the planes of
+      // M_0 and T_0 are made from A with the deflation applied on the way.
+      ritz_norm_kernel<<<(kc + 127) / 128, 128, 0, stream>>>(sumsq_a, rest_top, rest_trace, kc);
       count_launch();
       init_planes_kernel<<<dim3(ew_blocks, kc), 256, 0, stream>>>(A32, n, kc, sumsq_a, (float)sched[0].a, (float)sched[0].b,
-                                                                  s_m, s_t, Mb[0], Tb[0], Xb[1]);
+                                                                  s_m, s_t, Mb[0], Tb[0], Xb[1], dv, coef8, defl_r,
+                                                                  kMaxDeflate);
       count_launch();
       TONER_CUDA(cudaGetLastError());
     } else {
@@ -1448,27 +1490,27 @@ int toner_inv_roots_tracked(const float* ema, int32_t k, int32_t n, float dampin
         // and they are the dominant eigenvalues of R = I - M of the last M (kept in FP32): four power-iteration steps
         // on R from the tracked direction (the eigenvector of the smallest eigenvalue, as of the previous call) find
         // them.  The allowance: the assumed distance with 15 % and the noise floor of the estimate.
-        TONER_CUDA(cudaMemcpyAsync(pv, vt, sizeof(float) * (size_t)kc * n, cudaMemcpyDeviceToDevice, stream));
-        for (int sw = 0; sw < 4; ++sw) {
-          gemv_kernel<<<dim3((n + 7) / 8, kc), 256, 0, stream>>>(A32, pv, py, n);
-          count_launch();
-          power_shift_kernel<<<kc, 256, 0, stream>>>(pv, py, n, e_est);
-          count_launch();
-        }
         if (ritz_norm) {
           // The norm was an estimate too.  Eigenvalues of M_0 above 1 (the estimate was too low for them) come out of
           // the first Newton step BELOW the lower bound the schedule continues from -- T = a I - b M is small there --
           // and lag the same way; they belong to the top of A', so the same four steps from the largest Ritz vector
           // that stayed in A' find them.  (An eigenvalue beyond a / b, where T changes sign, makes M grow instead and
-          // fails the convergence test.)
-          float* pv2 = pv + (long long)kc * n;
-          float* py2 = py + (long long)kc * n;
-          pick_vector_kernel<<<dim3(8, kc), 256, 0, stream>>>(dv, rest_idx, pv2, n, kMaxDeflate);
+          // fails the convergence test.)  Both starting vectors go through M in one pass per step.
+          pick_vector_kernel<<<dim3(8, kc), 256, 0, stream>>>(vt, dv, rest_idx, pv, n, kMaxDeflate);
           count_launch();
+          const dim3 bg((n + kBlockGemvRows - 1) / kBlockGemvRows, kc);
           for (int sw = 0; sw < 4; ++sw) {
-            gemv_kernel<<<dim3((n + 7) / 8, kc), 256, 0, stream>>>(A32, pv2, py2, n);
+            block_gemv_kernel<2><<<bg, 256, 0, stream>>>(A32, pv, py, n, 2, 2);
             count_launch();
-            power_shift_kernel<<<kc, 256, 0, stream>>>(pv2, py2, n, e_top);
+            power_shift_kernel<<<dim3(kc, 2), 256, 0, stream>>>(pv, py, n, e_est, 2, (long long)(e_top - e_est));
+            count_launch();
+          }
+        } else {
+          TONER_CUDA(cudaMemcpyAsync(pv, vt, sizeof(float) * (size_t)kc * n, cudaMemcpyDeviceToDevice, stream));
+          for (int sw = 0; sw < 4; ++sw) {
+            gemv_kernel<<<dim3((n + 7) / 8, kc), 256, 0, stream>>>(A32, pv, py, n);
+            count_launch();
+            power_shift_kernel<<<kc, 256, 0, stream>>>(pv, py, n, e_est);
             count_launch();
           }
         }
