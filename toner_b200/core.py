@@ -249,7 +249,9 @@ class FactorSet:
             self.estimate_backoff -= 1
         if all(c in (0, 4) or (c == 1 and getattr(self, "_estimate_in_flight", False)) for c in codes) \
                 and math.isfinite(top) and top > 0:
-            hint = 0.6 * self.damping / top
+            # (a norm taken from the block iteration is an estimate and sits up to a third below the certified bound
+            # the device will check this hint against)
+            hint = 0.6 * self.damping / (top * (1.5 if getattr(self, "ritz_in_flight", False) else 1.0))
             if worst < hint < 1.0:
                 self.lower = hint
             if self.tracking and not self.estimate_backoff and not bad:
