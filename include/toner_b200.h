@@ -204,9 +204,10 @@ int toner_split16(const float* x, const float* const* x_list, int32_t batch, int
  *     fro2_lo[b] = ||root_lo[b]||_F^2  (gives the decay normalisation n / ||R||_F^2, src/toner/linalg.py:87-88)
  * Method: coupled Newton iteration T = a I - b M, X <- X T, M <- T^p M with minimax-scaled (a, b), batched
  * over the k statistics, all products FP32-accurate on tensor cores (FP16 hi/lo planes, three plane products
- * per accumulator).  The last of the `iters` steps applies the binomial series of (I - R)^(-1/p), R = I - M, to X
- * alone; its order (toner_inv_roots_finish_order_for) follows from the bound on R the schedule guarantees, and
- * its order - 1 products are single passes over FP16 planes of R.
+ * per accumulator).  The last of the `iters` steps applies a polynomial q(R) ~ (I - R)^(-1/p), R = I - M, to X
+ * alone: the Chebyshev interpolant of (1 - r)^(-1/p) on [-0.02, 1.15 e + 1e-3] of the smallest degree with relative
+ * error below 3e-6, e being the bound on R the schedule guarantees (toner_inv_roots_finish_order_for,
+ * toner_inv_roots_schedule); its degree - 1 products are single passes over FP16 planes of R.
  * `iters` <= 0 selects toner_inv_roots_iterations(n, damping, p), which depends only on
  * its arguments (8 for p = 8, 8 for p = 4, 10 for p = 2 at n = 5632, damping 1e-3): the count with the fewest
  * plane passes, Newton steps and series together.
@@ -218,8 +219,17 @@ int toner_split16(const float* x, const float* const* x_list, int32_t batch, int
 size_t toner_inv_roots_workspace_bytes(int32_t chunk, int32_t n);
 int toner_inv_roots_iterations(int32_t n, float damping, int32_t p);
 int toner_inv_roots_iterations_for(float lower, int32_t p);   /* the count for a given spectrum lower bound */
-/* order of the finishing series for that bound and count (iters <= 0: the default count); 0 on bad arguments */
+/* degree of the finishing polynomial for that bound and count (iters <= 0: the default count); 0 on bad arguments */
 int toner_inv_roots_finish_order_for(float lower, int32_t p, int32_t iters);
+/* The whole schedule the engine runs for a spectrum lower bound (host only, no device needed): returns the step count
+ * (iters <= 0: the default), and writes the (a_k, b_k) of its count - 1 Newton steps (ab_out: pairs of doubles, as many
+ * as ab_capacity holds), the degree of the finishing polynomial (order_out), its coefficients c_0 .. c_degree in powers
+ * of r (coef_out, as many as coef_capacity holds; at most 13), and the distance e of the last M from I it is cut for
+ * (e_out).  Every output pointer is optional.  0 on bad arguments.  With these a scalar can be taken through exactly
+ * what the engine does to every eigenvalue: x = 1, mu = lambda; per step t = a - b mu, x *= t, mu *= t^p; finally
+ * x * q(1 - mu) = lambda^(-1/p). */
+int toner_inv_roots_schedule(float lower, int32_t p, int32_t iters, double* ab_out, int32_t ab_capacity, double* coef_out,
+                             int32_t coef_capacity, int32_t* order_out, double* e_out);
 int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
                     float* root_lo, float* root_hi, float* fro2_lo, int32_t* status, void* workspace,
                     size_t workspace_bytes, void* stream);

@@ -155,3 +155,45 @@ def test_flat_exchange_layout_with_uneven_ownership():
     assert len(seen) == layers * len(shapes)
     for (role, layer), vals in seen.items():
         assert vals == [100.0 * list(shapes).index(role) + layer]
+
+
+@pytest.mark.parametrize("p", [2, 4, 8])
+def test_the_stated_schedule_takes_every_eigenvalue_to_its_root(p):
+    """toner_inv_roots_schedule states everything the factor engine does to an eigenvalue: the Newton coefficients
+    (a_k, b_k) and the finishing polynomial.  Taking scalars through it on the host -- x = 1, mu = lambda; t = a - b mu,
+    x *= t, mu *= t^p per step; then x q(1 - mu) -- must give lambda^(-1/p) for every lambda the bound allows; mu must
+    never exceed 1 (the iteration would leave the interval its coefficients were levelled for) and must end within the
+    stated distance of 1."""
+    import numpy as np
+    from toner_b200 import ops
+    for lower in (2e-7, 1e-5, 1e-3, 0.03, 0.12, 0.3, 0.6):
+        s = ops.inv_roots_schedule(lower, p)
+        assert s["iterations"] == ops.inv_roots_iterations_for(lower, p) >= 2
+        assert len(s["steps"]) == s["iterations"] - 1
+        lam = np.exp(np.linspace(np.log(float(np.float32(lower))), 0.0, 4001))   # (the entry point takes a float)
+        x, mu = np.ones_like(lam), lam.copy()
+        for a, b in s["steps"]:
+            t = a - b * mu
+            assert (t > 0).all()
+            x, mu = x * t, mu * t ** p
+            assert mu.max() <= 1.0 + 1e-9, (p, lower, mu.max())
+        assert 1.0 - mu.min() <= s["distance"] * (1 + 1e-6) + 1e-9, (p, lower)
+        q = np.polyval(np.array(s["coefficients"])[::-1], 1.0 - mu)
+        assert np.abs(x * q * lam ** (1.0 / p) - 1.0).max() < 5e-6, (p, lower)
+
+
+def test_finishing_polynomial_holds_its_tolerance():
+    """The Chebyshev fit of (1 - r)^(-1/p) the engine finishes with: relative error below 3e-6 on the interval it is
+    stated for, [-0.02, 1.15 e + 1e-3], and coefficients without cancellation."""
+    import numpy as np
+    from toner_b200 import ops
+    for p in (2, 4, 8):
+        for lower in (1e-6, 1e-4, 1e-2, 0.05, 0.1, 0.2, 0.4):
+            s = ops.inv_roots_schedule(lower, p)
+            c, e = np.array(s["coefficients"]), s["distance"]
+            assert 0 < e < 0.6 and 2 <= len(c) - 1 <= 12
+            hi = 1.15 * e + 1e-3
+            r = np.linspace(-0.02, hi, 2001)
+            q = np.polyval(c[::-1], r)
+            assert np.abs(q * (1 - r) ** (1.0 / p) - 1).max() < 3.2e-6, (p, lower)
+            assert (np.abs(c) * hi ** np.arange(len(c))).sum() <= 2.5 + 1e-9

@@ -78,6 +78,8 @@ SIGNATURES = {
     "toner_inv_roots": (C.c_int, [_vp, _i32, _i32, _f32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "toner_inv_roots_iterations_for": (C.c_int, [_f32, _i32]),
     "toner_inv_roots_finish_order_for": (C.c_int, [_f32, _i32, _i32]),
+    "toner_inv_roots_schedule": (C.c_int, [_f32, _i32, _i32, C.POINTER(C.c_double), _i32, C.POINTER(C.c_double), _i32,
+                                           C.POINTER(_i32), C.POINTER(C.c_double)]),
     "toner_inv_roots_ex": (C.c_int, [_vp, _i32, _i32, _f32, _i32, _i32, _i32, _f32, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "toner_inv_roots_tracked": (C.c_int, [_vp, _i32, _i32, _f32, _i32, _i32, _i32, _f32, _i32, _vp, _vp, _vp, _vp, _vp, _vp,
                                           _vp, _vp, _i32, _vp, _i32, _vp, _vp, _sz, _vp]),

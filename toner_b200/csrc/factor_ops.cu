@@ -1058,6 +1058,28 @@ int toner_inv_roots_finish_order_for(float lower, int32_t p, int32_t iters) {
   return toner::finish_order(p, 1.0 - l_last);
 }
 
+int toner_inv_roots_schedule(float lower, int32_t p, int32_t iters, double* ab_out, int32_t ab_capacity, double* coef_out,
+                             int32_t coef_capacity, int32_t* order_out, double* e_out) {
+  if (!(lower > 0.f) || !(lower < 1.f) || p < 1) return 0;
+  if (iters <= 0) iters = toner::default_iterations((double)lower, p);
+  if (iters < 2) return 0;
+  const std::vector<toner::NewtonStep> sched = toner::newton_schedule((double)lower, p, iters, nullptr);
+  double l_last;
+  toner::newton_schedule((double)lower, p, iters - 1, &l_last);
+  const toner::FinishPoly fin = toner::finish_poly_or_best(p, 1.0 - l_last);
+  if (ab_out) {
+    for (int k = 0; k < iters - 1 && 2 * k + 1 < ab_capacity; ++k) {
+      ab_out[2 * k] = sched[k].a;
+      ab_out[2 * k + 1] = sched[k].b;
+    }
+  }
+  if (coef_out)
+    for (int j = 0; j <= fin.order && j < coef_capacity; ++j) coef_out[j] = fin.c[j];
+  if (order_out) *order_out = fin.order;
+  if (e_out) *e_out = 1.0 - l_last;
+  return iters;
+}
+
 int toner_inv_roots(const float* ema, int32_t k, int32_t n, float damping, int32_t p, int32_t q, int32_t iters,
                     float* root_lo, float* root_hi, float* fro2_lo, int32_t* status, void* workspace,
                     size_t workspace_bytes, void* stream_) {

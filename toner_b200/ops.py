@@ -296,10 +296,24 @@ def inv_roots_iterations_for(lower: float, p: int) -> int:
 
 
 def inv_roots_finish_order(n: int, damping: float, p: int, lower: float = 0.0, iters: int = 0) -> int:
-    """Order of the series that finishes the iteration (its order - 1 products are single passes); `lower` = 0
+    """Degree of the polynomial that finishes the iteration (its degree - 1 products are single passes); `lower` = 0
     means the bound damping / (n (1 + damping)) that always holds."""
     worst = damping / (n * (1.0 + damping))
     return _lib.load().toner_inv_roots_finish_order_for(max(lower, worst), p, iters)
+
+
+def inv_roots_schedule(lower: float, p: int, iters: int = 0) -> dict:
+    """The whole schedule the engine runs for a spectrum lower bound (toner_inv_roots_schedule; needs no device):
+    {"iterations", "steps": [(a_k, b_k), ...], "coefficients": [c_0, ...] of the finishing polynomial in powers of
+    r = 1 - mu, "distance": e}."""
+    ab = (C.c_double * 128)()
+    coef = (C.c_double * 16)()
+    order, e = C.c_int32(0), C.c_double(0.0)
+    count = _lib.load().toner_inv_roots_schedule(lower, p, iters, ab, 128, coef, 16, C.byref(order), C.byref(e))
+    if count <= 0:
+        raise ValueError("inv_roots_schedule: lower must lie inside (0, 1), p >= 1, iters 0 or >= 2")
+    return {"iterations": count, "steps": [(ab[2 * k], ab[2 * k + 1]) for k in range(count - 1)],
+            "coefficients": [coef[j] for j in range(order.value + 1)], "distance": e.value}
 
 
 def inv_roots(ema: torch.Tensor, damping: float, p: int, q: int = 1, *, iters: int = 0,
