@@ -218,8 +218,9 @@ class FactorSet:
         ops.split16(self.root_lo, planes=self.lo_planes, inv_scale=self.lo_inv, maxabs=self._root_bounds[0])
         if self.q > 1:
             ops.split16(self.root_hi, planes=self.hi_planes, inv_scale=self.hi_inv, maxabs=self._root_bounds[1])
-            ops.sumsq(self.root_hi, out=self.fro2_hi,
-                      scratch=self.scratch.bytes_like("sumsq", ops.sumsq_scratch_bytes(self.k), self.device))
+            if self.outer_strength != 0 and self._is_hi(self.outer_strength):   # (only the outer factor's norm is used)
+                ops.sumsq(self.root_hi, out=self.fro2_hi,
+                          scratch=self.scratch.bytes_like("sumsq", ops.sumsq_scratch_bytes(self.k), self.device))
 
     def finish(self) -> int:
         """Wait for the convergence flags only; recompute flagged statistics by eigendecomposition (the
