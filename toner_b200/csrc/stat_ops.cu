@@ -10,24 +10,42 @@ namespace toner {
 
 // ------------------------------------------------------------------ packed triangle -> full EMA
 // One 32x32 tile pair per block: the upper tile is updated in place from the packed triangle, the lower
-// tile is its transpose written through shared memory, so every global access is row-contiguous.
+// tile is its transpose written through shared memory, so every global access is row-contiguous.  Only the
+// tiles that meet the upper triangle are launched (blockIdx.x counts them row by row), and a thread's four
+// elements are all loaded before the first is stored.
 __global__ void __launch_bounds__(256) unpack_ema_kernel(const float* __restrict__ packed, float* __restrict__ ema, int n,
-                                                         float beta, float gamma) {
-  const int ti = blockIdx.y, tj = blockIdx.x;
-  if (ti > tj) return;
+                                                         int tiles, float beta, float gamma) {
+  // tile (ti, tj), ti <= tj, from the running index: row ti holds tiles - ti of them
+  // (rows 0 .. ti-1 hold ti * tiles - ti (ti - 1) / 2 tiles: solve for ti, then correct the rounding)
+  const int idx = blockIdx.x;
+  const float w = 2.f * tiles + 1.f;
+  int ti = (int)((w - sqrtf(fmaxf(w * w - 8.f * idx, 0.f))) * 0.5f);
+  ti = min(max(ti, 0), tiles - 1);
+  while (ti > 0 && ti * tiles - ti * (ti - 1) / 2 > idx) --ti;
+  while ((ti + 1) * tiles - (ti + 1) * ti / 2 <= idx) ++ti;
+  const int tj = ti + (idx - (ti * tiles - ti * (ti - 1) / 2));
   __shared__ float tile[32][33];
   const long long b = blockIdx.z;
   const float* P = packed + b * ((long long)n * (n + 1) / 2);
   float* C = ema + b * (long long)n * n;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = tj * 32 + tx;
+  float s[4], old[4];
+  bool on[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = ti * 32 + ty + 8 * i;
+    on[i] = r < n && c < n && r <= c;
+    s[i] = on[i] ? P[packed_off(r, c, n)] : 0.f;
+    old[i] = on[i] ? C[(long long)r * n + c] : 0.f;
+  }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int lr = ty + 8 * i;
-    const int r = ti * 32 + lr, c = tj * 32 + tx;
+    const int r = ti * 32 + lr;
     float v = 0.f;
-    if (r < n && c < n && r <= c) {
-      const float s = P[packed_off(r, c, n)];
-      v = fmaf(beta, C[(long long)r * n + c], gamma * s);
+    if (on[i]) {
+      v = fmaf(beta, old[i], gamma * s[i]);
       C[(long long)r * n + c] = v;
     }
     tile[lr][tx] = v;
@@ -36,8 +54,8 @@ __global__ void __launch_bounds__(256) unpack_ema_kernel(const float* __restrict
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int lr = ty + 8 * i;
-    const int r = tj * 32 + lr, c = ti * 32 + tx;  // element of the lower triangle, value from (c, r)
-    if (r < n && c < n && r > c) C[(long long)r * n + c] = tile[tx][lr];
+    const int r = tj * 32 + lr, cc = ti * 32 + tx;  // element of the lower triangle, value from (cc, r)
+    if (r < n && cc < n && r > cc) C[(long long)r * n + cc] = tile[tx][lr];
   }
 }
 
@@ -388,7 +406,7 @@ int toner_unpack_ema(const float* packed, float* ema, int32_t k, int32_t n, floa
   if (!packed || !ema || k <= 0 || n <= 0) return fail(kErrArg, "unpack_ema: bad arguments");
   const int t = (n + 31) / 32;
   if (k > 65535) return fail(kErrArg, "unpack_ema: k too large");
-  unpack_ema_kernel<<<dim3(t, t, k), 256, 0, static_cast<cudaStream_t>(stream)>>>(packed, ema, n, beta, gamma);
+  unpack_ema_kernel<<<dim3(t * (t + 1) / 2, 1, k), 256, 0, static_cast<cudaStream_t>(stream)>>>(packed, ema, n, t, beta, gamma);
   count_launch();
   TONER_CUDA(cudaGetLastError());
   return 0;
