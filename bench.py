@@ -399,7 +399,7 @@ def run_fast(args, w: Workload) -> None:
                                 else None),
                     "peak_source": pk["source"] + " (sustained cuBLAS BF16: the kernel runs inside a long step)",
                     "note": "achieved = algorithmic single-pass flops of the phase / its CUDA-event time on the launching "
-                            "stream; this kernel is 100 / 79 / 91 % of the statistics / factor / update phase by ncu share"}
+                            "stream; this kernel is 100 / 82 / 91 % of the statistics / factor / update phase by ncu share"}
             roof["newton_steps"] = {"hidden": cd["newton_steps"], "mlp": cf["newton_steps"]}
             roof["finish_order"] = {"hidden": cd["finish_order"], "mlp": cf["finish_order"]}
             if top == "roots":

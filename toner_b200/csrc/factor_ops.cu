@@ -511,20 +511,29 @@ __global__ void __launch_bounds__(256) block_gemv_kernel(const float* __restrict
     }
     __syncthreads();
     const int ca = c0 + lane * 4, cb = ca + 128;
+    // this lane's eight columns of every vector, read from shared memory once for the warp's four rows (read per
+    // row, the shared-memory traffic is R times the traffic of A and sets the pace from four vectors on)
+    float4 x0[R], x1[R];
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+      x0[j] = sv[j][lane];
+      x1[j] = sv[j][lane + 32];
+    }
+    float4 p0[4], p1[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int row = row0 + i;
-      if (row < n) {
-        const float* Ar = A + (long long)row * n;
-        const float4 p0 = ca < n ? *reinterpret_cast<const float4*>(Ar + ca) : zero;
-        const float4 p1 = cb < n ? *reinterpret_cast<const float4*>(Ar + cb) : zero;
+      const float* Ar = A + (long long)row * n;
+      p0[i] = (row < n && ca < n) ? *reinterpret_cast<const float4*>(Ar + ca) : zero;
+      p1[i] = (row < n && cb < n) ? *reinterpret_cast<const float4*>(Ar + cb) : zero;
+    }
 #pragma unroll
-        for (int j = 0; j < R; ++j) {
-          const float4 x0 = sv[j][lane], x1 = sv[j][lane + 32];
-          const float s0 = fmaf(p0.x, x0.x, fmaf(p0.y, x0.y, fmaf(p0.z, x0.z, p0.w * x0.w)));
-          const float s1 = fmaf(p1.x, x1.x, fmaf(p1.y, x1.y, fmaf(p1.z, x1.z, p1.w * x1.w)));
-          part[i][j] += s0 + s1;
-        }
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+      for (int j = 0; j < R; ++j) {
+        const float s0 = fmaf(p0[i].x, x0[j].x, fmaf(p0[i].y, x0[j].y, fmaf(p0[i].z, x0[j].z, p0[i].w * x0[j].w)));
+        const float s1 = fmaf(p1[i].x, x1[j].x, fmaf(p1[i].y, x1[j].y, fmaf(p1[i].z, x1[j].z, p1[i].w * x1[j].w)));
+        part[i][j] += s0 + s1;
       }
     }
     if ((slice & 3) == 3) {
